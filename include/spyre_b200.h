@@ -1,0 +1,164 @@
+/* C ABI of libspyre_b200.so: hand-written sm_100a kernels for torch-spyre's
+ * data-parallel hot path (stick relayout in host<->device copy_, fp16
+ * pointwise / reduction / softmax / layernorm / matmul).
+ *
+ * Conventions for every entry point
+ *   - returns TS_OK (0) or a negative TS_ERR_* code; never throws, never
+ *     aborts, never synchronises the device;
+ *   - unless its comment says otherwise it allocates nothing: the caller owns
+ *     every buffer, including scratch;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream); work is enqueued on it and the call returns;
+ *   - device pointers are plain addresses in the current CUDA device's memory;
+ *   - a "stick image" is the device byte image of a tensor in the generic
+ *     stick layout of SpyreTensorLayout (torch_spyre/csrc/spyre_tensor_impl.cpp:
+ *     39-74): for a logical [rows..., cols] fp16 tensor it is the contiguous
+ *     array [ceil(cols/64)][rows...][64]; lanes past `cols` are zero.
+ *
+ * Each declaration cites the reference interface it stands in for.
+ */
+#ifndef SPYRE_B200_H_
+#define SPYRE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TS_MAX_DIMS 8
+
+enum {
+  TS_OK = 0,
+  TS_ERR_INVALID = -1,     /* null pointer, bad rank, negative size ...        */
+  TS_ERR_UNSUPPORTED = -2, /* well-formed request this build has no kernel for */
+  TS_ERR_CUDA = -3,        /* a CUDA runtime call or launch failed             */
+  TS_ERR_ALIGNMENT = -4,   /* pointer or stride not aligned as the entry needs */
+  TS_ERR_TOO_LARGE = -5    /* size beyond a stated maximum                      */
+};
+
+/* Human-readable text for a status code (static storage). */
+const char* ts_status_string(int status);
+/* ABI version of the loaded library (bumped on incompatible change). */
+int ts_abi_version(void);
+/* Text of the last CUDA error this thread's failing call saw, "" if none. */
+const char* ts_last_cuda_error(void);
+
+/* ---- stick relayout (the device half of host<->device copy_) -------------
+ *
+ * Replaces the SenDataConvert host pass + DMA that the reference builds in
+ * create_dma_graph / generate_dci / get_device_stride_info
+ * (torch_spyre/csrc/spyre_mem.cpp:213-279, 281-438).
+ *
+ * `strided` is a device-resident raw image of the host tensor's storage
+ * (element strides `host_strides`, any order, in elements); `sticks` is the
+ * image described by a SpyreTensorLayout (device_size / device_strides /
+ * dim_map, ndev entries, outermost first).  A host dim that appears several
+ * times in dim_map is split over those device dims, outermost most
+ * significant.  to_sticks writes every element of the stick image (pad lanes
+ * become zero); from_sticks writes exactly the host tensor's elements.
+ * elem_bytes is 1, 2 or 4.  Bit-exact: elements are moved, never converted.
+ */
+int ts_relayout_to_sticks(const void* strided, void* sticks, int elem_bytes,
+                          const int64_t* host_size, const int64_t* host_strides, int rank,
+                          const int64_t* device_size, const int64_t* device_strides,
+                          const int32_t* dim_map, int ndev, void* stream);
+int ts_relayout_from_sticks(const void* sticks, void* strided, int elem_bytes,
+                            const int64_t* host_size, const int64_t* host_strides, int rank,
+                            const int64_t* device_size, const int64_t* device_strides,
+                            const int32_t* dim_map, int ndev, void* stream);
+
+/* Host-buffer forms of the two calls above, i.e. copy_host_to_device /
+ * copy_device_to_host (torch_spyre/csrc/spyre_mem.cpp:408-438).  `host` points
+ * at the element with all-zero index; the host tensor must have non-negative
+ * strides.  `staging` is a caller-owned device buffer of at least
+ * ts_host_span_bytes(...) bytes.  The raw span of host storage the tensor
+ * touches is copied with cudaMemcpyAsync (pinned host memory makes it
+ * asynchronous) and relaid out on the device, all on `stream`.
+ */
+int64_t ts_host_span_bytes(int elem_bytes, const int64_t* host_size,
+                           const int64_t* host_strides, int rank);
+int ts_copy_host_to_sticks(const void* host, void* staging, void* sticks, int elem_bytes,
+                           const int64_t* host_size, const int64_t* host_strides, int rank,
+                           const int64_t* device_size, const int64_t* device_strides,
+                           const int32_t* dim_map, int ndev, void* stream);
+int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int elem_bytes,
+                           const int64_t* host_size, const int64_t* host_strides, int rank,
+                           const int64_t* device_size, const int64_t* device_strides,
+                           const int32_t* dim_map, int ndev, void* stream);
+
+/* SpyreTensorLayout::init (torch_spyre/csrc/spyre_tensor_impl.cpp:29-74) as a
+ * plain function: fills device_size / device_strides / dim_map (rank + 1
+ * entries each) for the generic stick layout of host_size; dim_order may be
+ * NULL for the identity order.  Returns the number of device dims or an error.
+ */
+int ts_layout_init(const int64_t* host_size, int rank, int elem_bytes, const int32_t* dim_order,
+                   int64_t* device_size, int64_t* device_strides, int32_t* dim_map);
+
+/* ---- fused pointwise chain with optional row reduction --------------------
+ *
+ * One launch evaluates a whole fused group of fp16 pointwise ops and, if
+ * asked, reduces the result along the innermost (stick) dim.  It replaces the
+ * one-op-per-kernel sfp programs generate_sfp_op emits
+ * (torch_spyre/_inductor/codegen/compute_ops.py:60-393, op table
+ * torch_spyre/_inductor/opfuncs.py:21-84) and the eager wrappers rendered from
+ * codegen/templates/base.jinja2:16-241 for the pointwise ops of
+ * codegen/inputs/Metadata.yaml.
+ *
+ * The group is a small program for an accumulator machine working on fp16
+ * values (every op result is rounded to fp16, as eager fp16 does):
+ *     acc = f(acc, A [, B])
+ * where A and B are operands: an input tensor, an immediate, or one of
+ * TS_PW_SAVED_SLOTS saved values.
+ *
+ * Shapes: the iteration space is [d0, d1, d2, cols]; every tensor's stick
+ * image is that of a logical tensor whose dims are either equal to the
+ * iteration space's or 1 (broadcast), given as 4 int64 per tensor.
+ * Full-shape outputs are written by TS_PW_STORE.  With reduce_op != 0 the
+ * final acc is reduced over `cols`, multiplied by reduce_scale, and written to
+ * reduce_out, which is the stick image of
+ *   - [d0*d1*d2, 1]            if reduce_keepdim != 0 (one stick per row), or
+ *   - [(d0*d1*d2)/reduce_inner, reduce_inner]  otherwise, reduce_inner being
+ *     the extent of the innermost dim the result keeps.
+ */
+enum {
+  TS_PW_NONE = 0, TS_PW_TENSOR = 1, TS_PW_IMM = 2, TS_PW_SAVED = 3
+};
+enum {
+  TS_PW_LOAD = 0,  /* acc = A                          */
+  TS_PW_SAVE,      /* saved[a_idx] = acc               */
+  TS_PW_STORE,     /* output[a_idx] = acc              */
+  TS_PW_ADD, TS_PW_SUB, TS_PW_RSUB, TS_PW_MUL, TS_PW_DIV, TS_PW_RDIV,
+  TS_PW_MAX, TS_PW_MIN, TS_PW_POW,
+  TS_PW_EQ, TS_PW_NE, TS_PW_LT, TS_PW_LE, TS_PW_GT, TS_PW_GE, /* acc ? A -> 1.0 / 0.0 */
+  TS_PW_WHERE,     /* acc = acc != 0 ? A : B           */
+  TS_PW_NEG, TS_PW_ABS, TS_PW_EXP, TS_PW_LOG, TS_PW_SQRT, TS_PW_RSQRT, TS_PW_RECIP,
+  TS_PW_SIGMOID, TS_PW_TANH, TS_PW_RELU, TS_PW_SILU, TS_PW_GELU, TS_PW_GELU_TANH,
+  TS_PW_SQUARE, TS_PW_LOGICAL_NOT, TS_PW_SIN, TS_PW_COS, TS_PW_ERF, TS_PW_FLOOR,
+  TS_PW_CEIL, TS_PW_SIGN, TS_PW_LOG1P, TS_PW_EXPM1, TS_PW_SOFTPLUS, TS_PW_MISH,
+  TS_PW_OPCOUNT
+};
+enum { TS_RED_NONE = 0, TS_RED_SUM = 1, TS_RED_MAX = 2, TS_RED_MIN = 3 };
+#define TS_PW_MAX_INSNS 32
+#define TS_PW_MAX_INPUTS 8
+#define TS_PW_MAX_OUTPUTS 4
+#define TS_PW_SAVED_SLOTS 4
+
+typedef struct ts_pw_insn {
+  int32_t op;
+  int32_t a_kind, a_idx;
+  int32_t b_kind, b_idx;
+  float a_imm, b_imm;
+} ts_pw_insn;
+
+int ts_pointwise_chain(const ts_pw_insn* insns, int n_insns,
+                       const void* const* inputs, const int64_t* input_shapes, int n_inputs,
+                       void* const* outputs, int n_outputs,
+                       const int64_t* shape /* d0, d1, d2, cols */,
+                       int reduce_op, float reduce_scale, void* reduce_out,
+                       int reduce_keepdim, int64_t reduce_inner, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPYRE_B200_H_ */
