@@ -1,0 +1,430 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Default workload ("fused"): y = exp(x*a + b).sum(-1), x fp16 [8192, 8192] N(0,1),
+a and b fp16 [8192] U(-1,1), one fused kernel per step over inputs resident in
+HBM as stick images.  A step reads a different x buffer of a ring larger than L2.
+Other workloads: softmax, softmax_scaled, relayout, relayout_permuted.
+Under torchrun every rank runs the same per-GPU workload on its own shard of
+rows (weak scaling, no collective on the data path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "torch-spyre_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p.get("hbm_gbs", 6650.0), p.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [p.strip() for p in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- workloads
+
+def make_workload(name: str, dev):
+    """Returns dict(step_dev, step_e2e, alg_bytes, h2d, d2h, launches, desc, cpu_step, sample)."""
+    from oracle import math_ref
+    from torch_spyre import stick_ops as K
+
+    if name == "fused":
+        rows = cols = 8192
+        x, a, b = math_ref.fused_inputs(rows, cols)
+        xp, ap, bp = x.pin_memory(), a.pin_memory(), b.pin_memory()
+        ring = max(2, -(-2 * L2_BYTES // (rows * cols * 2)) + 1)  # ring of x buffers > 2x L2
+        sa, sb = K.copy_host_to_sticks(ap), K.copy_host_to_sticks(bp)
+        xs = [K.copy_host_to_sticks(xp)]
+        for _ in range(ring - 1):
+            xs.append(K.StickTensor(xs[0].image.clone(), xs[0].shape))
+        out = K.empty((rows,))
+
+        def chain_on(sx, sa_, sb_):
+            c = K.Chain()
+            c.emit("LOAD", c.tensor(sx)).emit("MUL", c.tensor(sa_)).emit("ADD", c.tensor(sb_)).emit("EXP")
+            return c
+
+        launches = [K.prepare_chain(chain_on(sx, sa, sb), (rows, cols), n_outputs=0, reduce="sum")[0]
+                    for sx in xs]
+        state = {"i": 0}
+
+        def step_dev():
+            launches[state["i"] % ring]()
+            state["i"] += 1
+
+        staging = torch.empty(rows * cols * 2, dtype=torch.uint8, device=dev)
+        sx_e, sa_e, sb_e = K.empty((rows, cols)), K.empty((cols,)), K.empty((cols,))
+        y_host = torch.empty(rows, dtype=torch.float16).pin_memory()
+        y_stage = torch.empty(rows * 2, dtype=torch.uint8, device=dev)
+
+        def step_e2e():
+            K.copy_host_to_sticks(xp, sx_e, staging)
+            K.copy_host_to_sticks(ap, sa_e)
+            K.copy_host_to_sticks(bp, sb_e)
+            _, r = K.run_chain(chain_on(sx_e, sa_e, sb_e), (rows, cols), n_outputs=0, reduce="sum")
+            K.copy_sticks_to_host(r, y_host, y_stage)
+            torch.cuda.current_stream().synchronize()
+            return y_host
+
+        alg = rows * cols * 2 + cols * 2 * 2 + rows * 2
+
+        def cpu_step():
+            return math_ref.fused_ref(x, a, b)
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=alg,
+                    h2d=rows * cols * 2 + 2 * cols * 2, d2h=rows * 2, launches=1,
+                    desc=f"exp(x*a+b).sum(-1), x fp16 [{rows},{cols}] (BASELINE configs[1])",
+                    l2=f"ring of {ring} x buffers ({ring * rows * cols * 2 >> 20} MiB) > L2",
+                    cpu_step=cpu_step, sample="full [8192,8192] graph per CPU step",
+                    check=lambda: math_ref.assert_close(step_e2e().clone(), cpu_step()))
+
+    if name in ("softmax", "softmax_scaled"):
+        rows, cols = (256, 4096) if name == "softmax" else (65536, 4096)
+        x = math_ref.softmax_inputs(256, cols)
+        if rows != 256:
+            x = x.repeat(rows // 256, 1)
+        xp = x.pin_memory()
+        ring = max(2, -(-2 * L2_BYTES // (rows * cols * 2)) + 1)
+        ring = min(ring, 160)
+        xs = [K.copy_host_to_sticks(xp)]
+        for _ in range(ring - 1):
+            xs.append(K.StickTensor(xs[0].image.clone(), xs[0].shape))
+        outs = [K.empty((rows, cols)) for _ in range(min(ring, 4) if rows > 256 else ring)]
+        state = {"i": 0}
+
+        def step_dev():
+            i = state["i"]
+            state["i"] += 1
+            K.softmax_rows(xs[i % ring], out=outs[i % len(outs)])
+
+        staging = torch.empty(rows * cols * 2, dtype=torch.uint8, device=dev)
+        sx_e, sy_e = K.empty((rows, cols)), K.empty((rows, cols))
+        y_host = torch.empty(rows, cols, dtype=torch.float16).pin_memory()
+
+        def step_e2e():
+            K.copy_host_to_sticks(xp, sx_e, staging)
+            K.softmax_rows(sx_e, out=sy_e)
+            K.copy_sticks_to_host(sy_e, y_host, staging)
+            torch.cuda.current_stream().synchronize()
+            return y_host
+
+        def cpu_step():
+            return torch.softmax(x, -1)
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=2 * rows * cols * 2,
+                    h2d=rows * cols * 2, d2h=rows * cols * 2, launches=1,
+                    desc=f"softmax(dim=-1) fp16 [{rows},{cols}]" +
+                         (" (BASELINE configs[0])" if rows == 256 else " (configs[0] scaled along rows)"),
+                    l2=f"ring of {ring} input buffers ({ring * rows * cols * 2 >> 20} MiB) > L2",
+                    cpu_step=cpu_step, sample=f"full [{rows},{cols}] softmax per CPU step",
+                    check=lambda: math_ref.assert_close(step_e2e().clone(), cpu_step()))
+
+    if name in ("relayout", "relayout_permuted"):
+        permuted = name.endswith("permuted")
+        shape = (64, 2048, 4096)
+        g = torch.Generator().manual_seed(0)
+        # a [4,...] seeded block repeated along dim 0 keeps host generation quick
+        blk = math_ref.relayout_inputs((4,) + shape[1:], 0, permuted=False)
+        host = blk.repeat(16, 1, 1)
+        if permuted:
+            host = host.permute(0, 2, 1).contiguous().permute(0, 2, 1)
+        hp = host.pin_memory()
+        raw = hp.to(dev, non_blocking=True)
+        assert raw.stride() == host.stride()
+        st = K.to_sticks(raw)
+        back = torch.empty_strided(shape, host.stride(), dtype=host.dtype, device=dev)
+        state = {"i": 0}
+
+        def step_dev():
+            # one step = host image -> sticks -> host image, both directions of copy_
+            K.to_sticks(raw, out=st)
+            K.from_sticks(st, out=back)
+
+        staging = torch.empty(host.numel() * 2, dtype=torch.uint8, device=dev)
+        out_host = torch.empty_strided(shape, host.stride(), dtype=host.dtype).pin_memory()
+
+        def step_e2e():
+            K.copy_host_to_sticks(hp, st, staging)
+            K.copy_sticks_to_host(st, out_host, staging)
+            torch.cuda.current_stream().synchronize()
+            return out_host
+
+        nbytes = host.numel() * 2
+
+        def check():
+            if not torch.equal(step_e2e().view(torch.int16), host.view(torch.int16)):
+                raise AssertionError("relayout round trip is not the identity")
+            if not torch.equal(back.view(torch.int16).cpu()[:2], host.view(torch.int16)[:2]):
+                step_dev()
+                torch.cuda.synchronize()
+                assert torch.equal(back.view(torch.int16).cpu(), host.view(torch.int16))
+
+        def cpu_step():
+            import numpy as np
+            from oracle import layout as OL, relayout_c as OC
+            h = host[:8].view(torch.int16).numpy().view(np.uint16)
+            img = OC.to_sticks(h, OL.generic_stick_layout(h.shape), nthreads=os.cpu_count() or 1)
+            return OC.from_sticks(img, OL.generic_stick_layout(h.shape), h.shape,
+                                  nthreads=os.cpu_count() or 1)
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=4 * nbytes,
+                    h2d=nbytes, d2h=nbytes, launches=2,
+                    desc=f"stick relayout fp16 {list(shape)} host strides {list(host.stride())}, "
+                         "to sticks and back (BASELINE configs[2])",
+                    l2="1 GiB tensors, far larger than L2", cpu_step=cpu_step, cpu_scale=8.0,
+                    sample="C oracle on a [8,2048,4096] slice (1/8 of the tensor), all host threads",
+                    cpu_kind="port", check=check)
+    raise SystemExit(f"unknown workload {name}")
+
+
+# --------------------------------------------------------------------------- timing
+
+def time_device(step, steps, warmup):
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / 1e3
+
+
+def time_cpu(fn, budget_s=12.0, min_runs=3):
+    fn()
+    times = []
+    t_end = time.perf_counter() + budget_s
+    while len(times) < min_runs or time.perf_counter() < t_end:
+        t0 = time.perf_counter()
+        fn()
+        times.append(time.perf_counter() - t0)
+        if len(times) >= 200:
+            break
+    times.sort()
+    return times[len(times) // 2], len(times)
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the path's CPU implementation (torch CPU eager, which is what
+    the reference's tests hold the device to) on the host cores."""
+    if rank != 0:
+        return
+    from oracle import math_ref  # noqa: F401
+    wl = make_workload_cpu(args.workload)
+    wl["cpu_step"]()
+    for _ in range(max(args.warmup - 1, 0)):
+        wl["cpu_step"]()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        wl["cpu_step"]()
+    dt = (time.perf_counter() - t0) / args.steps
+    scale = wl.get("cpu_scale", 1.0)
+    gbs = wl["alg_bytes"] / scale / dt / 1e9
+    cores = torch.get_num_threads()
+    line = {"impl": "reference", "metric": "achieved GB/s (algorithmic bytes / time)", "value": gbs,
+            "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt * 1e3 * scale, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": wl["desc"]},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference",
+                             "sample": wl["sample"] + "; torch CPU eager / C oracle on host cores"},
+            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def make_workload_cpu(name):
+    """CPU-only description of a workload (no CUDA needed): used by the reference arm."""
+    from oracle import math_ref
+    if name == "fused":
+        x, a, b = math_ref.fused_inputs()
+        return dict(cpu_step=lambda: math_ref.fused_ref(x, a, b), alg_bytes=134266880,
+                    desc="exp(x*a+b).sum(-1), x fp16 [8192,8192] (BASELINE configs[1])",
+                    sample="full [8192,8192] graph per CPU step")
+    if name in ("softmax", "softmax_scaled"):
+        rows = 256 if name == "softmax" else 65536
+        x = math_ref.softmax_inputs(256, 4096).repeat(rows // 256, 1)
+        return dict(cpu_step=lambda: torch.softmax(x, -1), alg_bytes=2 * rows * 4096 * 2,
+                    desc=f"softmax(dim=-1) fp16 [{rows},4096]", sample="full softmax per CPU step")
+    if name in ("relayout", "relayout_permuted"):
+        import numpy as np
+        from oracle import layout as OL, relayout_c as OC
+        host = math_ref.relayout_inputs((8, 2048, 4096), 0, permuted=name.endswith("permuted"))
+        h = host.view(torch.int16).numpy().view(np.uint16)
+        lay = OL.generic_stick_layout(h.shape)
+        nt = os.cpu_count() or 1
+
+        def cpu_step():
+            return OC.from_sticks(OC.to_sticks(h, lay, nthreads=nt), lay, h.shape, nthreads=nt)
+
+        return dict(cpu_step=cpu_step, alg_bytes=4 * 64 * 2048 * 4096 * 2, cpu_scale=8.0,
+                    desc="stick relayout fp16 [64,2048,4096], to sticks and back (BASELINE configs[2])",
+                    sample="C oracle on a [8,2048,4096] slice (1/8 of the tensor)")
+    raise SystemExit(f"unknown workload {name}")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="fused")
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    wl = make_workload(args.workload, dev)
+    wl["check"]()  # parity of one step against the CPU oracle before timing anything
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    barrier()
+    dt = time_device(wl["step_dev"], args.steps, args.warmup)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+
+    e2e_dt = None
+    if not args.no_e2e:
+        e2e_steps = max(3, min(args.steps, 20))
+        for _ in range(3):
+            wl["step_e2e"]()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            wl["step_e2e"]()
+        torch.cuda.synchronize()
+        e2e_dt = (time.perf_counter() - t0) / e2e_steps
+
+    if dist is not None:
+        t = torch.tensor([dt, e2e_dt or 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dt, e2e_dt = float(t[0]), (float(t[1]) if e2e_dt is not None else None)
+
+    if rank == 0:
+        hbm, _, which = measured_peaks()
+        per_gpu = wl["alg_bytes"] * args.steps / dt / 1e9
+        line = {
+            "metric": "achieved GB/s (algorithmic bytes / time)", "value": per_gpu * world,
+            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": wl["desc"], "l2": wl["l2"],
+                       "sharding": f"{world} x the per-GPU workload, rows sharded, no collective"},
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s",
+                         "frac": per_gpu / hbm, "traffic": None, "peak_source": which},
+            "gpu_launches": wl["launches"] * args.steps,
+            "clocks": clocks,
+        }
+        if e2e_dt is not None:
+            line["e2e"] = {"value": wl["alg_bytes"] / e2e_dt / 1e9 * world, "unit": "GB/s",
+                           "h2d_bytes_per_step": wl["h2d"], "d2h_bytes_per_step": wl["d2h"],
+                           "ms_per_step": e2e_dt * 1e3}
+        if not args.no_cpu_baseline and world == 1:
+            med, n = time_cpu(wl["cpu_step"])
+            scale = wl.get("cpu_scale", 1.0)
+            line["cpu_baseline"] = {"value": wl["alg_bytes"] / scale / med / 1e9, "unit": "GB/s",
+                                    "cores": torch.get_num_threads(),
+                                    "kind": wl.get("cpu_kind", "reference"),
+                                    "sample": f"{wl['sample']}; median of {n} runs; "
+                                              "torch CPU eager / C oracle on the host cores"}
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

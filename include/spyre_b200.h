@@ -158,6 +158,52 @@ int ts_pointwise_chain(const ts_pw_insn* insns, int n_insns,
                        int reduce_op, float reduce_scale, void* reduce_out,
                        int reduce_keepdim, int64_t reduce_inner, void* stream);
 
+/* ---- row-wise normalisations along the stick dim ---------------------------
+ *
+ * x and y are stick images of a logical [rows, cols] fp16 tensor (leading dims
+ * flattened into rows); statistics are computed in fp32 and the result is
+ * rounded to fp16 once.  cols <= TS_ROW_MAX_COLS.
+ *
+ * ts_softmax_rows stands in for the eager _softmax wrapper (codegen/inputs/
+ * Metadata.yaml:275-277 via codegen/templates/base.jinja2:16-241) and for the
+ * max/sub/exp/sum/div kernels of the compiled decomposition
+ * (torch_spyre/_inductor/__init__.py:81-84).
+ * ts_layernorm_rows stands in for spyre.layer_norm and its exx2 ->
+ * layernormscale -> layernormnorm decomposition (torch_spyre/_inductor/
+ * customops.py:74-154, decompositions.py:26-36, lowering.py:78-153); weight and
+ * bias are 1-D [cols] stick images or NULL.
+ * ts_rmsnorm_rows is the pow/mean/rsqrt/mul chain of an RMSNorm module fused
+ * into one pass; round_before_weight != 0 rounds the normalised value to fp16
+ * before the fp16 multiply by weight (module semantics), 0 rounds once.
+ */
+#define TS_ROW_MAX_COLS 8192
+int ts_softmax_rows(const void* x, void* y, int64_t rows, int64_t cols, int log_softmax,
+                    void* stream);
+int ts_layernorm_rows(const void* x, const void* weight, const void* bias, void* y, int64_t rows,
+                      int64_t cols, float eps, void* stream);
+int ts_rmsnorm_rows(const void* x, const void* weight, void* y, int64_t rows, int64_t cols,
+                    float eps, int round_before_weight, void* stream);
+
+/* ---- reductions and softmax along a non-stick dim ---------------------------
+ *
+ * The image is viewed as the contiguous fp16 array [outer][red][inner] with
+ * inner a multiple of 8 elements (for a logical [A, red, B, cols] tensor:
+ * outer = ceil(cols/64) * A, inner = B * 64).  These are the "nonstick"
+ * reductions of generate_sfp_op (torch_spyre/_inductor/codegen/compute_ops.py:
+ * 75-76; ops sum/max/min, torch_spyre/_inductor/opfuncs.py:26-39).
+ *
+ * ts_reduce_mid writes [outer][inner] = scale * reduce(x) in fp16.  When the
+ * launch splits `red` over several thread blocks it needs `scratch`, a device
+ * buffer of ts_reduce_mid_scratch_bytes(outer, red, inner) bytes (0 means no
+ * scratch is needed and NULL may be passed).
+ * ts_softmax_mid writes the softmax along red, same shape as x.
+ */
+int64_t ts_reduce_mid_scratch_bytes(int64_t outer, int64_t red, int64_t inner);
+int ts_reduce_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t inner, int reduce_op,
+                  float scale, void* scratch, void* stream);
+int ts_softmax_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
+                   int log_softmax, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

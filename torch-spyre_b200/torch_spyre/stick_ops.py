@@ -1,0 +1,340 @@
+"""Kernel launches over stick images held in CUDA memory.
+
+A ``StickTensor`` is a logical fp16 tensor plus the flat CUDA buffer holding its
+stick image (generic SpyreTensorLayout: [ceil(cols/64)][leading dims...][64], pad
+lanes zero).  Every function here is a thin argument-marshalling layer over one
+C-ABI entry point; PyTorch is used for device memory and streams only.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _abi
+from ._abi import PwInsn
+from .layout import SpyreTensorLayout
+
+# Opcode / operand-kind numbers of include/spyre_b200.h.
+NONE, TENSOR, IMM, SAVED = 0, 1, 2, 3
+_OPS = ("LOAD SAVE STORE ADD SUB RSUB MUL DIV RDIV MAX MIN POW EQ NE LT LE GT GE WHERE NEG ABS "
+        "EXP LOG SQRT RSQRT RECIP SIGMOID TANH RELU SILU GELU GELU_TANH SQUARE LOGICAL_NOT SIN "
+        "COS ERF FLOOR CEIL SIGN LOG1P EXPM1 SOFTPLUS MISH").split()
+OP = {name: i for i, name in enumerate(_OPS)}
+RED = {None: 0, "sum": 1, "max": 2, "min": 3}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+@dataclass
+class StickTensor:
+    image: torch.Tensor          # flat CUDA tensor holding the stick image
+    shape: Tuple[int, ...]       # logical (host) shape
+    dtype: torch.dtype = torch.float16
+
+    @property
+    def layout(self) -> SpyreTensorLayout:
+        return SpyreTensorLayout(list(self.shape) if self.shape else [1], self.dtype)
+
+    @property
+    def rows(self) -> int:
+        n = 1
+        for s in self.shape[:-1]:
+            n *= s
+        return n
+
+    @property
+    def cols(self) -> int:
+        return self.shape[-1] if self.shape else 1
+
+    def ptr(self) -> int:
+        return self.image.data_ptr()
+
+
+def empty(shape: Sequence[int], dtype: torch.dtype = torch.float16, device=None) -> StickTensor:
+    shape = tuple(int(s) for s in shape)
+    lay = SpyreTensorLayout(list(shape) if shape else [1], dtype)
+    n = 0 if any(s == 0 for s in shape) else lay.numel()
+    return StickTensor(torch.empty(n, dtype=dtype, device=device or "cuda"), shape, dtype)
+
+
+def _layout_args(lay: SpyreTensorLayout):
+    return (_abi.i64(lay.device_size), _abi.i64(lay.device_strides), _abi.i32(lay.dim_map),
+            len(lay.device_size))
+
+
+def to_sticks(raw: torch.Tensor, layout: Optional[SpyreTensorLayout] = None,
+              out: Optional[StickTensor] = None) -> StickTensor:
+    """raw: CUDA tensor of any strides (a device-resident image of a host tensor)."""
+    shape = tuple(raw.shape) if raw.dim() else (1,)
+    strides = tuple(raw.stride()) if raw.dim() else (1,)
+    lay = layout or SpyreTensorLayout(list(shape), raw.dtype)
+    if out is None:
+        out = StickTensor(torch.empty(lay.numel(), dtype=raw.dtype, device=raw.device), shape,
+                          raw.dtype)
+    ds, dst, dm, nd = _layout_args(lay)
+    rc = _abi.lib().ts_relayout_to_sticks(raw.data_ptr(), out.ptr(), raw.element_size(),
+                                          _abi.i64(shape), _abi.i64(strides), len(shape),
+                                          ds, dst, dm, nd, _stream())
+    _abi.check(rc, "ts_relayout_to_sticks")
+    return out
+
+
+def from_sticks(st: StickTensor, out: Optional[torch.Tensor] = None,
+                layout: Optional[SpyreTensorLayout] = None) -> torch.Tensor:
+    """Returns (or fills) a CUDA tensor with the logical contents; ``out`` may have any strides."""
+    shape = st.shape if st.shape else (1,)
+    if out is None:
+        out = torch.empty(shape, dtype=st.dtype, device=st.image.device)
+    lay = layout or st.layout
+    ds, dst, dm, nd = _layout_args(lay)
+    rc = _abi.lib().ts_relayout_from_sticks(st.ptr(), out.data_ptr(), out.element_size(),
+                                            _abi.i64(shape), _abi.i64(tuple(out.stride())),
+                                            len(shape), ds, dst, dm, nd, _stream())
+    _abi.check(rc, "ts_relayout_from_sticks")
+    return out
+
+
+def host_span(t: torch.Tensor) -> int:
+    shape = tuple(t.shape) if t.dim() else (1,)
+    strides = tuple(t.stride()) if t.dim() else (1,)
+    n = _abi.lib().ts_host_span_bytes(t.element_size(), _abi.i64(shape), _abi.i64(strides),
+                                      len(shape))
+    if n < 0:
+        _abi.check(int(n), "ts_host_span_bytes")
+    return int(n)
+
+
+def copy_host_to_sticks(host: torch.Tensor, out: Optional[StickTensor] = None,
+                        staging: Optional[torch.Tensor] = None) -> StickTensor:
+    """Host tensor (any non-negative strides; pinned memory makes the copy asynchronous)
+    -> stick image on the current CUDA device."""
+    shape = tuple(host.shape) if host.dim() else (1,)
+    strides = tuple(host.stride()) if host.dim() else (1,)
+    lay = SpyreTensorLayout(list(shape), host.dtype)
+    if out is None:
+        out = empty(shape, host.dtype)
+    span = host_span(host)
+    if staging is None or staging.numel() * staging.element_size() < span:
+        staging = torch.empty(max(span, 16), dtype=torch.uint8, device=out.image.device)
+    ds, dst, dm, nd = _layout_args(lay)
+    rc = _abi.lib().ts_copy_host_to_sticks(host.data_ptr(), staging.data_ptr(), out.ptr(),
+                                           host.element_size(), _abi.i64(shape),
+                                           _abi.i64(strides), len(shape), ds, dst, dm, nd,
+                                           _stream())
+    _abi.check(rc, "ts_copy_host_to_sticks")
+    return out
+
+
+def copy_sticks_to_host(st: StickTensor, host: torch.Tensor,
+                        staging: Optional[torch.Tensor] = None) -> torch.Tensor:
+    shape = st.shape if st.shape else (1,)
+    strides = tuple(host.stride()) if host.dim() else (1,)
+    span = host_span(host)
+    if staging is None or staging.numel() * staging.element_size() < span:
+        staging = torch.empty(max(span, 16), dtype=torch.uint8, device=st.image.device)
+    ds, dst, dm, nd = _layout_args(st.layout)
+    rc = _abi.lib().ts_copy_sticks_to_host(st.ptr(), staging.data_ptr(), host.data_ptr(),
+                                           host.element_size(), _abi.i64(shape),
+                                           _abi.i64(strides), len(shape), ds, dst, dm, nd,
+                                           _stream())
+    _abi.check(rc, "ts_copy_sticks_to_host")
+    return host
+
+
+# ---- row-wise ops ---------------------------------------------------------------
+
+def softmax_rows(x: StickTensor, log: bool = False, out: Optional[StickTensor] = None) -> StickTensor:
+    out = out or empty(x.shape, x.dtype, x.image.device)
+    rc = _abi.lib().ts_softmax_rows(x.ptr(), out.ptr(), x.rows, x.cols, int(log), _stream())
+    _abi.check(rc, "ts_softmax_rows")
+    return out
+
+
+def layernorm_rows(x: StickTensor, weight: Optional[StickTensor], bias: Optional[StickTensor],
+                   eps: float, out: Optional[StickTensor] = None) -> StickTensor:
+    out = out or empty(x.shape, x.dtype, x.image.device)
+    rc = _abi.lib().ts_layernorm_rows(x.ptr(), weight.ptr() if weight else None,
+                                      bias.ptr() if bias else None, out.ptr(), x.rows, x.cols,
+                                      eps, _stream())
+    _abi.check(rc, "ts_layernorm_rows")
+    return out
+
+
+def rmsnorm_rows(x: StickTensor, weight: Optional[StickTensor], eps: float,
+                 round_before_weight: bool = True, out: Optional[StickTensor] = None) -> StickTensor:
+    out = out or empty(x.shape, x.dtype, x.image.device)
+    rc = _abi.lib().ts_rmsnorm_rows(x.ptr(), weight.ptr() if weight else None, out.ptr(), x.rows,
+                                    x.cols, eps, int(round_before_weight), _stream())
+    _abi.check(rc, "ts_rmsnorm_rows")
+    return out
+
+
+# ---- non-stick-dim ops ----------------------------------------------------------
+
+def _mid_view(shape: Sequence[int], dim: int) -> Tuple[int, int, int]:
+    """[outer][red][inner] view of the stick image for a reduction over `dim` (not the last)."""
+    nsticks = -(-shape[-1] // 64)
+    a = 1
+    for s in shape[:dim]:
+        a *= s
+    b = 1
+    for s in shape[dim + 1:-1]:
+        b *= s
+    return nsticks * a, shape[dim], b * 64
+
+
+def reduce_mid(x: StickTensor, dim: int, op: str, scale: float = 1.0, keepdim: bool = False) -> StickTensor:
+    outer, red, inner = _mid_view(x.shape, dim)
+    new_shape = list(x.shape)
+    if keepdim:
+        new_shape[dim] = 1
+    else:
+        del new_shape[dim]
+    out = empty(new_shape, x.dtype, x.image.device)
+    nbytes = _abi.lib().ts_reduce_mid_scratch_bytes(outer, red, inner)
+    if nbytes < 0:
+        _abi.check(int(nbytes), "ts_reduce_mid_scratch_bytes")
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.image.device) if nbytes else None
+    rc = _abi.lib().ts_reduce_mid(x.ptr(), out.ptr(), outer, red, inner, RED[op], scale,
+                                  scratch.data_ptr() if scratch is not None else None, _stream())
+    _abi.check(rc, "ts_reduce_mid")
+    return out
+
+
+def softmax_mid(x: StickTensor, dim: int, log: bool = False) -> StickTensor:
+    outer, red, inner = _mid_view(x.shape, dim)
+    out = empty(x.shape, x.dtype, x.image.device)
+    rc = _abi.lib().ts_softmax_mid(x.ptr(), out.ptr(), outer, red, inner, int(log), _stream())
+    _abi.check(rc, "ts_softmax_mid")
+    return out
+
+
+def softmax(x: StickTensor, dim: int, log: bool = False) -> StickTensor:
+    nd = len(x.shape)
+    dim = dim % nd
+    return softmax_rows(x, log) if dim == nd - 1 else softmax_mid(x, dim, log)
+
+
+# ---- fused pointwise chains -----------------------------------------------------
+
+class Chain:
+    """Builder for a ts_pointwise_chain program."""
+
+    def __init__(self):
+        self.insns: List[PwInsn] = []
+        self.inputs: List[StickTensor] = []
+
+    def tensor(self, t: StickTensor) -> Tuple[int, int, float]:
+        for i, u in enumerate(self.inputs):
+            if u is t:
+                return (TENSOR, i, 0.0)
+        self.inputs.append(t)
+        return (TENSOR, len(self.inputs) - 1, 0.0)
+
+    @staticmethod
+    def imm(v: float) -> Tuple[int, int, float]:
+        return (IMM, 0, float(v))
+
+    @staticmethod
+    def saved(k: int) -> Tuple[int, int, float]:
+        return (SAVED, k, 0.0)
+
+    def emit(self, op: str, a=(NONE, 0, 0.0), b=(NONE, 0, 0.0)) -> "Chain":
+        self.insns.append(PwInsn(OP[op], a[0], a[1], b[0], b[1], a[2], b[2]))
+        return self
+
+    def save(self, k: int) -> "Chain":
+        return self.emit("SAVE", (NONE, k, 0.0))
+
+    def store(self, k: int = 0) -> "Chain":
+        return self.emit("STORE", (NONE, k, 0.0))
+
+
+def _shape4(shape: Sequence[int], ref4: Optional[Sequence[int]] = None) -> List[int]:
+    """Collapse a logical shape to [d0, d1, d2, cols] (leading dims merged into d0)."""
+    shape = list(shape) if len(shape) else [1]
+    cols = shape[-1]
+    lead = shape[:-1]
+    while len(lead) > 3:
+        lead = [lead[0] * lead[1]] + lead[2:]
+    lead = [1] * (3 - len(lead)) + lead
+    return lead + [cols]
+
+
+def broadcast_shape4(out_shape: Sequence[int], in_shape: Sequence[int]) -> List[int]:
+    """Operand shape aligned (from the right) to out_shape, as the 4 numbers the ABI wants.
+    Only works when the out shape has at most 4 dims or leading dims can be merged safely."""
+    out_shape = list(out_shape) if len(out_shape) else [1]
+    in_shape = list(in_shape) if len(in_shape) else [1]
+    in_full = [1] * (len(out_shape) - len(in_shape)) + in_shape
+    if len(out_shape) <= 4:
+        return [1] * (4 - len(out_shape)) + in_full
+    # merge leading dims beyond 4: only legal if the operand is uniform over them
+    extra = len(out_shape) - 4
+    head_out, head_in = out_shape[:extra + 1], in_full[:extra + 1]
+    if all(a == b for a, b in zip(head_out, head_in)):
+        merged = 1
+        for v in head_in:
+            merged *= v
+    elif all(b == 1 for b in head_in):
+        merged = 1
+    else:
+        raise _abi.SpyreKernelError("broadcast pattern needs more than 4 iteration dims")
+    return [merged] + in_full[extra + 1:]
+
+
+def prepare_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
+                  reduce: Optional[str] = None, reduce_scale: float = 1.0,
+                  keepdim: bool = False, outputs: Optional[List[StickTensor]] = None):
+    """Allocates outputs and marshals every argument once.  Returns (launch, outputs,
+    reduced output); launch() enqueues the kernel on the current stream."""
+    out_shape = tuple(out_shape) if len(out_shape) else (1,)
+    if len(out_shape) <= 4:
+        shape4 = [1] * (4 - len(out_shape)) + list(out_shape)
+    else:
+        shape4 = broadcast_shape4(out_shape, out_shape)
+    dev = chain.inputs[0].image.device if chain.inputs else torch.device("cuda")
+    if outputs is None:
+        outputs = [empty(out_shape, torch.float16, dev) for _ in range(n_outputs)]
+    in_shapes: List[int] = []
+    for t in chain.inputs:
+        in_shapes += broadcast_shape4(out_shape, t.shape)
+    red_out = None
+    red_inner = 1
+    if reduce is not None:
+        lead = list(out_shape[:-1])
+        if keepdim:
+            red_out = empty(lead + [1], torch.float16, dev)
+        else:
+            red_out = empty(lead if lead else [1], torch.float16, dev)
+            red_inner = lead[-1] if lead else 1
+    insns = (PwInsn * len(chain.insns))(*chain.insns)
+    args = (insns, len(chain.insns), _abi.ptrs([t.ptr() for t in chain.inputs]),
+            _abi.i64(in_shapes), len(chain.inputs), _abi.ptrs([o.ptr() for o in outputs]),
+            len(outputs), _abi.i64(shape4), RED[reduce], reduce_scale,
+            red_out.ptr() if red_out is not None else None, int(keepdim), red_inner)
+    fn = _abi.lib().ts_pointwise_chain
+    keep = (chain, outputs, red_out)  # the launch closure keeps every buffer alive
+
+    def launch():
+        rc = fn(*args, torch.cuda.current_stream().cuda_stream)
+        if rc != 0:
+            _abi.check(rc, "ts_pointwise_chain")
+        return keep
+
+    return launch, outputs, red_out
+
+
+def run_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
+              reduce: Optional[str] = None, reduce_scale: float = 1.0,
+              keepdim: bool = False, outputs: Optional[List[StickTensor]] = None
+              ) -> Tuple[List[StickTensor], Optional[StickTensor]]:
+    """Launches the chain over `out_shape`.  Returns (full-shape outputs, reduced output)."""
+    launch, outs, red = prepare_chain(chain, out_shape, n_outputs, reduce, reduce_scale, keepdim,
+                                      outputs)
+    launch()
+    return outs, red
