@@ -90,7 +90,7 @@ class ClockSampler:
 
 # --------------------------------------------------------------------------- workloads
 
-def make_workload(name: str, dev):
+def make_workload(name: str, dev, scale_rows=None):
     """Returns dict(step_dev, step_e2e, alg_bytes, h2d, d2h, launches, desc, cpu_step, sample)."""
     from oracle import math_ref
     from torch_spyre import stick_ops as K
@@ -146,7 +146,7 @@ def make_workload(name: str, dev):
                     check=lambda: math_ref.assert_close(step_e2e().clone(), cpu_step()))
 
     if name in ("softmax", "softmax_scaled"):
-        rows, cols = (256, 4096) if name == "softmax" else (65536, 4096)
+        rows, cols = (256, 4096) if name == "softmax" else (scale_rows or 65536, 4096)
         x = math_ref.softmax_inputs(256, cols)
         if rows != 256:
             x = x.repeat(rows // 256, 1)
@@ -188,11 +188,10 @@ def make_workload(name: str, dev):
 
     if name in ("relayout", "relayout_permuted"):
         permuted = name.endswith("permuted")
-        shape = (64, 2048, 4096)
-        g = torch.Generator().manual_seed(0)
+        shape = (scale_rows or 64, 2048, 4096)
         # a [4,...] seeded block repeated along dim 0 keeps host generation quick
         blk = math_ref.relayout_inputs((4,) + shape[1:], 0, permuted=False)
-        host = blk.repeat(16, 1, 1)
+        host = blk.repeat(shape[0] // 4, 1, 1)
         if permuted:
             host = host.permute(0, 2, 1).contiguous().permute(0, 2, 1)
         hp = host.pin_memory()
@@ -340,6 +339,8 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--rows", type=int, default=None,
+                    help="profiling aid: rows of softmax_scaled / outer extent of relayout")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -360,7 +361,7 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
 
-    wl = make_workload(args.workload, dev)
+    wl = make_workload(args.workload, dev, args.rows)
     wl["check"]()  # parity of one step against the CPU oracle before timing anything
 
     def barrier():

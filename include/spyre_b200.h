@@ -204,6 +204,26 @@ int ts_reduce_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t in
 int ts_softmax_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
                    int log_softmax, void* stream);
 
+/* ---- fp16 matmul / batched matmul on the tcgen05 tensor cores ----------------
+ *
+ * c[batch, M, N] = a[batch, M, K] x B (+ bias[N]), fp32 accumulation, fp16 result;
+ * a, c, bias are stick images.  B is the stick image of
+ *   - [batch, K, N] when b_kmajor == 0 (torch.mm / torch.bmm operand order), or
+ *   - [batch, N, K] when b_kmajor != 0 (the weight of a linear layer: a x B^T);
+ * with b_batched == 0 a single [K, N] / [N, K] matrix is shared by every batch
+ * entry.  Pointers must be 128-byte aligned.  Stands in for spyre__mm_default,
+ * spyre__bmm_default and spyre__addmm_* (codegen/inputs/spyre_torch_ops.cpp:
+ * 214-452) and the compiled matmul program (torch_spyre/_inductor/lowering.py:
+ * 25-47, codegen/compute_ops.py:396-824).
+ *
+ * ts_gemm_error_state synchronises the device and returns 1 (clearing it) if a
+ * GEMM kernel gave up on one of its bounded internal waits since the last call,
+ * 0 otherwise.
+ */
+int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch, int64_t M,
+                int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream);
+int ts_gemm_error_state(void);
+
 #ifdef __cplusplus
 }
 #endif

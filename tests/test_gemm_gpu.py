@@ -1,0 +1,108 @@
+"""GPU parity: tcgen05 matmul / bmm against torch CPU eager (rtol 1e-2, atol 1e-3)."""
+import pytest
+import torch
+
+from oracle import math_ref
+from oracle.math_ref import assert_close
+from torch_spyre import _abi, stick_ops as K
+
+pytestmark = pytest.mark.gpu
+
+
+def up(t, cuda):
+    return K.to_sticks(t.to(cuda))
+
+
+def down(st):
+    return K.from_sticks(st).cpu()
+
+
+def rnd(*shape, seed=0, scale=1.0):
+    return (torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale).half()
+
+
+def no_kernel_timeout():
+    assert _abi.lib().ts_gemm_error_state() == 0, "a GEMM kernel gave up on an internal wait"
+
+
+MM_SHAPES = [(128, 64, 256), (128, 128, 256), (3, 5, 7), (67, 256, 128), (256, 128, 512),
+             (130, 70, 300), (1, 64, 64), (512, 1024, 768), (1000, 4096, 520)]
+
+
+@pytest.mark.parametrize("m,k,n", MM_SHAPES)
+def test_mm(m, k, n, cuda):
+    a, b = rnd(m, k, seed=1), rnd(k, n, seed=2, scale=0.05)
+    c = K.matmul(up(a, cuda), up(b, cuda))
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    assert_close(down(c), a @ b)
+    if n % 64:
+        img = c.image.cpu().view(-1, m, 64)
+        assert (img[-1, :, n % 64:] == 0).all()
+
+
+@pytest.mark.parametrize("m,k,n", MM_SHAPES)
+def test_linear_weight_layout(m, k, n, cuda):
+    """a @ w.T with w stored [N, K]; bias fused into the epilogue."""
+    a, w, bias = rnd(m, k, seed=1), rnd(n, k, seed=2, scale=0.05), rnd(n, seed=3)
+    c = K.matmul(up(a, cuda), up(w, cuda), bias=up(bias, cuda), b_kmajor=True)
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    assert_close(down(c), torch.nn.functional.linear(a, w, bias))
+
+
+@pytest.mark.parametrize("bsz,m,k,n", [(1, 128, 64, 256), (4, 200, 192, 320), (3, 67, 256, 128),
+                                       (2, 3, 5, 7), (5, 256, 512, 256)])
+def test_bmm(bsz, m, k, n, cuda):
+    a, b = rnd(bsz, m, k, seed=1), rnd(bsz, k, n, seed=2, scale=0.05)
+    c = K.matmul(up(a, cuda), up(b, cuda))
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    assert_close(down(c), torch.bmm(a, b))
+    # batched a, shared b; batched a, batched transposed b
+    c2 = K.matmul(up(a, cuda), up(b[0], cuda))
+    assert_close(down(c2), a @ b[0])
+    bt = b.transpose(1, 2).contiguous()
+    c3 = K.matmul(up(a, cuda), up(bt, cuda), b_kmajor=True)
+    assert_close(down(c3), torch.bmm(a, b))
+    no_kernel_timeout()
+
+
+def test_attention_building_block(cuda):
+    # tests/_inductor/test_building_blocks.py:67-89 of the reference
+    q, k, v = rnd(256, 128, seed=1), rnd(256, 128, seed=2), rnd(256, 128, seed=3)
+    scale = 128 ** -0.5
+    sq, sk, sv = up(q, cuda), up(k, cuda), up(v, cuda)
+    s = K.matmul(sq, sk, b_kmajor=True)           # q @ k^T
+    c = K.Chain()
+    c.emit("LOAD", c.tensor(s)).emit("MUL", c.imm(scale)).store(0)
+    (s,), _ = K.run_chain(c, s.shape)
+    p = K.softmax(s, -1)
+    o = K.matmul(p, sv)
+    want = torch.softmax((q @ k.t()) * scale, -1) @ v
+    assert_close(down(o), want)
+    no_kernel_timeout()
+
+
+def test_config4_slice(cuda):
+    """Two batch entries of the [32,2048,4096] x [32,4096,4096] benchmark bmm."""
+    a, b = math_ref.bmm_inputs(batch=2)
+    c = K.matmul(up(a, cuda), up(b, cuda))
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    want = torch.bmm(a[:1, :512], b[:1])          # CPU time: check a slab of rows exactly
+    assert_close(down(c)[:1, :512], want)
+    # and the rest against an fp32 GPU matmul of the same fp16 inputs
+    ref = torch.bmm(a.to(cuda).float(), b.to(cuda).float()).half().cpu()
+    assert_close(down(c), ref)
+
+
+def test_linearity_property_full_width(cuda):
+    """(a1 + a2) @ b == a1 @ b + a2 @ b up to rounding, at K = 4096."""
+    a1, a2 = rnd(256, 4096, seed=1), rnd(256, 4096, seed=2)
+    b = rnd(4096, 512, seed=3, scale=0.02)
+    sb = up(b, cuda)
+    lhs = down(K.matmul(up((a1 + a2), cuda), sb)).float()
+    rhs = down(K.matmul(up(a1, cuda), sb)).float() + down(K.matmul(up(a2, cuda), sb)).float()
+    torch.testing.assert_close(lhs, rhs, rtol=2e-2, atol=2e-2)
+    no_kernel_timeout()

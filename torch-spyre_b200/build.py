@@ -61,7 +61,7 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
         raise RuntimeError("nvcc failed")
     objs = [os.path.join(OBJ_DIR, f[:-3] + ".o") for f in sources]
     if jobs or not os.path.exists(LIB_PATH):
-        subprocess.check_call(["nvcc", "-shared", "-o", LIB_PATH, *objs, "-lcuda"])
+        subprocess.check_call(["nvcc", "-shared", "-o", LIB_PATH, *objs])
     return LIB_PATH
 
 

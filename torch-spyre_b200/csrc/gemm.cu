@@ -1,0 +1,321 @@
+// fp16 GEMM / batched GEMM on the 5th-generation tensor cores (tcgen05), operands
+// and result as stick images, fp32 accumulation in tensor memory.
+//
+// Stands in for the reference's mm / bmm / addmm eager wrappers
+// (codegen/inputs/spyre_torch_ops.cpp:214-452) and its compiled matmul program
+// (torch_spyre/_inductor/lowering.py:25-47, codegen/compute_ops.py:396-824).
+//
+// Why the stick layout suits the tensor cores.  The image of A[batch, M, K] is
+// [K/64][batch][M][64]: a 128-row x 64-k tile is 128 consecutive 128-byte rows,
+// which is exactly the K-major, 128-byte-swizzled shared-memory tile tcgen05.mma
+// consumes, so one 4-D TMA box fetches it.  B[batch, K, N] has image
+// [N/64][batch][K][64]: a 64-k x 64-n box is an "MN-major" swizzled operand block.
+// A weight stored as [N, K] (the x @ W^T of a linear layer) is K-major like A.
+// C[batch, M, N] has image [N/64][batch][M][64]: an accumulator row slice of 64
+// columns is one 128-byte stick.
+//
+// Kernel shape: persistent, one CTA per SM, tile 128 x 256 x 64, kStages-deep
+// TMA->smem ring.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 drain the
+// accumulator (TMEM -> registers -> fp16 -> global).  TMEM holds two 128x256 fp32
+// accumulators so the epilogue of tile i overlaps the main loop of tile i+1.
+// Every wait is bounded; on a timeout the CTA raises a flag, every role leaves its
+// loop, TMEM is released and the host-visible error word is set.
+#include <mutex>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kABytes = BM * BK * 2;          // 16 KiB
+constexpr int kBBytes = BN * BK * 2;          // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
+
+__device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
+
+struct GemmParams {
+  __half* c;
+  const __half* bias;   // [N] stick image or null
+  uint32_t M, N, K, batch;
+  uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
+  int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
+  int b_batched;         // 0: one B shared by every batch
+};
+
+struct Barriers {
+  uint64_t full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                const __grid_constant__ GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;               // 1024-byte aligned stage ring
+  uint8_t* gen_tiles = smem_raw + (tiles - raw);
+  Barriers* bars = reinterpret_cast<Barriers*>(gen_tiles + kStages * kStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 4);
+    }
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
+        const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
+        const uint32_t b = tile / (P.tiles_n * P.tiles_m);
+        const int bb = P.b_batched ? (int)b : 0;
+        for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[s]), ph ^ 1, abort_flag,
+                                      kWaitLimit)) { ok = false; break; }
+          const uint32_t full = ptx::smem_u32(&bars->full[s]);
+          ptx::mbar_arrive_expect_tx(full, kStageBytes);
+          const uint32_t sa = tiles + s * kStageBytes, sb = sa + kABytes;
+          ptx::tma_load_4d(sa, &map_a, full, 0, (int)(tm * BM), (int)b, (int)kb);
+          if (P.b_kmajor) {
+            ptx::tma_load_4d(sb, &map_b, full, 0, (int)(tn * BN), bb, (int)kb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              ptx::tma_load_4d(sb + j * (BK * 128), &map_b, full, 0, (int)(kb * BK), bb,
+                               (int)(tn * (BN / 64) + j));
+          }
+        }
+      }
+      // Let copies still in flight land before the CTA can exit.
+      const uint32_t issued = it < (uint32_t)kStages ? it : (uint32_t)kStages;
+      for (uint32_t k = 0; k < issued; ++k) {
+        const uint32_t j = it - 1 - k, s = j % kStages, ph = (j / kStages) & 1;
+        ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), ph, abort_flag, kWaitLimit);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = ptx::idesc_f16_f32(BM, BN, 0, P.b_kmajor ? 0 : 1);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (uint32_t tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_empty[acc]), acc_ph ^ 1, abort_flag,
+                                    kWaitLimit)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), ph, abort_flag, kWaitLimit)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = tiles + s * kStageBytes, sb = sa + kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {
+            // A, K-major: 16 k = 32 bytes along the swizzled 128-byte row.
+            const uint64_t da = ptx::smem_desc_sw128(sa + k16 * 32, 16, 1024);
+            // B, K-major: same form.  B, MN-major: 16 k rows = 2048 bytes; 64-wide n
+            // blocks are BK*128 bytes apart (leading offset), 8-row groups 1024 apart.
+            const uint64_t db = P.b_kmajor ? ptx::smem_desc_sw128(sb + k16 * 32, 16, 1024)
+                                           : ptx::smem_desc_sw128(sb + k16 * 2048, BK * 128, 1024);
+            ptx::umma_f16(d_tmem, da, db, idesc, (kb | (uint32_t)k16) != 0);
+          }
+          ptx::umma_commit(ptx::smem_u32(&bars->empty[s]));
+        }
+        if (ok) ptx::umma_commit(ptx::smem_u32(&bars->acc_full[acc]));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t local_tile = 0;
+    const uint32_t c_sticks = (P.N + 63) / 64;
+    for (uint32_t tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
+      const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
+      const uint32_t b = tile / (P.tiles_n * P.tiles_m);
+      const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
+                                  kWaitLimit)) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t row = tm * BM + q * 32 + lane;
+      const bool row_ok = row < P.M;
+      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + chunk * 32, r);
+        ptx::tmem_ld_wait();
+        const uint32_t col = tn * BN + chunk * 32;
+        const uint32_t stick = col >> 6;
+        if (row_ok && stick < c_sticks) {
+          Vec8h bv[4];
+          if (P.bias) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + v * 8);
+          }
+          __half* dst = P.c + (((int64_t)stick * P.batch + b) * P.M + row) * kStickHalfs + (col & 63);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            Vec8h o;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
+              if (P.bias) {
+                x0 += __half2float(bv[v].h[2 * e]);
+                x1 += __half2float(bv[v].h[2 * e + 1]);
+              }
+              o.h2[e] = __floats2half2_rn(x0, x1);
+            }
+            st_global_v4(dst + v * 8, o.u);
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_gemm_error, 1);
+}
+
+// ---- host side --------------------------------------------------------------------
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeFn)p;
+  });
+  return fn;
+}
+
+// Tensor map over the stick image [sticks][batch][rows][64] of a [batch, rows, cols] fp16
+// tensor; the box is 64 lanes x box_rows rows of one stick column of one batch entry.
+bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t batch, uint64_t sticks,
+              uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[4] = {64, rows, batch, sticks};
+  const cuuint64_t strides[3] = {128, rows * 128, batch * rows * 128};
+  const cuuint32_t box[4] = {64, box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int g_sm_count = 0;
+
+}  // namespace
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch,
+                           int64_t M, int64_t N, int64_t K, int b_kmajor, int b_batched,
+                           void* stream) {
+  if (batch < 0 || M < 0 || N < 0 || K < 0) return TS_ERR_INVALID;
+  if (batch == 0 || M == 0 || N == 0) return TS_OK;
+  if (!a || !b || !c) return TS_ERR_INVALID;
+  if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)bias) % 128) return TS_ERR_ALIGNMENT;
+  if (K == 0) return TS_ERR_UNSUPPORTED;
+  if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31) || batch >= (1ll << 31))
+    return TS_ERR_TOO_LARGE;
+  GemmParams P{};
+  P.c = (__half*)c;
+  P.bias = (const __half*)bias;
+  P.M = (uint32_t)M; P.N = (uint32_t)N; P.K = (uint32_t)K; P.batch = (uint32_t)batch;
+  P.tiles_m = (uint32_t)ceil_div(M, BM);
+  P.tiles_n = (uint32_t)ceil_div(N, BN);
+  const int64_t tiles = (int64_t)P.tiles_m * P.tiles_n * batch;
+  if (tiles >= (1ll << 31)) return TS_ERR_TOO_LARGE;
+  P.num_tiles = (uint32_t)tiles;
+  P.k_blocks = (uint32_t)ceil_div(K, BK);
+  P.b_kmajor = b_kmajor ? 1 : 0;
+  P.b_batched = b_batched ? 1 : 0;
+
+  CUtensorMap map_a, map_b;
+  const uint64_t bb = b_batched ? (uint64_t)batch : 1;
+  if (!make_map(&map_a, a, (uint64_t)M, (uint64_t)batch, P.k_blocks, BM)) return TS_ERR_CUDA;
+  const bool okb = b_kmajor ? make_map(&map_b, b, (uint64_t)N, bb, P.k_blocks, BN)
+                            : make_map(&map_b, b, (uint64_t)K, bb, (uint64_t)ceil_div(N, 64), BK);
+  if (!okb) return TS_ERR_CUDA;
+
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemBytes);
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  });
+  if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }
+  const uint32_t grid = (uint32_t)std::min<int64_t>(tiles, g_sm_count > 0 ? g_sm_count : 148);
+  gemm_f16_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, P);
+  TSB_CHECK_LAUNCH();
+  return TS_OK;
+}
+
+// Synchronises the device and reports (and clears) the sticky error word the GEMM
+// kernel sets when one of its bounded waits gave up.  Returns 0, 1 or an error code.
+extern "C" int ts_gemm_error_state(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gemm_error, sizeof(int)) != cudaSuccess) return TS_ERR_CUDA;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
+  }
+  return v;
+}

@@ -338,3 +338,40 @@ def run_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
                                       outputs)
     launch()
     return outs, red
+
+
+# ---- matmul ---------------------------------------------------------------------
+
+def matmul(a: StickTensor, b: StickTensor, bias: Optional[StickTensor] = None,
+           b_kmajor: bool = False, out: Optional[StickTensor] = None) -> StickTensor:
+    """a: [..., M, K].  b: [K, N] or [batch..., K, N] (b_kmajor=False), or [N, K] /
+    [batch..., N, K] (b_kmajor=True, i.e. a @ b^T).  fp32 accumulation, fp16 result."""
+    if len(a.shape) < 2 or len(b.shape) < 2:
+        raise _abi.SpyreKernelError("matmul operands need at least 2 dims")
+    M, K = a.shape[-2], a.shape[-1]
+    if b_kmajor:
+        N, Kb = b.shape[-2], b.shape[-1]
+    else:
+        Kb, N = b.shape[-2], b.shape[-1]
+    if K != Kb:
+        raise _abi.SpyreKernelError(f"matmul shape mismatch: {a.shape} x {b.shape}")
+    batch = 1
+    for s in a.shape[:-2]:
+        batch *= s
+    b_batched = len(b.shape) > 2
+    if b_batched:
+        nb = 1
+        for s in b.shape[:-2]:
+            nb *= s
+        if nb != batch:
+            raise _abi.SpyreKernelError("batched matmul needs equal batch extents")
+    else:
+        # a shared B sees [batch*M, K] as one matrix
+        M, batch = M * batch, 1
+    if out is None:
+        out = empty(tuple(a.shape[:-1]) + (N,), torch.float16, a.image.device)
+    rc = _abi.lib().ts_gemm_f16(a.ptr(), b.ptr(), bias.ptr() if bias is not None else None,
+                                out.ptr(), batch, M, N, K, int(b_kmajor), int(b_batched),
+                                _stream())
+    _abi.check(rc, "ts_gemm_f16")
+    return out
