@@ -240,6 +240,49 @@ def make_workload(name: str, dev, scale_rows=None):
                     l2="1 GiB tensors, far larger than L2", cpu_step=cpu_step, cpu_scale=8.0,
                     sample="C oracle on a [8,2048,4096] slice (1/8 of the tensor), all host threads",
                     cpu_kind="port", check=check)
+    if name == "bmm":
+        batch, m, k, n = scale_rows or 32, 2048, 4096, 4096
+        a1, b1 = math_ref.bmm_inputs(batch=1)
+        sa1, sb1 = K.copy_host_to_sticks(a1.pin_memory()), K.copy_host_to_sticks(b1.pin_memory())
+        # the seeded [1, ...] block repeated along the batch keeps host generation quick
+        sa = K.StickTensor(sa1.image.view(k // 64, 1, m * 64).repeat(1, batch, 1).reshape(-1), (batch, m, k))
+        sb = K.StickTensor(sb1.image.view(n // 64, 1, k * 64).repeat(1, batch, 1).reshape(-1), (batch, k, n))
+        sc = K.empty((batch, m, n))
+
+        def step_dev():
+            K.matmul(sa, sb, out=sc)
+
+        ah = a1.repeat(batch, 1, 1).pin_memory()
+        bh = b1.repeat(batch, 1, 1).pin_memory()
+        ch = torch.empty(batch, m, n, dtype=torch.float16).pin_memory()
+        staging = torch.empty(bh.numel() * 2, dtype=torch.uint8, device=dev)
+        sa_e, sb_e = K.empty((batch, m, k)), K.empty((batch, k, n))
+
+        def step_e2e():
+            K.copy_host_to_sticks(ah, sa_e, staging)
+            K.copy_host_to_sticks(bh, sb_e, staging)
+            K.matmul(sa_e, sb_e, out=sc)
+            K.copy_sticks_to_host(sc, ch, staging)
+            torch.cuda.current_stream().synchronize()
+            return ch
+
+        def cpu_step():
+            return torch.bmm(a1, b1)
+
+        def check():
+            got = step_e2e()[batch - 1, :256].clone()
+            math_ref.assert_close(got, torch.bmm(a1[:, :256], b1)[0])
+            if K._abi.lib().ts_gemm_error_state() != 0:
+                raise AssertionError("GEMM kernel gave up on an internal wait")
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0,
+                    flops=2.0 * batch * m * k * n, cpu_scale=float(batch),
+                    h2d=(ah.numel() + bh.numel()) * 2, d2h=ch.numel() * 2, launches=1,
+                    desc=f"bmm fp16 [{batch},{m},{k}] x [{batch},{k},{n}], fp32 accumulate "
+                         "(BASELINE configs[3])",
+                    l2="operands 1.5 GiB, far larger than L2", cpu_step=cpu_step,
+                    sample="one batch entry [1,2048,4096]x[1,4096,4096] per CPU step (1/32 of the job)",
+                    check=check)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -287,16 +330,19 @@ def run_reference(args, rank, world):
         wl["cpu_step"]()
     dt = (time.perf_counter() - t0) / args.steps
     scale = wl.get("cpu_scale", 1.0)
-    gbs = wl["alg_bytes"] / scale / dt / 1e9
+    is_flops = "flops" in wl
+    gbs = (wl["flops"] / 1e3 if is_flops else wl["alg_bytes"]) / scale / dt / 1e9
     cores = torch.get_num_threads()
-    line = {"impl": "reference", "metric": "achieved GB/s (algorithmic bytes / time)", "value": gbs,
-            "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+    unit = "TFLOP/s" if is_flops else "GB/s"
+    line = {"impl": "reference",
+            "metric": "fp16 GEMM TFLOP/s" if is_flops else "achieved GB/s (algorithmic bytes / time)",
+            "value": gbs, "unit": unit, "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt * 1e3 * scale, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": wl["desc"]},
-            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": cores, "kind": "reference",
+            "cpu_baseline": {"value": gbs, "unit": unit, "cores": cores, "kind": "reference",
                              "sample": wl["sample"] + "; torch CPU eager / C oracle on host cores"},
-            "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "e2e": {"value": gbs, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
 
@@ -327,6 +373,12 @@ def make_workload_cpu(name):
         return dict(cpu_step=cpu_step, alg_bytes=4 * 64 * 2048 * 4096 * 2, cpu_scale=8.0,
                     desc="stick relayout fp16 [64,2048,4096], to sticks and back (BASELINE configs[2])",
                     sample="C oracle on a [8,2048,4096] slice (1/8 of the tensor)")
+    if name == "bmm":
+        a1, b1 = math_ref.bmm_inputs(batch=1)
+        return dict(cpu_step=lambda: torch.bmm(a1, b1), flops=2.0 * 32 * 2048 * 4096 * 4096,
+                    cpu_scale=32.0, alg_bytes=0,
+                    desc="bmm fp16 [32,2048,4096] x [32,4096,4096] (BASELINE configs[3])",
+                    sample="one batch entry per CPU step (1/32 of the job)")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -396,28 +448,34 @@ def main():
         dt, e2e_dt = float(t[0]), (float(t[1]) if e2e_dt is not None else None)
 
     if rank == 0:
-        hbm, _, which = measured_peaks()
-        per_gpu = wl["alg_bytes"] * args.steps / dt / 1e9
+        hbm, tflops_peak, which = measured_peaks()
+        is_flops = "flops" in wl
+        work = wl["flops"] / 1e3 if is_flops else wl["alg_bytes"]   # per step, in units of 1e-9 * unit
+        per_gpu = work * args.steps / dt / 1e9
+        unit = "TFLOP/s" if is_flops else "GB/s"
         line = {
-            "metric": "achieved GB/s (algorithmic bytes / time)", "value": per_gpu * world,
-            "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": ("fp16 GEMM TFLOP/s" if is_flops else "achieved GB/s (algorithmic bytes / time)"),
+            "value": per_gpu * world,
+            "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": wl["desc"], "l2": wl["l2"],
                        "sharding": f"{world} x the per-GPU workload, rows sharded, no collective"},
-            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": hbm, "unit": "GB/s",
-                         "frac": per_gpu / hbm, "traffic": None, "peak_source": which},
+            "roofline": {"bound": "tensor" if is_flops else "hbm", "achieved": per_gpu,
+                         "peak": tflops_peak if is_flops else hbm, "unit": unit,
+                         "frac": per_gpu / (tflops_peak if is_flops else hbm), "traffic": None,
+                         "peak_source": which + (" (bf16 cuBLAS burst)" if is_flops else " (copy)")},
             "gpu_launches": wl["launches"] * args.steps,
             "clocks": clocks,
         }
         if e2e_dt is not None:
-            line["e2e"] = {"value": wl["alg_bytes"] / e2e_dt / 1e9 * world, "unit": "GB/s",
+            line["e2e"] = {"value": work / e2e_dt / 1e9 * world, "unit": unit,
                            "h2d_bytes_per_step": wl["h2d"], "d2h_bytes_per_step": wl["d2h"],
                            "ms_per_step": e2e_dt * 1e3}
         if not args.no_cpu_baseline and world == 1:
             med, n = time_cpu(wl["cpu_step"])
             scale = wl.get("cpu_scale", 1.0)
-            line["cpu_baseline"] = {"value": wl["alg_bytes"] / scale / med / 1e9, "unit": "GB/s",
+            line["cpu_baseline"] = {"value": work / scale / med / 1e9, "unit": unit,
                                     "cores": torch.get_num_threads(),
                                     "kind": wl.get("cpu_kind", "reference"),
                                     "sample": f"{wl['sample']}; median of {n} runs; "

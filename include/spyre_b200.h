@@ -157,6 +157,10 @@ int ts_pointwise_chain(const ts_pw_insn* insns, int n_insns,
                        const int64_t* shape /* d0, d1, d2, cols */,
                        int reduce_op, float reduce_scale, void* reduce_out,
                        int reduce_keepdim, int64_t reduce_inner, void* stream);
+/* Number of chains the library holds as pre-compiled straight-line kernels (a
+ * chain whose opcodes and operand selectors match one of them runs on it; any
+ * other chain runs on the interpreter kernel).  No counterpart in the reference. */
+int ts_pointwise_static_count(void);
 
 /* ---- row-wise normalisations along the stick dim ---------------------------
  *

@@ -1,0 +1,473 @@
+// Fused fp16 pointwise chains over stick images: program encoding, the per-item
+// executor, and the two kernel templates (plain pointwise, and pointwise followed
+// by a reduction along the stick dim).
+//
+// A program is a list of 32-bit code words (opcode and operand selectors) plus a
+// pair of immediates per instruction.  The executor is one function,
+// exec_insn(code, ...); the kernels are templated on where the code words come
+// from:
+//   * Dyn      - read from the kernel parameters at run time (an interpreter whose
+//                registers are statically allocated: accumulator, operand buffers
+//                and four saved slots, so nothing is indexed dynamically and every
+//                branch is uniform across the grid);
+//   * Fixed<…> - compile-time constants: the switch folds away and the compiler
+//                schedules the whole chain as straight-line code.  Frequently fused
+//                patterns are pre-instantiated this way; anything else runs on Dyn.
+// Values travel as packed half2 and every op result is rounded to fp16, which is
+// what eager fp16 does op by op.
+#pragma once
+
+#include "common.cuh"
+
+namespace tsb {
+namespace pw {
+
+constexpr int kThreads = 256;
+
+constexpr uint32_t enc(int op, int a_kind = 0, int a_idx = 0, int b_kind = 0, int b_idx = 0) {
+  return (uint32_t)op | ((uint32_t)a_kind << 8) | ((uint32_t)a_idx << 12) | ((uint32_t)b_kind << 16) |
+         ((uint32_t)b_idx << 20);
+}
+__host__ __device__ constexpr int code_op(uint32_t c) { return (int)(c & 0xff); }
+__host__ __device__ constexpr int code_ak(uint32_t c) { return (int)((c >> 8) & 0xf); }
+__host__ __device__ constexpr int code_ai(uint32_t c) { return (int)((c >> 12) & 0xf); }
+__host__ __device__ constexpr int code_bk(uint32_t c) { return (int)((c >> 16) & 0xf); }
+__host__ __device__ constexpr int code_bi(uint32_t c) { return (int)((c >> 20) & 0xf); }
+
+struct TensorDesc {
+  const __half* ptr;
+  int64_t stick_stride;  // elements between consecutive stick columns of this tensor
+  int32_t m0, m1, m2;    // tensor row = i0*m0 + i1*m1 + i2*m2
+  int32_t col_bcast;     // single column: the value sits in lane 0 of its stick
+  int32_t flat;          // same shape as the iteration space
+};
+
+struct Params {
+  int n_insns, n_in, n_out;
+  uint32_t code[TS_PW_MAX_INSNS];
+  float imm_a[TS_PW_MAX_INSNS], imm_b[TS_PW_MAX_INSNS];
+  TensorDesc in[TS_PW_MAX_INPUTS];
+  __half* out[TS_PW_MAX_OUTPUTS];
+  uint32_t rows, nsticks, cols, total_sticks;
+  FastDiv div_rows, div_d2, div_d1;
+  int need_index;  // some input is not flat
+  int ragged;      // cols is not a stick multiple
+  int red_keepdim, ws_log;
+  float red_scale;
+  __half* red_out;
+  uint32_t red_inner, red_outer;
+  FastDiv div_red_inner;
+};
+
+struct Dyn {
+  static constexpr bool kStatic = false;
+};
+template <uint32_t... C>
+struct Fixed {
+  static constexpr bool kStatic = true;
+  static constexpr int n = sizeof...(C);
+  template <int I>
+  __host__ __device__ static constexpr uint32_t at() {
+    constexpr uint32_t a[] = {C...};
+    return a[I];
+  }
+};
+
+struct Item {
+  uint32_t s, r, lv, i0, i1, i2;
+  int64_t flat_off;  // element offset in a full-shape stick image
+  bool live;
+};
+
+using V = __half2[4];
+
+template <int U>
+struct Regs {
+  V acc[U], opa[U], opb[U], s0[U], s1[U], s2[U], s3[U];
+};
+
+__device__ __forceinline__ void set_all(V& v, __half2 x) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = x;
+}
+template <int U>
+__device__ __forceinline__ void copy_v(V (&dst)[U], const V (&src)[U]) {
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[u][j] = src[u][j];
+}
+
+__device__ __forceinline__ void fetch_tensor(const Params& P, int t, const Item& it, V& v) {
+  const TensorDesc& d = P.in[t];
+  if (!it.live) {
+    set_all(v, __float2half2_rn(0.f));
+    return;
+  }
+  Vec8h x;
+  if (d.flat) {
+    x.u = ld_stream_v4(d.ptr + it.flat_off);
+  } else {
+    const uint32_t row = it.i0 * (uint32_t)d.m0 + it.i1 * (uint32_t)d.m1 + it.i2 * (uint32_t)d.m2;
+    if (!d.col_bcast) {
+      x.u = ld_global_v4(d.ptr + (int64_t)it.s * d.stick_stride + (int64_t)row * kStickHalfs +
+                         it.lv * 8);
+    } else {
+      set_all(v, __half2half2(__ldg(d.ptr + (int64_t)row * kStickHalfs)));
+      return;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) v[j] = x.h2[j];
+}
+
+template <int U>
+__device__ __forceinline__ void fetch(const Params& P, Regs<U>& R, int kind, int idx, float imm,
+                                      const Item (&it)[U], V (&v)[U]) {
+  if (kind == TS_PW_TENSOR) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) fetch_tensor(P, idx, it[u], v[u]);
+  } else if (kind == TS_PW_IMM) {
+    const __half2 x = __float2half2_rn(imm);
+#pragma unroll
+    for (int u = 0; u < U; ++u) set_all(v[u], x);
+  } else if (kind == TS_PW_SAVED) {
+    switch (idx) {
+      case 0: copy_v<U>(v, R.s0); break;
+      case 1: copy_v<U>(v, R.s1); break;
+      case 2: copy_v<U>(v, R.s2); break;
+      default: copy_v<U>(v, R.s3); break;
+    }
+  }
+}
+
+template <int U, class F>
+__device__ __forceinline__ void map_f32(V (&acc)[U], F f) {
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = __half22float2(acc[u][j]);
+      x.x = f(x.x);
+      x.y = f(x.y);
+      acc[u][j] = __floats2half2_rn(x.x, x.y);
+    }
+}
+template <int U, class F>
+__device__ __forceinline__ void zip_f32(V (&acc)[U], const V (&b)[U], F f) {
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float2 x = __half22float2(acc[u][j]);
+      const float2 y = __half22float2(b[u][j]);
+      x.x = f(x.x, y.x);
+      x.y = f(x.y, y.y);
+      acc[u][j] = __floats2half2_rn(x.x, x.y);
+    }
+}
+template <int U, class F>
+__device__ __forceinline__ void zip_h2(V (&acc)[U], const V (&b)[U], F f) {
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[u][j] = f(acc[u][j], b[u][j]);
+}
+template <int U, class F>
+__device__ __forceinline__ void map_h2(V (&acc)[U], F f) {
+#pragma unroll
+  for (int u = 0; u < U; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[u][j] = f(acc[u][j]);
+}
+
+// e^x through the special-function unit: one multiply and one ex2.approx.ftz.
+__device__ __forceinline__ float exp_f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.f, 1.f + exp_f(-x)); }
+// 1 - 2 / (e^{2x} + 1): exact limits at +-inf, relative error of a few fp32 ulp.
+__device__ __forceinline__ float tanh_f(float x) {
+  return 1.f - __fdividef(2.f, exp_f(2.f * x) + 1.f);
+}
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(exp_f(x)); }
+
+template <int U>
+__device__ __forceinline__ void store_full(const Params& P, __half* out, const Item& it, const V& v) {
+  if (!it.live) return;
+  Vec8h t;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) t.h2[j] = v[j];
+  if (P.ragged) {
+    const uint32_t col = it.s * kStickHalfs + it.lv * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (col + e >= P.cols) t.h[e] = __float2half(0.f);
+  }
+  st_global_v4(out + it.flat_off, t.u);
+}
+
+// One instruction on U items.  With a compile-time `code` everything but the
+// selected case disappears.
+template <int U>
+__device__ __forceinline__ void exec_insn(const Params& P, Regs<U>& R, const Item (&it)[U],
+                                          uint32_t code, float imm_a, float imm_b) {
+  const int op = code_op(code);
+  const __half2 zero2 = __float2half2_rn(0.f);
+  V(&acc)[U] = R.acc;
+  V(&opa)[U] = R.opa;
+  if (op != TS_PW_SAVE && op != TS_PW_STORE)
+    fetch<U>(P, R, code_ak(code), code_ai(code), imm_a, it, R.opa);
+  if (op == TS_PW_WHERE) fetch<U>(P, R, code_bk(code), code_bi(code), imm_b, it, R.opb);
+  switch (op) {
+    case TS_PW_LOAD: copy_v<U>(acc, opa); break;
+    case TS_PW_SAVE:
+      switch (code_ai(code)) {
+        case 0: copy_v<U>(R.s0, acc); break;
+        case 1: copy_v<U>(R.s1, acc); break;
+        case 2: copy_v<U>(R.s2, acc); break;
+        default: copy_v<U>(R.s3, acc); break;
+      }
+      break;
+    case TS_PW_STORE:
+#pragma unroll
+      for (int u = 0; u < U; ++u) store_full<U>(P, P.out[code_ai(code)], it[u], acc[u]);
+      break;
+    case TS_PW_ADD: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hadd2(x, y); }); break;
+    case TS_PW_SUB: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hsub2(x, y); }); break;
+    case TS_PW_RSUB: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hsub2(y, x); }); break;
+    case TS_PW_MUL: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hmul2(x, y); }); break;
+    case TS_PW_DIV: zip_f32<U>(acc, opa, [](float x, float y) { return x / y; }); break;
+    case TS_PW_RDIV: zip_f32<U>(acc, opa, [](float x, float y) { return y / x; }); break;
+    case TS_PW_MAX: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hmax2_nan(x, y); }); break;
+    case TS_PW_MIN: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hmin2_nan(x, y); }); break;
+    case TS_PW_POW: zip_f32<U>(acc, opa, [](float x, float y) { return powf(x, y); }); break;
+    case TS_PW_EQ: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __heq2(x, y); }); break;
+    case TS_PW_NE: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hneu2(x, y); }); break;
+    case TS_PW_LT: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hlt2(x, y); }); break;
+    case TS_PW_LE: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hle2(x, y); }); break;
+    case TS_PW_GT: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hgt2(x, y); }); break;
+    case TS_PW_GE: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hge2(x, y); }); break;
+    case TS_PW_WHERE:
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t m = __hneu2_mask(acc[u][j], zero2);
+          const uint32_t a = *reinterpret_cast<const uint32_t*>(&opa[u][j]);
+          const uint32_t b = *reinterpret_cast<const uint32_t*>(&R.opb[u][j]);
+          const uint32_t r = (a & m) | (b & ~m);
+          acc[u][j] = *reinterpret_cast<const __half2*>(&r);
+        }
+      break;
+    case TS_PW_NEG: map_h2<U>(acc, [](__half2 x) { return __hneg2(x); }); break;
+    case TS_PW_ABS: map_h2<U>(acc, [](__half2 x) { return __habs2(x); }); break;
+    case TS_PW_EXP: map_f32<U>(acc, [](float x) { return exp_f(x); }); break;
+    case TS_PW_LOG: map_f32<U>(acc, [](float x) { return __logf(x); }); break;
+    case TS_PW_SQRT: map_f32<U>(acc, [](float x) { return sqrtf(x); }); break;
+    case TS_PW_RSQRT: map_f32<U>(acc, [](float x) { return rsqrtf(x); }); break;
+    case TS_PW_RECIP: map_f32<U>(acc, [](float x) { return 1.f / x; }); break;
+    case TS_PW_SIGMOID: map_f32<U>(acc, [](float x) { return sigmoid_f(x); }); break;
+    case TS_PW_TANH: map_f32<U>(acc, [](float x) { return tanh_f(x); }); break;
+    case TS_PW_RELU: map_h2<U>(acc, [zero2](__half2 x) { return __hmax2_nan(x, zero2); }); break;
+    case TS_PW_SILU: map_f32<U>(acc, [](float x) { return x * sigmoid_f(x); }); break;
+    case TS_PW_GELU:
+      map_f32<U>(acc, [](float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); });
+      break;
+    case TS_PW_GELU_TANH:
+      map_f32<U>(acc, [](float x) {
+        const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+        return 0.5f * x * (1.f + tanh_f(inner));
+      });
+      break;
+    case TS_PW_SQUARE: map_h2<U>(acc, [](__half2 x) { return __hmul2(x, x); }); break;
+    case TS_PW_LOGICAL_NOT: map_h2<U>(acc, [zero2](__half2 x) { return __heq2(x, zero2); }); break;
+    case TS_PW_SIN: map_f32<U>(acc, [](float x) { return sinf(x); }); break;
+    case TS_PW_COS: map_f32<U>(acc, [](float x) { return cosf(x); }); break;
+    case TS_PW_ERF: map_f32<U>(acc, [](float x) { return erff(x); }); break;
+    case TS_PW_FLOOR: map_h2<U>(acc, [](__half2 x) { return h2floor(x); }); break;
+    case TS_PW_CEIL: map_h2<U>(acc, [](__half2 x) { return h2ceil(x); }); break;
+    case TS_PW_SIGN: map_f32<U>(acc, [](float x) { return x > 0.f ? 1.f : (x < 0.f ? -1.f : x); }); break;
+    case TS_PW_LOG1P: map_f32<U>(acc, [](float x) { return log1pf(x); }); break;
+    case TS_PW_EXPM1: map_f32<U>(acc, [](float x) { return expm1f(x); }); break;
+    case TS_PW_SOFTPLUS: map_f32<U>(acc, [](float x) { return softplus_f(x); }); break;
+    case TS_PW_MISH: map_f32<U>(acc, [](float x) { return x * tanh_f(softplus_f(x)); }); break;
+    default: break;
+  }
+}
+
+template <class Prog, int U, int I>
+__device__ __forceinline__ void run_fixed(const Params& P, Regs<U>& R, const Item (&it)[U]) {
+  if constexpr (I < Prog::n) {
+    exec_insn<U>(P, R, it, Prog::template at<I>(), P.imm_a[I], P.imm_b[I]);
+    run_fixed<Prog, U, I + 1>(P, R, it);
+  }
+}
+
+// Runs the whole program on U items; the result is left in R.acc.
+template <class Prog, int U>
+__device__ __forceinline__ void run_program(const Params& P, Regs<U>& R, const Item (&it)[U]) {
+  const __half2 zero2 = __float2half2_rn(0.f);
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    set_all(R.acc[u], zero2);
+    set_all(R.opa[u], zero2);
+    set_all(R.opb[u], zero2);
+    set_all(R.s0[u], zero2);
+    set_all(R.s1[u], zero2);
+    set_all(R.s2[u], zero2);
+    set_all(R.s3[u], zero2);
+  }
+  if constexpr (Prog::kStatic) {
+    run_fixed<Prog, U, 0>(P, R, it);
+  } else {
+    for (int pc = 0; pc < P.n_insns; ++pc) exec_insn<U>(P, R, it, P.code[pc], P.imm_a[pc], P.imm_b[pc]);
+  }
+}
+
+__device__ __forceinline__ void split_row(const Params& P, Item& it) {
+  uint32_t q, r2;
+  P.div_d2.divmod(it.r, q, r2);
+  it.i2 = r2;
+  P.div_d1.divmod(q, it.i0, it.i1);
+}
+
+// ---- no reduction: items are the 16-byte vectors of the output image ----------
+template <class Prog, int U>
+__global__ void __launch_bounds__(kThreads) flat_kernel(const __grid_constant__ Params P) {
+  Item it[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const uint32_t stick = blockIdx.x * (32 * U) + u * 32 + (threadIdx.x >> 3);
+    it[u].lv = threadIdx.x & 7;
+    it[u].live = stick < P.total_sticks;
+    it[u].flat_off = (int64_t)stick * kStickHalfs + it[u].lv * 8;
+    it[u].s = it[u].r = it[u].i0 = it[u].i1 = it[u].i2 = 0;
+    if (P.need_index || P.ragged) {
+      P.div_rows.divmod(stick, it[u].s, it[u].r);
+      if (P.need_index) split_row(P, it[u]);
+    }
+  }
+  Regs<U> R;
+  run_program<Prog, U>(P, R, it);
+}
+
+template <int RED>
+__device__ __forceinline__ float red_identity() {
+  return RED == TS_RED_SUM ? 0.f : (RED == TS_RED_MAX ? -INFINITY : INFINITY);
+}
+template <int RED>
+__device__ __forceinline__ float red_combine(float a, float b) {
+  if (RED == TS_RED_SUM) return a + b;
+  const float r = RED == TS_RED_MAX ? fmaxf(a, b) : fminf(a, b);
+  return (b != b) ? b : ((a != a) ? a : r);  // NaN propagates, as torch.max / torch.min do
+}
+
+// ---- reduction along the stick dim ----------------------------------------------
+// A warp covers 4 adjacent rows x 8 vector lanes (512 contiguous bytes per stick
+// column).  2^ws_log warps share a row group and split its stick columns.
+template <class Prog, int RED, int U>
+__global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant__ Params P) {
+  __shared__ float part[8][4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ws = 1 << P.ws_log;
+  const int ws_idx = warp & (ws - 1);
+  const uint32_t group = blockIdx.x * (8 >> P.ws_log) + (warp >> P.ws_log);
+  const uint32_t row = group * 4 + (lane >> 3);
+  const bool row_live = row < P.rows;
+  Item it[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    it[u].r = row;
+    it[u].lv = lane & 7;
+    it[u].i0 = it[u].i1 = it[u].i2 = 0;
+    if (P.need_index && row_live) split_row(P, it[u]);
+  }
+  float partial = red_identity<RED>();
+  Regs<U> R;
+  for (uint32_t s0 = ws_idx; s0 < P.nsticks; s0 += ws * U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const uint32_t s = s0 + u * ws;
+      it[u].s = s;
+      it[u].live = row_live && s < P.nsticks;
+      it[u].flat_off = ((int64_t)s * P.rows + row) * kStickHalfs + it[u].lv * 8;
+    }
+    run_program<Prog, U>(P, R, it);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!it[u].live) continue;
+      const uint32_t col = it[u].s * kStickHalfs + it[u].lv * 8;
+      if (!P.ragged || col + 8 <= P.cols) {
+        float t = red_identity<RED>();
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = __half22float2(R.acc[u][j]);
+          t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
+        }
+        partial = red_combine<RED>(partial, t);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 x = __half22float2(R.acc[u][j]);
+          if (col + 2 * j < P.cols) partial = red_combine<RED>(partial, x.x);
+          if (col + 2 * j + 1 < P.cols) partial = red_combine<RED>(partial, x.y);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 1; o < 8; o <<= 1)
+    partial = red_combine<RED>(partial, __shfl_xor_sync(0xffffffffu, partial, o));
+  if ((lane & 7) == 0) part[warp][lane >> 3] = partial;
+  __syncthreads();
+  if (ws_idx != 0 || !row_live) return;
+  float total = part[warp][lane >> 3];
+  for (int k = 1; k < ws; ++k) total = red_combine<RED>(total, part[warp + k][lane >> 3]);
+  const __half result = __float2half_rn(total * P.red_scale);
+  const uint32_t lv = lane & 7;
+  if (P.red_keepdim) {
+    Vec8h t;
+    t.u = make_uint4(0, 0, 0, 0);
+    if (lv == 0) t.h[0] = result;
+    st_global_v4(P.red_out + (int64_t)row * kStickHalfs + lv * 8, t.u);
+  } else {
+    uint32_t o, l;
+    P.div_red_inner.divmod(row, o, l);
+    __half* base = P.red_out + ((int64_t)(l >> 6) * P.red_outer + o) * kStickHalfs;
+    if (lv == 0) base[l & 63] = result;
+    if (l == P.red_inner - 1)
+      for (uint32_t e = (l & 63) + 1 + lv; e < 64; e += 8) base[e] = __float2half(0.f);
+  }
+}
+
+// ---- registry of pre-instantiated programs ----------------------------------------
+using LaunchFn = void (*)(const Params&, uint32_t blocks, cudaStream_t);
+
+struct StaticEntry {
+  const uint32_t* codes;
+  int n;
+  int red;  // TS_RED_*
+  int items;  // work items per thread per step (U)
+  LaunchFn fn;
+};
+void register_static(const StaticEntry& e);  // pointwise.cu
+
+template <class Prog, int RED, int U>
+void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
+  if constexpr (RED == TS_RED_NONE) flat_kernel<Prog, U><<<blocks, kThreads, 0, st>>>(P);
+  else rowred_kernel<Prog, RED, U><<<blocks, kThreads, 0, st>>>(P);
+}
+
+template <int RED, int U, uint32_t... C>
+struct Registrar {
+  Registrar() {
+    static const uint32_t codes[] = {C...};
+    register_static(StaticEntry{codes, (int)sizeof...(C), RED, U, &launch_instance<Fixed<C...>, RED, U>});
+  }
+};
+
+}  // namespace pw
+}  // namespace tsb

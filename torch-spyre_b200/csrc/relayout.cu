@@ -19,27 +19,29 @@ namespace tsb {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kUnitsPerThread = 4;
-constexpr int kTileUnits = kThreads * kUnitsPerThread;  // 1024
+constexpr int kUnitsPerThread = 8;
 constexpr int kMaxChecks = 2;
 
+// Plan dims are stored innermost first: copy_tiles uses dim 0 = the unit-stride run,
+// dim 1 = the dim next-most contiguous in the source, dim 2 = next-most contiguous
+// in the destination (extent-1 dummies when absent); transpose_tiles uses dim 0 =
+// unit stride in the source, dim 1 = unit stride in the destination.
 struct CopyPlan {
-  int nd;                        // iteration dims, outermost first
-  uint32_t size[kMaxDims];       // extent per dim (last dim of copy_tiles: in units)
+  int nd;
+  uint32_t size[kMaxDims];       // extent per dim (copy_tiles dim 0: in units)
   int64_t sbytes[kMaxDims];      // source stride per dim, bytes
   int64_t dbytes[kMaxDims];      // destination stride per dim, bytes
-  uint32_t tile[kMaxDims];       // tile extent per dim (1 = not tiled)
+  uint32_t tile[kMaxDims];       // CTA tile extent per dim (1 = not tiled)
   FastDiv ntiles[kMaxDims];      // tiles per dim
   // Padding: index is inside the host tensor iff, for every check c,
   // sum_d idx[d] * vmul[c][d] < vlimit[c].
   int nchecks;
   int64_t vmul[kMaxChecks][kMaxDims];
   int64_t vlimit[kMaxChecks];
-  // copy_tiles: tile = T0 (dim nd-1) x T1 (dim tx) x T2 (dim ty), powers of two.
-  int tx, ty, log_t0, log_t1;
-  uint32_t t2;
-  // transpose_tiles: dim `ta` is unit-stride in the source, `tb` in the destination.
-  int ta, tb;
+  // copy_tiles: 256 threads cover T0 x T1 x T2 indices of dims 0,1,2; each thread then
+  // walks kUnitsPerThread steps of `kstep` indices along dim `kd`.
+  int log_t0, log_t1, kd;
+  uint32_t kstep;
 };
 
 template <int UNIT>
@@ -54,91 +56,108 @@ template <class T> __device__ __forceinline__ T zero_of() { return T(0); }
 template <> __device__ __forceinline__ uint4 zero_of<uint4>() { return make_uint4(0, 0, 0, 0); }
 template <> __device__ __forceinline__ uint2 zero_of<uint2>() { return make_uint2(0, 0); }
 
-__device__ __forceinline__ void decode_tile(const CopyPlan& p, uint32_t tile_id, uint32_t* origin) {
+template <class T> __device__ __forceinline__ T load_unit(const char* p) {
+  return *reinterpret_cast<const T*>(p);
+}
+template <> __device__ __forceinline__ uint4 load_unit<uint4>(const char* p) { return ld_stream_v4(p); }
+
+struct TileBase {
+  uint32_t o0, o1, o2;       // tile origin along dims 0, 1, 2
+  int64_t soff, doff;        // byte offsets of the tile origin
+  int64_t v[kMaxChecks];     // check sums at the tile origin
+};
+
+template <bool CHECKS>
+__device__ __forceinline__ TileBase decode_tile(const CopyPlan& p, uint32_t tile_id) {
+  TileBase b;
+  b.o0 = b.o1 = b.o2 = 0;
+  b.soff = b.doff = 0;
+  b.v[0] = b.v[1] = 0;
   uint32_t rem = tile_id;
 #pragma unroll
-  for (int d = kMaxDims - 1; d >= 0; --d) {
-    if (d < p.nd) {
-      uint32_t q, r;
-      p.ntiles[d].divmod(rem, q, r);
-      origin[d] = r * p.tile[d];
-      rem = q;
+  for (int d = 0; d < kMaxDims; ++d) {
+    if (d >= p.nd) break;
+    uint32_t q, r;
+    p.ntiles[d].divmod(rem, q, r);
+    rem = q;
+    const uint32_t o = r * p.tile[d];
+    if (d == 0) b.o0 = o;
+    if (d == 1) b.o1 = o;
+    if (d == 2) b.o2 = o;
+    b.soff += (int64_t)o * p.sbytes[d];
+    b.doff += (int64_t)o * p.dbytes[d];
+    if (CHECKS) {
+#pragma unroll
+      for (int c = 0; c < kMaxChecks; ++c) b.v[c] += (int64_t)o * p.vmul[c][d];
     }
   }
+  return b;
 }
 
 // ---------------------------------------------------------------------------
-template <int UNIT, bool TO_DEVICE>
+template <int UNIT, bool TO_DEVICE, bool CHECKS>
 __global__ void __launch_bounds__(kThreads)
 copy_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src, char* __restrict__ dst) {
   using T = typename UnitType<UNIT>::T;
-  uint32_t origin[kMaxDims];
-  decode_tile(p, blockIdx.x, origin);
-  int64_t soff = 0, doff = 0, v[kMaxChecks] = {0, 0};
+  const TileBase b = decode_tile<CHECKS>(p, blockIdx.x);
+  const uint32_t t = threadIdx.x;
+  const uint32_t i0 = t & ((1u << p.log_t0) - 1);
+  const uint32_t i1 = (t >> p.log_t0) & ((1u << p.log_t1) - 1);
+  const uint32_t i2 = t >> (p.log_t0 + p.log_t1);
+  const uint32_t x0 = b.o0 + i0, x1 = b.o1 + i1, x2 = b.o2 + i2;
+  const char* sp = src + b.soff + (int64_t)i0 * p.sbytes[0] + (int64_t)i1 * p.sbytes[1] +
+                   (int64_t)i2 * p.sbytes[2];
+  char* dp = dst + b.doff + (int64_t)i0 * p.dbytes[0] + (int64_t)i1 * p.dbytes[1] +
+             (int64_t)i2 * p.dbytes[2];
+  int64_t vv[kMaxChecks] = {0, 0};
+  if (CHECKS) {
 #pragma unroll
-  for (int d = 0; d < kMaxDims; ++d) {
-    if (d < p.nd) {
-      soff += (int64_t)origin[d] * p.sbytes[d];
-      doff += (int64_t)origin[d] * p.dbytes[d];
-#pragma unroll
-      for (int c = 0; c < kMaxChecks; ++c)
-        if (c < p.nchecks) v[c] += (int64_t)origin[d] * p.vmul[c][d];
-    }
+    for (int c = 0; c < kMaxChecks; ++c)
+      vv[c] = b.v[c] + (int64_t)i0 * p.vmul[c][0] + (int64_t)i1 * p.vmul[c][1] +
+              (int64_t)i2 * p.vmul[c][2];
   }
-  const int d0 = p.nd - 1, dx = p.tx, dy = p.ty;
-  const uint32_t m0 = (1u << p.log_t0) - 1, m1 = (1u << p.log_t1) - 1;
+  // the dim the k loop walks, its current index and the per-step deltas
+  const int kd = p.kd;
+  uint32_t xk = kd == 0 ? x0 : (kd == 1 ? x1 : x2);
+  const uint32_t nk = p.size[kd];
+  const bool fixed_ok = (kd == 0 || x0 < p.size[0]) && (kd == 1 || x1 < p.size[1]) &&
+                        (kd == 2 || x2 < p.size[2]);
+  const int64_t ds = (int64_t)p.kstep * p.sbytes[kd], dd = (int64_t)p.kstep * p.dbytes[kd];
+  int64_t dv[kMaxChecks] = {0, 0};
+  if (CHECKS) {
+#pragma unroll
+    for (int c = 0; c < kMaxChecks; ++c) dv[c] = (int64_t)p.kstep * p.vmul[c][kd];
+  }
   T val[kUnitsPerThread];
-  int64_t dpos[kUnitsPerThread];
   bool live[kUnitsPerThread];
 #pragma unroll
   for (int k = 0; k < kUnitsPerThread; ++k) {
-    const uint32_t t = threadIdx.x + k * kThreads;
-    const uint32_t i0 = t & m0, i1 = (t >> p.log_t0) & m1, i2 = t >> (p.log_t0 + p.log_t1);
-    bool inb = origin[d0] + i0 < p.size[d0];
-    int64_t so = soff + (int64_t)i0 * p.sbytes[d0], dof = doff + (int64_t)i0 * p.dbytes[d0];
-    int64_t vv[kMaxChecks];
-#pragma unroll
-    for (int c = 0; c < kMaxChecks; ++c) vv[c] = v[c] + (int64_t)i0 * p.vmul[c][d0];
-    if (dx >= 0) {
-      inb = inb && (origin[dx] + i1 < p.size[dx]);
-      so += (int64_t)i1 * p.sbytes[dx];
-      dof += (int64_t)i1 * p.dbytes[dx];
-#pragma unroll
-      for (int c = 0; c < kMaxChecks; ++c) vv[c] += (int64_t)i1 * p.vmul[c][dx];
-    } else {
-      inb = inb && (i1 == 0);
-    }
-    if (dy >= 0) {
-      inb = inb && (i2 < p.t2) && (origin[dy] + i2 < p.size[dy]);
-      so += (int64_t)i2 * p.sbytes[dy];
-      dof += (int64_t)i2 * p.dbytes[dy];
-#pragma unroll
-      for (int c = 0; c < kMaxChecks; ++c) vv[c] += (int64_t)i2 * p.vmul[c][dy];
-    } else {
-      inb = inb && (i2 == 0);
-    }
+    const bool inb = fixed_ok && (xk + k * p.kstep < nk);
     bool valid = true;
+    if (CHECKS) {
 #pragma unroll
-    for (int c = 0; c < kMaxChecks; ++c)
-      if (c < p.nchecks) valid = valid && (vv[c] < p.vlimit[c]);
+      for (int c = 0; c < kMaxChecks; ++c)
+        if (c < p.nchecks) valid = valid && (vv[c] + k * dv[c] < p.vlimit[c]);
+    }
     val[k] = zero_of<T>();
-    if (inb && valid) val[k] = *reinterpret_cast<const T*>(src + so);
+    if (inb && valid) val[k] = load_unit<T>(sp + k * ds);
     live[k] = inb && (TO_DEVICE || valid);
-    dpos[k] = dof;
   }
 #pragma unroll
   for (int k = 0; k < kUnitsPerThread; ++k)
-    if (live[k]) *reinterpret_cast<T*>(dst + dpos[k]) = val[k];
+    if (live[k]) *reinterpret_cast<T*>(dp + k * dd) = val[k];
 }
 
 // ---------------------------------------------------------------------------
-// 64x64 tile of 2-byte elements.  smem holds the tile as [row = tb index][col =
-// ta index], 32-bit words, pitch 33 words so that both phases are conflict free.
+// 64x64 tiles of 2-byte elements; a CTA walks kSubTiles of them along dim 0.  smem
+// holds a tile as [row = dim-1 index][col = dim-0 index], 32-bit words, pitch 33 words
+// so that both phases are free of bank conflicts.
 constexpr int kTT = 64;
+constexpr int kSubTiles = 4;
 constexpr int kPitchWords = 33;
 
-// Number of leading elements (0..8), along a dim whose check multipliers are
-// `mul`, that satisfy every check, given the check sums at the first element.
+// Number of leading elements (0..8), along dim `dim`, that satisfy every check, given
+// the check sums at the first element.
 __device__ __forceinline__ int valid_run(const CopyPlan& p, const int64_t* vsum, int dim) {
   int n = 8;
 #pragma unroll
@@ -156,97 +175,95 @@ __device__ __forceinline__ int valid_run(const CopyPlan& p, const int64_t* vsum,
   return n;
 }
 
-template <bool TO_DEVICE, bool VEC_IN, bool VEC_OUT>
+template <bool TO_DEVICE, bool VEC_IN, bool VEC_OUT, bool CHECKS>
 __global__ void __launch_bounds__(kThreads)
 transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src,
                 char* __restrict__ dst) {
-  __shared__ uint32_t tile[kTT * kPitchWords];
-  uint32_t origin[kMaxDims];
-  decode_tile(p, blockIdx.x, origin);
-  int64_t soff = 0, doff = 0, v[kMaxChecks] = {0, 0};
-#pragma unroll
-  for (int d = 0; d < kMaxDims; ++d) {
-    if (d < p.nd) {
-      soff += (int64_t)origin[d] * p.sbytes[d];
-      doff += (int64_t)origin[d] * p.dbytes[d];
-#pragma unroll
-      for (int c = 0; c < kMaxChecks; ++c)
-        if (c < p.nchecks) v[c] += (int64_t)origin[d] * p.vmul[c][d];
-    }
-  }
-  const int da = p.ta, db = p.tb;
-  const int rem_a = (int)min((uint32_t)kTT, p.size[da] - origin[da]);
-  const int rem_b = (int)min((uint32_t)kTT, p.size[db] - origin[db]);
+  __shared__ uint32_t tile[2][kTT * kPitchWords];
+  const TileBase b = decode_tile<CHECKS>(p, blockIdx.x);
+  const int rem_b = (int)min((uint32_t)kTT, p.size[1] - b.o1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // phase 1 role: row (dim 1) and 16-byte vector (dim 0)
+  const int row1 = threadIdx.x >> 3, vec1 = threadIdx.x & 7;
+  // phase 2 role: word column (two dim-0 indices) and group of 8 dim-1 indices
+  const int pcol = 8 * (warp & 3) + (lane & 7);
+  const int grp = 4 * (warp >> 2) + (lane >> 3);
+  const char* sp0 = src + b.soff + (int64_t)row1 * p.sbytes[1] + vec1 * 16;
+  const int64_t srow32 = 32 * p.sbytes[1];
+  char* dp0 = dst + b.doff + (int64_t)(2 * pcol) * p.dbytes[0] + grp * 16;
 
-  // Phase 1: rows along tb, 16-byte vectors along ta.
+#pragma unroll 1
+  for (int sub = 0; sub < kSubTiles; ++sub) {
+    const uint32_t a0 = b.o0 + sub * kTT;
+    if (a0 >= p.size[0]) break;
+    const int rem_a = (int)min((uint32_t)kTT, p.size[0] - a0);
+    uint32_t* tl = tile[sub & 1];
+    // Phase 1: rows along dim 1, 16-byte vectors along dim 0.
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
-    const int row = (threadIdx.x >> 3) + k * 32;
-    const int vec = threadIdx.x & 7;
-    uint32_t w[4] = {0, 0, 0, 0};
-    int na = rem_a - vec * 8;
-    na = na < 0 ? 0 : (na > 8 ? 8 : na);
-    if (row >= rem_b) na = 0;
-    if (TO_DEVICE && na > 0) {
-      int64_t vs[kMaxChecks];
+    for (int k = 0; k < 2; ++k) {
+      const int row = row1 + k * 32;
+      uint32_t w[4] = {0, 0, 0, 0};
+      int na = rem_a - vec1 * 8;
+      na = na < 0 ? 0 : (na > 8 ? 8 : na);
+      if (row >= rem_b) na = 0;
+      if (CHECKS && TO_DEVICE && na > 0) {
+        int64_t vs[kMaxChecks];
 #pragma unroll
-      for (int c = 0; c < kMaxChecks; ++c)
-        vs[c] = v[c] + (int64_t)row * p.vmul[c][db] + (int64_t)(vec * 8) * p.vmul[c][da];
-      na = min(na, valid_run(p, vs, da));
-    }
-    const char* sp = src + soff + (int64_t)row * p.sbytes[db] + vec * 16;
-    if (VEC_IN && na == 8) {
-      const uint4 q = ld_stream_v4(sp);
-      w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
-    } else {
+        for (int c = 0; c < kMaxChecks; ++c)
+          vs[c] = b.v[c] + (int64_t)row * p.vmul[c][1] + (int64_t)(sub * kTT + vec1 * 8) * p.vmul[c][0];
+        na = min(na, valid_run(p, vs, 0));
+      }
+      const char* sp = sp0 + k * srow32 + (int64_t)sub * (kTT * 2);
+      if (VEC_IN && na == 8) {
+        const uint4 q = ld_stream_v4(sp);
+        w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (j < na) {
-          const uint32_t e = *reinterpret_cast<const uint16_t*>(sp + 2 * j);
-          w[j >> 1] |= e << ((j & 1) * 16);
+        for (int j = 0; j < 8; ++j) {
+          if (j < na) {
+            const uint32_t e = *reinterpret_cast<const uint16_t*>(sp + 2 * j);
+            w[j >> 1] |= e << ((j & 1) * 16);
+          }
         }
       }
+      uint32_t* tp = &tl[row * kPitchWords + vec1 * 4];
+      tp[0] = w[0]; tp[1] = w[1]; tp[2] = w[2]; tp[3] = w[3];
     }
-    uint32_t* tp = &tile[row * kPitchWords + vec * 4];
-    tp[0] = w[0]; tp[1] = w[1]; tp[2] = w[2]; tp[3] = w[3];
-  }
-  __syncthreads();
+    __syncthreads();  // (the other smem buffer is still being read by slower warps)
 
-  // Phase 2: output rows along ta (two per thread), 8 consecutive tb per thread.
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int pcol = 8 * (warp & 3) + (lane & 7);   // word column: ta = 2*pcol, 2*pcol+1
-  const int grp = 4 * (warp >> 2) + (lane >> 3);  // tb = 8*grp .. 8*grp+7
-  uint32_t w[8];
+    // Phase 2: output rows along dim 0 (two per thread), 8 consecutive dim-1 indices each.
+    uint32_t w[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) w[j] = tile[(8 * grp + j) * kPitchWords + pcol];
-  int nb = rem_b - grp * 8;
-  nb = nb < 0 ? 0 : (nb > 8 ? 8 : nb);
+    for (int j = 0; j < 8; ++j) w[j] = tl[(8 * grp + j) * kPitchWords + pcol];
+    int nb = rem_b - grp * 8;
+    nb = nb < 0 ? 0 : (nb > 8 ? 8 : nb);
 #pragma unroll
-  for (int half = 0; half < 2; ++half) {
-    const int a = 2 * pcol + half;
-    if (a >= rem_a) continue;
-    int n = nb;
-    if (!TO_DEVICE && n > 0) {
-      int64_t vs[kMaxChecks];
+    for (int half = 0; half < 2; ++half) {
+      const int a = 2 * pcol + half;
+      if (a >= rem_a) continue;
+      int n = nb;
+      if (CHECKS && !TO_DEVICE && n > 0) {
+        int64_t vs[kMaxChecks];
 #pragma unroll
-      for (int c = 0; c < kMaxChecks; ++c)
-        vs[c] = v[c] + (int64_t)a * p.vmul[c][da] + (int64_t)(grp * 8) * p.vmul[c][db];
-      n = min(n, valid_run(p, vs, db));
-    }
-    const uint32_t sel = half ? 0x7632u : 0x5410u;
-    uint4 q;
-    q.x = __byte_perm(w[0], w[1], sel);
-    q.y = __byte_perm(w[2], w[3], sel);
-    q.z = __byte_perm(w[4], w[5], sel);
-    q.w = __byte_perm(w[6], w[7], sel);
-    char* dp = dst + doff + (int64_t)a * p.dbytes[da] + grp * 16;
-    if (VEC_OUT && n == 8) {
-      st_global_v4(dp, q);
-    } else {
-      const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
+        for (int c = 0; c < kMaxChecks; ++c)
+          vs[c] = b.v[c] + (int64_t)(sub * kTT + a) * p.vmul[c][0] + (int64_t)(grp * 8) * p.vmul[c][1];
+        n = min(n, valid_run(p, vs, 1));
+      }
+      const uint32_t sel = half ? 0x7632u : 0x5410u;
+      uint4 q;
+      q.x = __byte_perm(w[0], w[1], sel);
+      q.y = __byte_perm(w[2], w[3], sel);
+      q.z = __byte_perm(w[4], w[5], sel);
+      q.w = __byte_perm(w[6], w[7], sel);
+      char* dp = dp0 + (int64_t)(sub * kTT + half) * p.dbytes[0];
+      if (VEC_OUT && n == 8) {
+        st_global_v4(dp, q);
+      } else {
+        const uint32_t ww[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (j < n) *reinterpret_cast<uint16_t*>(dp + 2 * j) = (uint16_t)(ww[j >> 1] >> ((j & 1) * 16));
+        for (int j = 0; j < 8; ++j)
+          if (j < n) *reinterpret_cast<uint16_t*>(dp + 2 * j) = (uint16_t)(ww[j >> 1] >> ((j & 1) * 16));
+      }
     }
   }
 }
@@ -282,29 +299,41 @@ struct Request {
   int ndev;
 };
 
-template <bool TO_DEVICE>
-int launch_copy(const CopyPlan& plan, int unit, uint32_t blocks, const char* src, char* dst,
-                cudaStream_t st) {
+template <bool TO_DEVICE, bool CHECKS>
+int launch_copy2(const CopyPlan& plan, int unit, uint32_t blocks, const char* src, char* dst,
+                 cudaStream_t st) {
   switch (unit) {
-    case 16: copy_tiles<16, TO_DEVICE><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    case 8: copy_tiles<8, TO_DEVICE><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    case 4: copy_tiles<4, TO_DEVICE><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    case 2: copy_tiles<2, TO_DEVICE><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    default: copy_tiles<1, TO_DEVICE><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 16: copy_tiles<16, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 8: copy_tiles<8, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 4: copy_tiles<4, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 2: copy_tiles<2, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    default: copy_tiles<1, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
   }
   TSB_CHECK_LAUNCH();
   return TS_OK;
 }
-
 template <bool TO_DEVICE>
-int launch_transpose(const CopyPlan& plan, bool vin, bool vout, uint32_t blocks, const char* src,
-                     char* dst, cudaStream_t st) {
-  if (vin && vout) transpose_tiles<TO_DEVICE, true, true><<<blocks, kThreads, 0, st>>>(plan, src, dst);
-  else if (vin) transpose_tiles<TO_DEVICE, true, false><<<blocks, kThreads, 0, st>>>(plan, src, dst);
-  else if (vout) transpose_tiles<TO_DEVICE, false, true><<<blocks, kThreads, 0, st>>>(plan, src, dst);
-  else transpose_tiles<TO_DEVICE, false, false><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+int launch_copy(const CopyPlan& plan, int unit, bool checks, uint32_t blocks, const char* src,
+                char* dst, cudaStream_t st) {
+  return checks ? launch_copy2<TO_DEVICE, true>(plan, unit, blocks, src, dst, st)
+                : launch_copy2<TO_DEVICE, false>(plan, unit, blocks, src, dst, st);
+}
+
+template <bool TO_DEVICE, bool CHECKS>
+int launch_transpose2(const CopyPlan& plan, bool vin, bool vout, uint32_t blocks, const char* src,
+                      char* dst, cudaStream_t st) {
+  if (vin && vout) transpose_tiles<TO_DEVICE, true, true, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  else if (vin) transpose_tiles<TO_DEVICE, true, false, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  else if (vout) transpose_tiles<TO_DEVICE, false, true, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  else transpose_tiles<TO_DEVICE, false, false, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
   TSB_CHECK_LAUNCH();
   return TS_OK;
+}
+template <bool TO_DEVICE>
+int launch_transpose(const CopyPlan& plan, bool vin, bool vout, bool checks, uint32_t blocks,
+                     const char* src, char* dst, cudaStream_t st) {
+  return checks ? launch_transpose2<TO_DEVICE, true>(plan, vin, vout, blocks, src, dst, st)
+                : launch_transpose2<TO_DEVICE, false>(plan, vin, vout, blocks, src, dst, st);
 }
 
 int run(const Request& rq, cudaStream_t st) {
@@ -380,6 +409,7 @@ int run(const Request& rq, cudaStream_t st) {
   CopyPlan plan{};
   plan.nchecks = nchecks;
   for (int c = 0; c < kMaxChecks; ++c) plan.vlimit[c] = vlimit[c];
+  const bool checks = nchecks > 0;
 
   int ua = -1, ub = -1;  // unit-stride dims of source / destination
   for (int d = 0; d < nd; ++d) {
@@ -388,36 +418,61 @@ int run(const Request& rq, cudaStream_t st) {
   }
   const uintptr_t sbase = (uintptr_t)rq.src, dbase = (uintptr_t)rq.dst;
 
-  if (eb == 2 && ua >= 0 && ub >= 0 && ua != ub && it[ua].size >= 16 && it[ub].size >= 16) {
-    // ---- transpose path
-    plan.nd = nd;
-    bool vin = sbase % 16 == 0, vout = dbase % 16 == 0;
-    uint64_t ntiles = 1;
-    for (int d = 0; d < nd; ++d) {
-      plan.size[d] = (uint32_t)it[d].size;
-      plan.sbytes[d] = it[d].s * eb;
-      plan.dbytes[d] = it[d].d * eb;
-      plan.tile[d] = (d == ua || d == ub) ? kTT : 1;
-      const uint32_t nt = (uint32_t)ceil_div(it[d].size, plan.tile[d]);
-      plan.ntiles[d].init(nt);
-      ntiles *= nt;
-      for (int c = 0; c < kMaxChecks; ++c) plan.vmul[c][d] = it[d].vm[c];
-      if (d != ua && plan.sbytes[d] % 16) vin = false;
-      if (d != ub && plan.dbytes[d] % 16) vout = false;
+  // Fills plan dims from `order` (plan position -> index into it[]); unit = bytes per
+  // index step of plan dim 0 on the copy path (elements there are grouped into units).
+  auto fill = [&](const int* order, int n, int unit_elems) {
+    plan.nd = n;
+    for (int k = 0; k < n; ++k) {
+      const IterDim& d = it[order[k]];
+      const bool grouped = k == 0 && unit_elems > 1;
+      plan.size[k] = (uint32_t)(grouped ? d.size / unit_elems : d.size);
+      plan.sbytes[k] = d.s * eb * (grouped ? unit_elems : 1);
+      plan.dbytes[k] = d.d * eb * (grouped ? unit_elems : 1);
+      for (int c = 0; c < kMaxChecks; ++c) plan.vmul[c][k] = d.vm[c] * (grouped ? unit_elems : 1);
+      plan.tile[k] = 1;
     }
-    if (ntiles >= (1ull << 31)) return TS_ERR_TOO_LARGE;
-    plan.ta = ua;
-    plan.tb = ub;
-    return rq.to_device ? launch_transpose<true>(plan, vin, vout, (uint32_t)ntiles, rq.src, rq.dst, st)
-                        : launch_transpose<false>(plan, vin, vout, (uint32_t)ntiles, rq.src, rq.dst, st);
+  };
+  auto count_tiles = [&](uint64_t& ntiles) {
+    ntiles = 1;
+    for (int k = 0; k < plan.nd; ++k) {
+      const uint32_t nt = (uint32_t)ceil_div(plan.size[k], plan.tile[k]);
+      plan.ntiles[k].init(nt);
+      ntiles *= nt;
+    }
+    return ntiles < (1ull << 31);
+  };
+
+  if (eb == 2 && ua >= 0 && ub >= 0 && ua != ub && it[ua].size >= 16 && it[ub].size >= 16) {
+    // ---- transpose path: plan dim 0 = source-contiguous, dim 1 = destination-contiguous
+    int order[kMaxDims], n = 0;
+    order[n++] = ua;
+    order[n++] = ub;
+    for (int d = nd - 1; d >= 0; --d)
+      if (d != ua && d != ub) order[n++] = d;
+    fill(order, n, 1);
+    bool vin = sbase % 16 == 0, vout = dbase % 16 == 0;
+    for (int k = 0; k < n; ++k) {
+      if (k != 0 && plan.sbytes[k] % 16) vin = false;
+      if (k != 1 && plan.dbytes[k] % 16) vout = false;
+    }
+    plan.tile[0] = kTT * kSubTiles;
+    plan.tile[1] = kTT;
+    uint64_t ntiles;
+    if (!count_tiles(ntiles)) return TS_ERR_TOO_LARGE;
+    return rq.to_device
+               ? launch_transpose<true>(plan, vin, vout, checks, (uint32_t)ntiles, rq.src, rq.dst, st)
+               : launch_transpose<false>(plan, vin, vout, checks, (uint32_t)ntiles, rq.src, rq.dst, st);
   }
 
-  // ---- copy path.  Needs an innermost dim with unit stride on both sides; a
-  // dummy one of extent 1 is appended when the tensor has none.
-  if (!(it[nd - 1].s == 1 && it[nd - 1].d == 1)) {
+  // ---- copy path.  Plan dim 0 must have unit stride on both sides; an extent-1 dummy
+  // stands in when the tensor has none.
+  int inner = -1;
+  for (int d = 0; d < nd; ++d)
+    if (it[d].s == 1 && it[d].d == 1) inner = d;
+  if (inner < 0) {
     if (nd == kMaxDims) return TS_ERR_UNSUPPORTED;
     it[nd] = IterDim{1, 1, 1, {0, 0}};
-    ++nd;
+    inner = nd++;
   }
   // Widest unit (bytes) dividing every address, the inner extent and the limits.
   int unit = 16;
@@ -426,64 +481,61 @@ int run(const Request& rq, cudaStream_t st) {
     if (u == eb) return true;
     const int ue = u / eb;
     if (sbase % u || dbase % u) return false;
-    if (it[nd - 1].size % ue) return false;
-    for (int d = 0; d < nd - 1; ++d)
-      if ((it[d].s * eb) % u || (it[d].d * eb) % u) return false;
+    if (it[inner].size % ue) return false;
+    for (int d = 0; d < nd; ++d)
+      if (d != inner && ((it[d].s * eb) % u || (it[d].d * eb) % u)) return false;
     for (int c = 0; c < nchecks; ++c)
-      if (it[nd - 1].vm[c] != 0 && vlimit[c] % ue) return false;
+      if (it[inner].vm[c] != 0 && vlimit[c] % ue) return false;
     return true;
   };
   while (!fits(unit)) unit >>= 1;
-  const int ue = unit / eb;
-  plan.nd = nd;
+  // dims next-most contiguous in the source (dx) and in the destination (dy)
+  int dx = -1, dy = -1;
   for (int d = 0; d < nd; ++d) {
-    const bool last = d == nd - 1;
-    plan.size[d] = (uint32_t)(last ? it[d].size / ue : it[d].size);
-    plan.sbytes[d] = last ? unit : it[d].s * eb;
-    plan.dbytes[d] = last ? unit : it[d].d * eb;
-    for (int c = 0; c < kMaxChecks; ++c) plan.vmul[c][d] = it[d].vm[c] * (last ? ue : 1);
-    plan.tile[d] = 1;
+    if (d == inner) continue;
+    if (dx < 0 || llabs(it[d].s) < llabs(it[dx].s)) dx = d;
   }
-  // Tile: inner run first, then the dims next-most contiguous in source and in destination.
-  const uint32_t t0 = std::min<uint32_t>(pow2_ceil(plan.size[nd - 1]), kTileUnits);
-  uint32_t rest = kTileUnits / t0;
-  int tx = -1, ty = -1;
-  for (int d = 0; d < nd - 1; ++d) {
-    if (tx < 0 || llabs(plan.sbytes[d]) < llabs(plan.sbytes[tx])) tx = d;
-    if (ty < 0 || llabs(plan.dbytes[d]) < llabs(plan.dbytes[ty])) ty = d;
+  for (int d = 0; d < nd; ++d) {
+    if (d == inner || d == dx) continue;
+    if (dy < 0 || llabs(it[d].d) < llabs(it[dy].d)) dy = d;
   }
-  uint32_t t1 = 1, t2 = 1;
-  if (tx >= 0 && rest > 1) {
-    if (tx == ty) {
-      t1 = std::min<uint32_t>(rest, pow2_ceil(plan.size[tx]));
-      ty = -1;
-    } else {
-      const uint32_t want = 1u << ((log2_floor(rest) + 1) / 2);
-      t1 = std::min<uint32_t>(want, pow2_ceil(plan.size[tx]));
-      t2 = std::min<uint32_t>(rest / t1, pow2_ceil(plan.size[ty]));
-      // hand unused budget back to the source-side dim
-      t1 = std::min<uint32_t>(rest / t2, pow2_ceil(plan.size[tx]));
-    }
+  // extent-1 dummies keep dims 1 and 2 present
+  int extra = nd;
+  IterDim dummy{1, 0, 0, {0, 0}};
+  if (dx < 0) { if (extra == kMaxDims) return TS_ERR_UNSUPPORTED; it[extra] = dummy; dx = extra++; }
+  if (dy < 0) { if (extra == kMaxDims) return TS_ERR_UNSUPPORTED; it[extra] = dummy; dy = extra++; }
+  int order[kMaxDims], n = 0;
+  order[n++] = inner;
+  order[n++] = dx;
+  order[n++] = dy;
+  for (int d = nd - 1; d >= 0; --d)
+    if (d != inner && d != dx && d != dy) order[n++] = d;
+  fill(order, n, unit / eb);
+  // Thread tile T0 x T1 x T2 = 256 threads; the k loop extends the CTA tile along kd.
+  const uint32_t t0 = std::min<uint32_t>(pow2_ceil(plan.size[0]), kThreads);
+  const uint32_t rest = kThreads / t0;
+  uint32_t t1, t2;
+  if (plan.size[2] > 1) {
+    const uint32_t want = 1u << ((log2_floor(rest) + 1) / 2);
+    t1 = std::min<uint32_t>(want, pow2_ceil(plan.size[1]));
+    t2 = rest / t1;
   } else {
-    tx = ty = -1;
+    t1 = rest;
+    t2 = 1;
   }
-  plan.tile[nd - 1] = t0;
-  if (tx >= 0) plan.tile[tx] = t1;
-  if (ty >= 0) plan.tile[ty] = t2;
-  plan.tx = tx;
-  plan.ty = ty;
   plan.log_t0 = log2_floor(t0);
   plan.log_t1 = log2_floor(t1);
-  plan.t2 = t2;
-  uint64_t ntiles = 1;
-  for (int d = 0; d < nd; ++d) {
-    const uint32_t nt = (uint32_t)ceil_div(plan.size[d], plan.tile[d]);
-    plan.ntiles[d].init(nt);
-    ntiles *= nt;
-  }
-  if (ntiles >= (1ull << 31)) return TS_ERR_TOO_LARGE;
-  return rq.to_device ? launch_copy<true>(plan, unit, (uint32_t)ntiles, rq.src, rq.dst, st)
-                      : launch_copy<false>(plan, unit, (uint32_t)ntiles, rq.src, rq.dst, st);
+  const int kd = plan.size[2] > 1 ? 2 : (plan.size[1] > t1 ? 1 : 0);
+  plan.kd = kd;
+  plan.kstep = kd == 2 ? t2 : (kd == 1 ? t1 : t0);
+  plan.tile[0] = t0;
+  plan.tile[1] = t1;
+  plan.tile[2] = t2;
+  plan.tile[kd] *= kUnitsPerThread;
+  uint64_t ntiles;
+  if (!count_tiles(ntiles)) return TS_ERR_TOO_LARGE;
+  return rq.to_device ? launch_copy<true>(plan, unit, checks, (uint32_t)ntiles, rq.src, rq.dst, st)
+                      : launch_copy<false>(plan, unit, checks, (uint32_t)ntiles, rq.src, rq.dst, st);
 }
 
 // Lowest and one-past-highest element offsets a non-negatively strided host tensor touches.

@@ -60,9 +60,19 @@ __device__ __forceinline__ float row_allreduce(float v, const RowCtx& c, float (
   return total;
 }
 
-template <int K, int OP>
+__device__ __forceinline__ float ex2_f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// FULL: every (row, stick) a thread is assigned exists and cols is a stick multiple,
+// so no load, store or reduction needs a predicate.
+template <int K, int OP, bool FULL>
 __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ RowParams P) {
   __shared__ float part[kWarps][4];
+  constexpr bool kSoft = OP == kSoftmax || OP == kLogSoftmax;
+  constexpr float kLog2e = 1.4426950408889634f;
   RowCtx c;
   c.lane = threadIdx.x & 31;
   c.warp = threadIdx.x >> 5;
@@ -71,84 +81,101 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
   c.rsub = c.lane >> 3;
   const uint32_t group = blockIdx.x * (kWarps >> P.ws_log) + (c.warp >> P.ws_log);
   c.row = group * 4 + c.rsub;
-  c.live = c.row < P.rows;
+  c.live = FULL || c.row < P.rows;
   const uint32_t lv = c.lane & 7;
-  const bool ragged = (P.cols & 63) != 0;
+  const bool ragged = !FULL && (P.cols & 63) != 0;
+  const int64_t row_off = (int64_t)c.row * kStickHalfs + lv * 8;
+  const int64_t stick_stride = (int64_t)P.rows * kStickHalfs;
 
-  float v[K][8];
+  Vec8h raw[K];
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const uint32_t s = c.ws_idx + k * c.ws;
-    const bool have = c.live && s < P.nsticks;
-    Vec8h t;
-    t.u = make_uint4(0, 0, 0, 0);
-    if (have) t.u = ld_stream_v4(P.x + ((int64_t)s * P.rows + c.row) * kStickHalfs + lv * 8);
+    const bool have = FULL || (c.live && s < P.nsticks);
+    raw[k].u = make_uint4(0, 0, 0, 0);
+    if (have) raw[k].u = ld_stream_v4(P.x + s * stick_stride + row_off);
+    if (!FULL) {
+      const __half fill = kSoft ? __ushort_as_half((unsigned short)0xFC00) : __float2half(0.f);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      const bool valid = have && (!ragged || s * 64 + lv * 8 + e < P.cols);
-      const float f = __half2float(t.h[e]);
-      v[k][e] = valid ? f : ((OP == kSoftmax || OP == kLogSoftmax) ? -INFINITY : 0.f);
+      for (int e = 0; e < 8; ++e)
+        if (!have || (ragged && s * 64 + lv * 8 + e >= P.cols)) raw[k].h[e] = fill;
     }
   }
 
+  float v[K][8];
   const float inv_n = 1.f / (float)P.cols;
   float shift = 0.f, scale = 1.f, lse = 0.f;
-  if (OP == kSoftmax || OP == kLogSoftmax) {
-    float m = -INFINITY;
+  if (kSoft) {
+    __half2 m2 = raw[0].h2[0];
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) m = fmaxf(m, v[k][e]);
+      for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, raw[k].h2[j]);
+    float m = fmaxf(__low2float(m2), __high2float(m2));
     m = row_allreduce<true>(m, c, part);
+    const float ml = m * kLog2e;
     float sum = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const float d = v[k][e] - m;
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(raw[k].h2[j]);
+        const float e0 = ex2_f(fmaf(f.x, kLog2e, -ml)), e1 = ex2_f(fmaf(f.y, kLog2e, -ml));
+        sum += e0 + e1;
         if (OP == kSoftmax) {
-          v[k][e] = __expf(d);
-          sum += v[k][e];
+          v[k][2 * j] = e0;
+          v[k][2 * j + 1] = e1;
         } else {
-          v[k][e] = d;
-          sum += __expf(d);
+          v[k][2 * j] = f.x - m;
+          v[k][2 * j + 1] = f.y - m;
         }
       }
     sum = row_allreduce<false>(sum, c, part);
     scale = __fdividef(1.f, sum);
     lse = __logf(sum);
-  } else if (OP == kLayerNorm) {
-    float sum = 0.f;
+  } else {
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
-      for (int e = 0; e < 8; ++e) sum += v[k][e];
-    shift = row_allreduce<false>(sum, c, part) * inv_n;
-    float sq = 0.f;
-#pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const uint32_t s = c.ws_idx + k * c.ws;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        const bool valid = s < P.nsticks && (!ragged || s * 64 + lv * 8 + e < P.cols);
-        const float d = valid ? v[k][e] - shift : 0.f;
-        sq += d * d;
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(raw[k].h2[j]);
+        v[k][2 * j] = f.x;
+        v[k][2 * j + 1] = f.y;
       }
+    if (OP == kLayerNorm) {
+      float sum = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sum += v[k][e];
+      shift = row_allreduce<false>(sum, c, part) * inv_n;
+      float sq = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const uint32_t s = c.ws_idx + k * c.ws;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const bool valid = FULL || (s < P.nsticks && (!ragged || s * 64 + lv * 8 + e < P.cols));
+          const float d = valid ? v[k][e] - shift : 0.f;
+          v[k][e] = d;
+          sq = fmaf(d, d, sq);
+        }
+      }
+      scale = rsqrtf(row_allreduce<false>(sq, c, part) * inv_n + P.eps);
+    } else {  // RMS norm
+      float sq = 0.f;
+#pragma unroll
+      for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sq = fmaf(v[k][e], v[k][e], sq);
+      scale = rsqrtf(row_allreduce<false>(sq, c, part) * inv_n + P.eps);
     }
-    scale = rsqrtf(row_allreduce<false>(sq, c, part) * inv_n + P.eps);
-  } else {  // RMS norm
-    float sq = 0.f;
-#pragma unroll
-    for (int k = 0; k < K; ++k)
-#pragma unroll
-      for (int e = 0; e < 8; ++e) sq += v[k][e] * v[k][e];
-    scale = rsqrtf(row_allreduce<false>(sq, c, part) * inv_n + P.eps);
   }
 
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const uint32_t s = c.ws_idx + k * c.ws;
-    if (!(c.live && s < P.nsticks)) continue;
+    if (!FULL && !(c.live && s < P.nsticks)) continue;
     const uint32_t col = s * 64 + lv * 8;
     Vec8h w, b, out;
     w.u = b.u = make_uint4(0, 0, 0, 0);
@@ -157,26 +184,42 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
       if (P.bias) b.u = ld_global_v4(P.bias + col);
     }
 #pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      float r;
-      if (OP == kSoftmax) r = v[k][e] * scale;
-      else if (OP == kLogSoftmax) r = v[k][e] - lse;
-      else r = (v[k][e] - shift) * scale;
-      __half h;
-      if (OP == kLayerNorm) {
-        if (P.weight) r *= __half2float(w.h[e]);
-        if (P.bias) r += __half2float(b.h[e]);
-        h = __float2half_rn(r);
-      } else if (OP == kRmsNorm) {
-        if (P.weight && P.round_before_weight) h = __hmul(w.h[e], __float2half_rn(r));
-        else h = __float2half_rn(P.weight ? r * __half2float(w.h[e]) : r);
+    for (int j = 0; j < 4; ++j) {
+      float r0, r1;
+      if (OP == kSoftmax) {
+        r0 = v[k][2 * j] * scale;
+        r1 = v[k][2 * j + 1] * scale;
+      } else if (OP == kLogSoftmax) {
+        r0 = v[k][2 * j] - lse;
+        r1 = v[k][2 * j + 1] - lse;
       } else {
-        h = __float2half_rn(r);
+        r0 = v[k][2 * j] * scale;      // layer norm: v already holds x - mean
+        r1 = v[k][2 * j + 1] * scale;
       }
-      if (ragged && col + e >= P.cols) h = __float2half(0.f);
-      out.h[e] = h;
+      __half2 h;
+      if (OP == kLayerNorm) {
+        const float2 wf = __half22float2(w.h2[j]), bf = __half22float2(b.h2[j]);
+        if (P.weight) { r0 *= wf.x; r1 *= wf.y; }
+        if (P.bias) { r0 += bf.x; r1 += bf.y; }
+        h = __floats2half2_rn(r0, r1);
+      } else if (OP == kRmsNorm) {
+        if (P.weight && P.round_before_weight) {
+          h = __hmul2(w.h2[j], __floats2half2_rn(r0, r1));
+        } else {
+          const float2 wf = __half22float2(w.h2[j]);
+          h = P.weight ? __floats2half2_rn(r0 * wf.x, r1 * wf.y) : __floats2half2_rn(r0, r1);
+        }
+      } else {
+        h = __floats2half2_rn(r0, r1);
+      }
+      out.h2[j] = h;
     }
-    st_global_v4(P.y + ((int64_t)s * P.rows + c.row) * kStickHalfs + lv * 8, out.u);
+    if (ragged) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (col + e >= P.cols) out.h[e] = __float2half(0.f);
+    }
+    st_global_v4(P.y + s * stick_stride + row_off, out.u);
   }
 }
 
@@ -189,12 +232,18 @@ int launch_rows(const RowParams& P0, cudaStream_t st) {
   const uint32_t per_thread = (uint32_t)ceil_div(P.nsticks, 1 << ws_log);
   const uint32_t groups = (uint32_t)ceil_div(P.rows, 4);
   const uint32_t blocks = (uint32_t)ceil_div(groups, kWarps >> ws_log);
-  if (per_thread <= 1) row_kernel<1, OP><<<blocks, kThreads, 0, st>>>(P);
-  else if (per_thread <= 2) row_kernel<2, OP><<<blocks, kThreads, 0, st>>>(P);
-  else if (per_thread <= 4) row_kernel<4, OP><<<blocks, kThreads, 0, st>>>(P);
-  else if (per_thread <= 8) row_kernel<8, OP><<<blocks, kThreads, 0, st>>>(P);
-  else if (per_thread <= 16) row_kernel<16, OP><<<blocks, kThreads, 0, st>>>(P);
+  const bool full = P.cols % 64 == 0 && P.nsticks % (1u << ws_log) == 0 &&
+                    P.rows % (4 * (kWarps >> ws_log)) == 0;
+#define TSB_ROW_CASE(KK)                                                        \
+  if (full && per_thread == KK) row_kernel<KK, OP, true><<<blocks, kThreads, 0, st>>>(P); \
+  else row_kernel<KK, OP, false><<<blocks, kThreads, 0, st>>>(P)
+  if (per_thread <= 1) { TSB_ROW_CASE(1); }
+  else if (per_thread <= 2) { TSB_ROW_CASE(2); }
+  else if (per_thread <= 4) { TSB_ROW_CASE(4); }
+  else if (per_thread <= 8) { TSB_ROW_CASE(8); }
+  else if (per_thread <= 16) { TSB_ROW_CASE(16); }
   else return TS_ERR_TOO_LARGE;
+#undef TSB_ROW_CASE
   TSB_CHECK_LAUNCH();
   return TS_OK;
 }
