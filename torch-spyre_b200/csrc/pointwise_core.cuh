@@ -121,12 +121,108 @@ __device__ __forceinline__ void fetch_tensor(const Params& P, int t, const Item&
   for (int j = 0; j < 4; ++j) v[j] = x.h2[j];
 }
 
+__device__ __forceinline__ void store_full(const Params& P, __half* out, const Item& it, const V& v) {
+  if (!it.live) return;
+  Vec8h t;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) t.h2[j] = v[j];
+  if (P.ragged) {
+    const uint32_t col = it.s * kStickHalfs + it.lv * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+      if (col + e >= P.cols) t.h[e] = __float2half(0.f);
+  }
+  st_global_v4(out + it.flat_off, t.u);
+}
+
+// ---- operand contexts ---------------------------------------------------------------
+// General: every item carries its own coordinates.
 template <int U>
-__device__ __forceinline__ void fetch(const Params& P, Regs<U>& R, int kind, int idx, float imm,
-                                      const Item (&it)[U], V (&v)[U]) {
+struct ItemCtx {
+  const Params& P;
+  Item it[U];
+  __device__ __forceinline__ explicit ItemCtx(const Params& p) : P(p) {}
+  __device__ __forceinline__ void tensor(int t, int u, V& v) const { fetch_tensor(P, t, it[u], v); }
+  __device__ __forceinline__ void store(int o, int u, const V& v) const {
+    store_full(P, P.out[o], it[u], v);
+  }
+};
+
+// Row kernels with a compile-time program: all items of a thread lie in one row, so
+// each tensor needs one base pointer and one stride per stick column, set up once.
+// FULL: no item is ever out of range and cols is a stick multiple.
+template <int U, bool FULL>
+struct RowCtx {
+  const Params& P;
+  const __half* base[TS_PW_MAX_INPUTS];
+  int64_t sstride[TS_PW_MAX_INPUTS];
+  __half2 bval[TS_PW_MAX_INPUTS];
+  int64_t out_base;   // element offset of this thread's vector in stick column 0 of an output
+  int64_t out_stride;
+  uint32_t lv, s[U];
+  bool live[U];
+  __device__ __forceinline__ RowCtx(const Params& p, uint32_t row, uint32_t lane_vec, bool row_live)
+      : P(p), lv(lane_vec) {
+    Item it;
+    it.r = row;
+    it.i0 = it.i1 = it.i2 = 0;
+    if (p.need_index && row_live) {
+      uint32_t q;
+      p.div_d2.divmod(row, q, it.i2);
+      p.div_d1.divmod(q, it.i0, it.i1);
+    }
+    out_base = (int64_t)row * kStickHalfs + lane_vec * 8;
+    out_stride = (int64_t)p.rows * kStickHalfs;
+#pragma unroll
+    for (int t = 0; t < TS_PW_MAX_INPUTS; ++t) {
+      base[t] = nullptr;
+      sstride[t] = 0;
+      bval[t] = __float2half2_rn(0.f);
+      if (t < p.n_in) {
+        const TensorDesc& d = p.in[t];
+        const uint32_t trow = d.flat ? row : it.i0 * (uint32_t)d.m0 + it.i1 * (uint32_t)d.m1 +
+                                                 it.i2 * (uint32_t)d.m2;
+        base[t] = d.ptr + (int64_t)trow * kStickHalfs + (d.col_bcast ? 0 : lane_vec * 8);
+        sstride[t] = d.col_bcast ? 0 : d.stick_stride;
+        if (d.col_bcast && row_live) bval[t] = __half2half2(__ldg(base[t]));
+      }
+    }
+  }
+  __device__ __forceinline__ void tensor(int t, int u, V& v) const {
+    if (!FULL && !live[u]) {
+      set_all(v, __float2half2_rn(0.f));
+      return;
+    }
+    if (P.in[t].col_bcast) {
+      set_all(v, bval[t]);
+      return;
+    }
+    Vec8h x;
+    x.u = ld_stream_v4(base[t] + (int64_t)s[u] * sstride[t]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = x.h2[j];
+  }
+  __device__ __forceinline__ void store(int o, int u, const V& v) const {
+    if (!FULL && !live[u]) return;
+    Vec8h t;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) t.h2[j] = v[j];
+    if (!FULL && P.ragged) {
+      const uint32_t col = s[u] * kStickHalfs + lv * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (col + e >= P.cols) t.h[e] = __float2half(0.f);
+    }
+    st_global_v4(P.out[o] + out_base + (int64_t)s[u] * out_stride, t.u);
+  }
+};
+
+template <int U, class Ctx>
+__device__ __forceinline__ void fetch(const Ctx& ctx, Regs<U>& R, int kind, int idx, float imm,
+                                      V (&v)[U]) {
   if (kind == TS_PW_TENSOR) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) fetch_tensor(P, idx, it[u], v[u]);
+    for (int u = 0; u < U; ++u) ctx.tensor(idx, u, v[u]);
   } else if (kind == TS_PW_IMM) {
     const __half2 x = __float2half2_rn(imm);
 #pragma unroll
@@ -194,33 +290,56 @@ __device__ __forceinline__ float tanh_f(float x) {
 }
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(exp_f(x)); }
 
-template <int U>
-__device__ __forceinline__ void store_full(const Params& P, __half* out, const Item& it, const V& v) {
-  if (!it.live) return;
-  Vec8h t;
-#pragma unroll
-  for (int j = 0; j < 4; ++j) t.h2[j] = v[j];
-  if (P.ragged) {
-    const uint32_t col = it.s * kStickHalfs + it.lv * 8;
-#pragma unroll
-    for (int e = 0; e < 8; ++e)
-      if (col + e >= P.cols) t.h[e] = __float2half(0.f);
+// Unary ops evaluated in fp32.  `op` is a literal at every call site.
+__host__ __device__ constexpr bool is_unary_f32(int op) {
+  return op == TS_PW_EXP || op == TS_PW_LOG || op == TS_PW_SQRT || op == TS_PW_RSQRT ||
+         op == TS_PW_RECIP || op == TS_PW_SIGMOID || op == TS_PW_TANH || op == TS_PW_SILU ||
+         op == TS_PW_GELU || op == TS_PW_GELU_TANH || op == TS_PW_SIN || op == TS_PW_COS ||
+         op == TS_PW_ERF || op == TS_PW_SIGN || op == TS_PW_LOG1P || op == TS_PW_EXPM1 ||
+         op == TS_PW_SOFTPLUS || op == TS_PW_MISH;
+}
+__device__ __forceinline__ float unary_f32(int op, float x) {
+  switch (op) {
+    case TS_PW_EXP: return exp_f(x);
+    case TS_PW_LOG: return __logf(x);
+    case TS_PW_SQRT: return sqrtf(x);
+    case TS_PW_RSQRT: return rsqrtf(x);
+    case TS_PW_RECIP: return 1.f / x;
+    case TS_PW_SIGMOID: return sigmoid_f(x);
+    case TS_PW_TANH: return tanh_f(x);
+    case TS_PW_SILU: return x * sigmoid_f(x);
+    case TS_PW_GELU: return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
+    case TS_PW_GELU_TANH: {
+      const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+      return 0.5f * x * (1.f + tanh_f(inner));
+    }
+    case TS_PW_SIN: return sinf(x);
+    case TS_PW_COS: return cosf(x);
+    case TS_PW_ERF: return erff(x);
+    case TS_PW_SIGN: return x > 0.f ? 1.f : (x < 0.f ? -1.f : x);
+    case TS_PW_LOG1P: return log1pf(x);
+    case TS_PW_EXPM1: return expm1f(x);
+    case TS_PW_SOFTPLUS: return softplus_f(x);
+    case TS_PW_MISH: return x * tanh_f(softplus_f(x));
+    default: return x;
   }
-  st_global_v4(out + it.flat_off, t.u);
 }
 
 // One instruction on U items.  With a compile-time `code` everything but the
 // selected case disappears.
-template <int U>
-__device__ __forceinline__ void exec_insn(const Params& P, Regs<U>& R, const Item (&it)[U],
-                                          uint32_t code, float imm_a, float imm_b) {
+#define TSB_PW_F32_CASE(OPC) \
+  case OPC: map_f32<U>(acc, [](float x) { return unary_f32(OPC, x); }); break;
+
+template <int U, class Ctx>
+__device__ __forceinline__ void exec_insn(const Params& P, Regs<U>& R, const Ctx& ctx, uint32_t code,
+                                          float imm_a, float imm_b) {
   const int op = code_op(code);
   const __half2 zero2 = __float2half2_rn(0.f);
   V(&acc)[U] = R.acc;
   V(&opa)[U] = R.opa;
   if (op != TS_PW_SAVE && op != TS_PW_STORE)
-    fetch<U>(P, R, code_ak(code), code_ai(code), imm_a, it, R.opa);
-  if (op == TS_PW_WHERE) fetch<U>(P, R, code_bk(code), code_bi(code), imm_b, it, R.opb);
+    fetch<U>(ctx, R, code_ak(code), code_ai(code), imm_a, R.opa);
+  if (op == TS_PW_WHERE) fetch<U>(ctx, R, code_bk(code), code_bi(code), imm_b, R.opb);
   switch (op) {
     case TS_PW_LOAD: copy_v<U>(acc, opa); break;
     case TS_PW_SAVE:
@@ -233,7 +352,7 @@ __device__ __forceinline__ void exec_insn(const Params& P, Regs<U>& R, const Ite
       break;
     case TS_PW_STORE:
 #pragma unroll
-      for (int u = 0; u < U; ++u) store_full<U>(P, P.out[code_ai(code)], it[u], acc[u]);
+      for (int u = 0; u < U; ++u) ctx.store(code_ai(code), u, acc[u]);
       break;
     case TS_PW_ADD: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hadd2(x, y); }); break;
     case TS_PW_SUB: zip_h2<U>(acc, opa, [](__half2 x, __half2 y) { return __hsub2(x, y); }); break;
@@ -264,51 +383,32 @@ __device__ __forceinline__ void exec_insn(const Params& P, Regs<U>& R, const Ite
       break;
     case TS_PW_NEG: map_h2<U>(acc, [](__half2 x) { return __hneg2(x); }); break;
     case TS_PW_ABS: map_h2<U>(acc, [](__half2 x) { return __habs2(x); }); break;
-    case TS_PW_EXP: map_f32<U>(acc, [](float x) { return exp_f(x); }); break;
-    case TS_PW_LOG: map_f32<U>(acc, [](float x) { return __logf(x); }); break;
-    case TS_PW_SQRT: map_f32<U>(acc, [](float x) { return sqrtf(x); }); break;
-    case TS_PW_RSQRT: map_f32<U>(acc, [](float x) { return rsqrtf(x); }); break;
-    case TS_PW_RECIP: map_f32<U>(acc, [](float x) { return 1.f / x; }); break;
-    case TS_PW_SIGMOID: map_f32<U>(acc, [](float x) { return sigmoid_f(x); }); break;
-    case TS_PW_TANH: map_f32<U>(acc, [](float x) { return tanh_f(x); }); break;
     case TS_PW_RELU: map_h2<U>(acc, [zero2](__half2 x) { return __hmax2_nan(x, zero2); }); break;
-    case TS_PW_SILU: map_f32<U>(acc, [](float x) { return x * sigmoid_f(x); }); break;
-    case TS_PW_GELU:
-      map_f32<U>(acc, [](float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); });
-      break;
-    case TS_PW_GELU_TANH:
-      map_f32<U>(acc, [](float x) {
-        const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-        return 0.5f * x * (1.f + tanh_f(inner));
-      });
-      break;
     case TS_PW_SQUARE: map_h2<U>(acc, [](__half2 x) { return __hmul2(x, x); }); break;
     case TS_PW_LOGICAL_NOT: map_h2<U>(acc, [zero2](__half2 x) { return __heq2(x, zero2); }); break;
-    case TS_PW_SIN: map_f32<U>(acc, [](float x) { return sinf(x); }); break;
-    case TS_PW_COS: map_f32<U>(acc, [](float x) { return cosf(x); }); break;
-    case TS_PW_ERF: map_f32<U>(acc, [](float x) { return erff(x); }); break;
     case TS_PW_FLOOR: map_h2<U>(acc, [](__half2 x) { return h2floor(x); }); break;
     case TS_PW_CEIL: map_h2<U>(acc, [](__half2 x) { return h2ceil(x); }); break;
-    case TS_PW_SIGN: map_f32<U>(acc, [](float x) { return x > 0.f ? 1.f : (x < 0.f ? -1.f : x); }); break;
-    case TS_PW_LOG1P: map_f32<U>(acc, [](float x) { return log1pf(x); }); break;
-    case TS_PW_EXPM1: map_f32<U>(acc, [](float x) { return expm1f(x); }); break;
-    case TS_PW_SOFTPLUS: map_f32<U>(acc, [](float x) { return softplus_f(x); }); break;
-    case TS_PW_MISH: map_f32<U>(acc, [](float x) { return x * tanh_f(softplus_f(x)); }); break;
+    TSB_PW_F32_CASE(TS_PW_EXP) TSB_PW_F32_CASE(TS_PW_LOG) TSB_PW_F32_CASE(TS_PW_SQRT)
+    TSB_PW_F32_CASE(TS_PW_RSQRT) TSB_PW_F32_CASE(TS_PW_RECIP) TSB_PW_F32_CASE(TS_PW_SIGMOID)
+    TSB_PW_F32_CASE(TS_PW_TANH) TSB_PW_F32_CASE(TS_PW_SILU) TSB_PW_F32_CASE(TS_PW_GELU)
+    TSB_PW_F32_CASE(TS_PW_GELU_TANH) TSB_PW_F32_CASE(TS_PW_SIN) TSB_PW_F32_CASE(TS_PW_COS)
+    TSB_PW_F32_CASE(TS_PW_ERF) TSB_PW_F32_CASE(TS_PW_SIGN) TSB_PW_F32_CASE(TS_PW_LOG1P)
+    TSB_PW_F32_CASE(TS_PW_EXPM1) TSB_PW_F32_CASE(TS_PW_SOFTPLUS) TSB_PW_F32_CASE(TS_PW_MISH)
     default: break;
   }
 }
+#undef TSB_PW_F32_CASE
 
-template <class Prog, int U, int I>
-__device__ __forceinline__ void run_fixed(const Params& P, Regs<U>& R, const Item (&it)[U]) {
-  if constexpr (I < Prog::n) {
-    exec_insn<U>(P, R, it, Prog::template at<I>(), P.imm_a[I], P.imm_b[I]);
-    run_fixed<Prog, U, I + 1>(P, R, it);
+template <class Prog, int U, int I, int END, class Ctx>
+__device__ __forceinline__ void run_fixed(const Params& P, Regs<U>& R, const Ctx& ctx) {
+  if constexpr (I < END) {
+    exec_insn<U>(P, R, ctx, Prog::template at<I>(), P.imm_a[I], P.imm_b[I]);
+    run_fixed<Prog, U, I + 1, END>(P, R, ctx);
   }
 }
 
-// Runs the whole program on U items; the result is left in R.acc.
-template <class Prog, int U>
-__device__ __forceinline__ void run_program(const Params& P, Regs<U>& R, const Item (&it)[U]) {
+template <int U>
+__device__ __forceinline__ void clear_regs(Regs<U>& R) {
   const __half2 zero2 = __float2half2_rn(0.f);
 #pragma unroll
   for (int u = 0; u < U; ++u) {
@@ -320,10 +420,16 @@ __device__ __forceinline__ void run_program(const Params& P, Regs<U>& R, const I
     set_all(R.s2[u], zero2);
     set_all(R.s3[u], zero2);
   }
+}
+
+// Runs instructions [0, END) (all of them when END < 0); the result is left in R.acc.
+template <class Prog, int U, int END = -1, class Ctx>
+__device__ __forceinline__ void run_program(const Params& P, Regs<U>& R, const Ctx& ctx) {
+  clear_regs<U>(R);
   if constexpr (Prog::kStatic) {
-    run_fixed<Prog, U, 0>(P, R, it);
+    run_fixed<Prog, U, 0, (END < 0 ? Prog::n : END)>(P, R, ctx);
   } else {
-    for (int pc = 0; pc < P.n_insns; ++pc) exec_insn<U>(P, R, it, P.code[pc], P.imm_a[pc], P.imm_b[pc]);
+    for (int pc = 0; pc < P.n_insns; ++pc) exec_insn<U>(P, R, ctx, P.code[pc], P.imm_a[pc], P.imm_b[pc]);
   }
 }
 
@@ -337,21 +443,22 @@ __device__ __forceinline__ void split_row(const Params& P, Item& it) {
 // ---- no reduction: items are the 16-byte vectors of the output image ----------
 template <class Prog, int U>
 __global__ void __launch_bounds__(kThreads) flat_kernel(const __grid_constant__ Params P) {
-  Item it[U];
+  ItemCtx<U> ctx(P);
 #pragma unroll
   for (int u = 0; u < U; ++u) {
+    Item& it = ctx.it[u];
     const uint32_t stick = blockIdx.x * (32 * U) + u * 32 + (threadIdx.x >> 3);
-    it[u].lv = threadIdx.x & 7;
-    it[u].live = stick < P.total_sticks;
-    it[u].flat_off = (int64_t)stick * kStickHalfs + it[u].lv * 8;
-    it[u].s = it[u].r = it[u].i0 = it[u].i1 = it[u].i2 = 0;
+    it.lv = threadIdx.x & 7;
+    it.live = stick < P.total_sticks;
+    it.flat_off = (int64_t)stick * kStickHalfs + it.lv * 8;
+    it.s = it.r = it.i0 = it.i1 = it.i2 = 0;
     if (P.need_index || P.ragged) {
-      P.div_rows.divmod(stick, it[u].s, it[u].r);
-      if (P.need_index) split_row(P, it[u]);
+      P.div_rows.divmod(stick, it.s, it.r);
+      if (P.need_index) split_row(P, it);
     }
   }
   Regs<U> R;
-  run_program<Prog, U>(P, R, it);
+  run_program<Prog, U>(P, R, ctx);
 }
 
 template <int RED>
@@ -365,59 +472,11 @@ __device__ __forceinline__ float red_combine(float a, float b) {
   return (b != b) ? b : ((a != a) ? a : r);  // NaN propagates, as torch.max / torch.min do
 }
 
-// ---- reduction along the stick dim ----------------------------------------------
-// A warp covers 4 adjacent rows x 8 vector lanes (512 contiguous bytes per stick
-// column).  2^ws_log warps share a row group and split its stick columns.
-template <class Prog, int RED, int U>
-__global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant__ Params P) {
-  __shared__ float part[8][4];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ws = 1 << P.ws_log;
-  const int ws_idx = warp & (ws - 1);
-  const uint32_t group = blockIdx.x * (8 >> P.ws_log) + (warp >> P.ws_log);
-  const uint32_t row = group * 4 + (lane >> 3);
-  const bool row_live = row < P.rows;
-  Item it[U];
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    it[u].r = row;
-    it[u].lv = lane & 7;
-    it[u].i0 = it[u].i1 = it[u].i2 = 0;
-    if (P.need_index && row_live) split_row(P, it[u]);
-  }
-  float partial = red_identity<RED>();
-  Regs<U> R;
-  for (uint32_t s0 = ws_idx; s0 < P.nsticks; s0 += ws * U) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const uint32_t s = s0 + u * ws;
-      it[u].s = s;
-      it[u].live = row_live && s < P.nsticks;
-      it[u].flat_off = ((int64_t)s * P.rows + row) * kStickHalfs + it[u].lv * 8;
-    }
-    run_program<Prog, U>(P, R, it);
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (!it[u].live) continue;
-      const uint32_t col = it[u].s * kStickHalfs + it[u].lv * 8;
-      if (!P.ragged || col + 8 <= P.cols) {
-        float t = red_identity<RED>();
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 x = __half22float2(R.acc[u][j]);
-          t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
-        }
-        partial = red_combine<RED>(partial, t);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 x = __half22float2(R.acc[u][j]);
-          if (col + 2 * j < P.cols) partial = red_combine<RED>(partial, x.x);
-          if (col + 2 * j + 1 < P.cols) partial = red_combine<RED>(partial, x.y);
-        }
-      }
-    }
-  }
+// Cross-lane / cross-warp part of a row reduction and the write of the result.
+template <int RED>
+__device__ __forceinline__ void finish_row(const Params& P, float partial, uint32_t row,
+                                           bool row_live, int lane, int warp, int ws, int ws_idx,
+                                           float (*part)[4]) {
 #pragma unroll
   for (int o = 1; o < 8; o <<= 1)
     partial = red_combine<RED>(partial, __shfl_xor_sync(0xffffffffu, partial, o));
@@ -443,6 +502,104 @@ __global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant_
   }
 }
 
+// ---- reduction along the stick dim ----------------------------------------------
+// A warp covers 4 adjacent rows x 8 vector lanes (512 contiguous bytes per stick
+// column).  2^ws_log warps share a row group and split its stick columns.
+//
+// Interpreter form: items carry full coordinates, every flag is read at run time.
+template <int RED, int U>
+__global__ void __launch_bounds__(kThreads) rowred_dyn_kernel(const __grid_constant__ Params P) {
+  __shared__ float part[8][4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ws = 1 << P.ws_log;
+  const int ws_idx = warp & (ws - 1);
+  const uint32_t group = blockIdx.x * (8 >> P.ws_log) + (warp >> P.ws_log);
+  const uint32_t row = group * 4 + (lane >> 3);
+  const bool row_live = row < P.rows;
+  ItemCtx<U> ctx(P);
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    Item& it = ctx.it[u];
+    it.r = row;
+    it.lv = lane & 7;
+    it.i0 = it.i1 = it.i2 = 0;
+    if (P.need_index && row_live) split_row(P, it);
+  }
+  float partial = red_identity<RED>();
+  Regs<U> R;
+  for (uint32_t s0 = ws_idx; s0 < P.nsticks; s0 += ws * U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      Item& it = ctx.it[u];
+      const uint32_t s = s0 + u * ws;
+      it.s = s;
+      it.live = row_live && s < P.nsticks;
+      it.flat_off = ((int64_t)s * P.rows + row) * kStickHalfs + it.lv * 8;
+    }
+    run_program<Dyn, U>(P, R, ctx);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!ctx.it[u].live) continue;
+      const uint32_t col = ctx.it[u].s * kStickHalfs + ctx.it[u].lv * 8;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 x = __half22float2(R.acc[u][j]);
+        if (!P.ragged || col + 2 * j < P.cols) partial = red_combine<RED>(partial, x.x);
+        if (!P.ragged || col + 2 * j + 1 < P.cols) partial = red_combine<RED>(partial, x.y);
+      }
+    }
+  }
+  finish_row<RED>(P, partial, row, row_live, lane, warp, ws, ws_idx, part);
+}
+
+// Compile-time program.  When the program ends in a unary op evaluated in fp32, that
+// op's fp32 results feed the reduction directly, skipping the fp16 round trip (the
+// reduction accumulates in fp32 either way).
+template <class Prog, int RED, int U, bool FULL>
+__global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant__ Params P) {
+  __shared__ float part[8][4];
+  constexpr int kLastOp = code_op(Prog::template at<Prog::n - 1>());
+  constexpr bool kFuseTail = is_unary_f32(kLastOp);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int ws = 1 << P.ws_log;
+  const int ws_idx = warp & (ws - 1);
+  const uint32_t group = blockIdx.x * (8 >> P.ws_log) + (warp >> P.ws_log);
+  const uint32_t row = group * 4 + (lane >> 3);
+  const bool row_live = FULL || row < P.rows;
+  RowCtx<U, FULL> ctx(P, row, lane & 7, row_live);
+  float partial = red_identity<RED>();
+  Regs<U> R;
+  for (uint32_t s0 = ws_idx; s0 < P.nsticks; s0 += ws * U) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      ctx.s[u] = s0 + u * ws;
+      ctx.live[u] = FULL || (row_live && ctx.s[u] < P.nsticks);
+    }
+    run_program<Prog, U, (kFuseTail ? Prog::n - 1 : Prog::n)>(P, R, ctx);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (!FULL && !ctx.live[u]) continue;
+      const uint32_t col = ctx.s[u] * kStickHalfs + ctx.lv * 8;
+      float t = red_identity<RED>();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 x = __half22float2(R.acc[u][j]);
+        if (kFuseTail) {
+          x.x = unary_f32(kLastOp, x.x);
+          x.y = unary_f32(kLastOp, x.y);
+        }
+        if (!FULL && P.ragged) {
+          if (col + 2 * j >= P.cols) x.x = red_identity<RED>();
+          if (col + 2 * j + 1 >= P.cols) x.y = red_identity<RED>();
+        }
+        t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
+      }
+      partial = red_combine<RED>(partial, t);
+    }
+  }
+  finish_row<RED>(P, partial, row, row_live, lane, warp, ws, ws_idx, part);
+}
+
 // ---- registry of pre-instantiated programs ----------------------------------------
 using LaunchFn = void (*)(const Params&, uint32_t blocks, cudaStream_t);
 
@@ -455,10 +612,22 @@ struct StaticEntry {
 };
 void register_static(const StaticEntry& e);  // pointwise.cu
 
+// Whether the row kernels may drop every predicate for this launch.
+inline bool rows_full(const Params& P, int U) {
+  const uint32_t ws = 1u << P.ws_log;
+  return P.cols % 64 == 0 && P.nsticks % (ws * U) == 0 && P.rows % (4 * (8 >> P.ws_log)) == 0;
+}
+
 template <class Prog, int RED, int U>
 void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
-  if constexpr (RED == TS_RED_NONE) flat_kernel<Prog, U><<<blocks, kThreads, 0, st>>>(P);
-  else rowred_kernel<Prog, RED, U><<<blocks, kThreads, 0, st>>>(P);
+  if constexpr (RED == TS_RED_NONE) {
+    flat_kernel<Prog, U><<<blocks, kThreads, 0, st>>>(P);
+  } else if constexpr (!Prog::kStatic) {
+    rowred_dyn_kernel<RED, U><<<blocks, kThreads, 0, st>>>(P);
+  } else {
+    if (rows_full(P, U)) rowred_kernel<Prog, RED, U, true><<<blocks, kThreads, 0, st>>>(P);
+    else rowred_kernel<Prog, RED, U, false><<<blocks, kThreads, 0, st>>>(P);
+  }
 }
 
 template <int RED, int U, uint32_t... C>
