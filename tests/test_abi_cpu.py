@@ -8,7 +8,8 @@ import re
 import pytest
 import torch
 
-from torch_spyre import SpyreTensorLayout, _abi, storage_nbytes
+from torch_spyre import _abi, storage_nbytes
+from torch_spyre.layout import SpyreTensorLayout
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 GOLD = os.path.join(os.path.dirname(__file__), "golden")

@@ -7,7 +7,8 @@ import torch
 
 from oracle import layout as L
 from oracle import relayout_c as C
-from torch_spyre import SpyreTensorLayout, _abi, stick_ops as K
+from torch_spyre import _abi, stick_ops as K
+from torch_spyre.layout import SpyreTensorLayout
 
 pytestmark = pytest.mark.gpu
 GOLD = os.path.join(os.path.dirname(__file__), "golden")

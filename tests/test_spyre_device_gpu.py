@@ -1,0 +1,180 @@
+"""GPU tests through the `spyre` device string: the assertions of the reference's own
+tests/test_spyre.py, tests/test_ops.py and tests/test_modules.py, against torch CPU eager
+(bit-exact for copies, rtol 1e-2 / atol 1e-3 for math)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+import torch_spyre  # noqa: F401
+from oracle.math_ref import assert_close
+
+pytestmark = pytest.mark.gpu
+DEV = "spyre"
+
+
+@pytest.fixture(autouse=True)
+def _need_gpu(cuda):
+    yield
+
+
+def test_empty_fill_and_ones():
+    a = torch.empty(50, device=DEV, dtype=torch.float16)
+    assert a.device.type == "spyre"
+    a.fill_(3.5)
+    assert a.cpu().eq(3.5).all()
+    b = torch.ones(50, device=DEV, dtype=torch.float16)
+    assert b.cpu().eq(1).all()
+    assert torch.zeros(3, 70, device=DEV, dtype=torch.float16).cpu().eq(0).all()
+
+
+def test_repr_and_str():
+    # tests/test_spyre.py:63-95 of the reference
+    t = torch.tensor([1, 2], dtype=torch.float16, device=DEV)
+    assert repr(t) == "tensor([1., 2.], dtype=torch.float16, device='spyre:0')"
+    assert str(t) == "tensor([1., 2.], dtype=torch.float16, device='spyre:0')"
+
+
+def test_scalar_becomes_one_dim():
+    # tests/test_spyre.py:108-114 of the reference
+    x = torch.tensor(5, dtype=torch.float16)
+    y = x.to(DEV)
+    assert list(y.shape) == [1]
+    back = y.cpu()
+    assert list(back.shape) == [1] and back.item() == 5
+
+
+def test_storage_is_whole_sticks():
+    # tests/test_spyre.py:171-176 of the reference
+    y = torch.tensor([1, 2], dtype=torch.float16).to(DEV)
+    assert y.untyped_storage().nbytes() == 128
+    assert torch.empty(3, 70, dtype=torch.float16, device=DEV).untyped_storage().nbytes() == 2 * 3 * 128
+
+
+@pytest.mark.parametrize("shape", [(3,), (256,), (3, 3), (256, 128), (3, 3, 3), (256, 128, 64),
+                                   (3, 3, 3, 3), (2, 6, 3, 128), (5, 70), (2, 3, 65)])
+def test_copy_round_trip(shape):
+    # tests/test_ops.py:56-97 of the reference
+    bits = torch.randint(-32768, 32768, shape, dtype=torch.int16,
+                         generator=torch.Generator().manual_seed(1))
+    x = bits.view(torch.float16)
+    y = x.to(DEV)
+    assert y.shape == x.shape and y.dtype == x.dtype
+    assert torch.equal(y.cpu().view(torch.int16), bits)
+    # a permuted host tensor and a non-contiguous destination
+    if len(shape) >= 2:
+        xt = x.transpose(0, -1)
+        assert torch.equal(xt.to(DEV).cpu().view(torch.int16), xt.view(torch.int16))
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.int8, torch.int32, torch.uint8])
+def test_dtype_round_trips(dtype):
+    # tests/test_spyre.py:121-155 of the reference (bits only: no conversion on the way)
+    x = (torch.randn(64, 64, generator=torch.Generator().manual_seed(2)) * 50).to(dtype)
+    assert torch.equal(x.to(DEV).cpu(), x)
+
+
+def test_dtype_converting_copy_is_refused():
+    x = torch.zeros(4, 64, dtype=torch.float16, device=DEV)
+    with pytest.raises(RuntimeError, match="type conversion"):
+        x.copy_(torch.zeros(4, 64, dtype=torch.float32))
+
+
+def test_views_and_device_copies():
+    x = torch.randn(6, 200, generator=torch.Generator().manual_seed(3)).half()
+    y = x.to(DEV)
+    assert torch.equal(y.t().cpu(), x.t())
+    assert torch.equal(y[1:4, 8:136].cpu(), x[1:4, 8:136])
+    assert torch.equal(y.view(3, 2, 200).cpu(), x.view(3, 2, 200))
+    assert torch.equal(y.view(6, 4, 50).cpu(), x.view(6, 4, 50))
+    assert torch.equal(y.unsqueeze(1).expand(6, 3, 200).cpu(), x.unsqueeze(1).expand(6, 3, 200))
+    assert torch.equal(y.clone().cpu(), x)
+    assert torch.equal(y.t().contiguous().cpu(), x.t().contiguous())
+    z = torch.zeros(6, 200, dtype=torch.float16, device=DEV)
+    z[:, 10:20] = y[:, 30:40]
+    ref = torch.zeros(6, 200, dtype=torch.float16)
+    ref[:, 10:20] = x[:, 30:40]
+    assert torch.equal(z.cpu(), ref)
+    assert y[2, 5].item() == x[2, 5].item()
+
+
+def test_eager_pointwise():
+    # tests/test_ops.py:136-263 and tests/test_spyre.py:116-119 of the reference
+    g = torch.Generator().manual_seed(4)
+    x = torch.rand(67, 256, generator=g).half() + 0.1
+    y = torch.rand(67, 256, generator=g).half() + 0.1
+    xs, ys = x.to(DEV), y.to(DEV)
+    for fn in (torch.abs, torch.relu, torch.exp, torch.log, torch.reciprocal, torch.sigmoid,
+               torch.sqrt, torch.tanh, torch.rsqrt, torch.neg, F.silu, F.gelu):
+        assert_close(fn(xs).cpu(), fn(x))
+    for fn in (torch.add, torch.sub, torch.mul, torch.div, torch.maximum):
+        assert_close(fn(xs, ys).cpu(), fn(x, y))
+    assert_close(xs.add(2).cpu(), x.add(2))
+    assert_close((xs * 0.5 - 1).cpu(), x * 0.5 - 1)
+    assert_close((2 - xs).cpu(), 2 - x)
+    assert_close((1 / xs).cpu(), 1 / x)
+    assert_close(torch.add(xs, ys, alpha=2).cpu(), torch.add(x, y, alpha=2))
+    assert torch.equal(torch.eq(xs, xs).cpu().bool(), torch.eq(x, x))
+    assert torch.equal(torch.ge(xs, ys).cpu().bool(), torch.ge(x, y))
+    assert_close(torch.where(torch.ge(xs, ys), xs, ys).cpu(), torch.where(x >= y, x, y))
+    # broadcast add (tests/_inductor/test_inductor_ops.py:121-134 of the reference)
+    v = torch.rand(256, generator=g).half()
+    assert_close((xs + v.to(DEV)).cpu(), x + v)
+    # in place and out=
+    zs = xs.clone()
+    zs.mul_(ys)
+    zs += 1
+    assert_close(zs.cpu(), x * y + 1)
+    # alias operands
+    assert_close((xs * xs * xs).cpu(), x * x * x)
+
+
+def test_eager_reductions_softmax_norm():
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(67, 256, generator=g).half()
+    xs = x.to(DEV)
+    assert_close(xs.sum(0).cpu(), x.sum(0), atol=2e-2)
+    assert_close(xs.sum(1).cpu(), x.sum(1), atol=2e-2)
+    assert_close(xs.sum(1, keepdim=True).cpu(), x.sum(1, keepdim=True), atol=2e-2)
+    assert_close(xs.mean(1).cpu(), x.mean(1))
+    assert_close(xs.mean().cpu().reshape(()), x.mean(), atol=2e-3)
+    assert_close(xs.amax(1).cpu(), x.amax(1))
+    assert_close(xs.amax(0).cpu(), x.amax(0))
+    assert_close((xs - xs.amax(1, keepdim=True)).cpu(), x - x.amax(1, keepdim=True))
+    for dim in (0, 1, -1):
+        assert_close(torch.softmax(xs, dim).cpu(), torch.softmax(x, dim))
+    assert_close(F.log_softmax(xs, -1).cpu(), F.log_softmax(x, -1))
+    w, b = torch.randn(256, generator=g).half(), torch.randn(256, generator=g).half()
+    assert_close(F.layer_norm(xs, (256,), w.to(DEV), b.to(DEV)).cpu(), F.layer_norm(x, (256,), w, b))
+    # tests/test_modules.py:57-67 of the reference
+    x2 = torch.randn(1024, 256, generator=g).half()
+    assert_close(torch.nn.Softmax(dim=1)(x2.to(DEV)).cpu(), torch.nn.Softmax(dim=1)(x2))
+
+
+def test_eager_matmul_and_linear():
+    g = torch.Generator().manual_seed(6)
+    a, b = torch.randn(67, 256, generator=g).half(), (torch.randn(256, 128, generator=g) * 0.05).half()
+    assert_close(torch.mm(a.to(DEV), b.to(DEV)).cpu(), a @ b)
+    assert_close((a.to(DEV) @ b.to(DEV)).cpu(), a @ b)
+    a3, b3 = torch.randn(3, 5, generator=g).half(), torch.randn(5, 7, generator=g).half()
+    assert_close(torch.mm(a3.to(DEV), b3.to(DEV)).cpu(), a3 @ b3)       # tests/test_ops.py:265-275
+    ab, bb = torch.randn(4, 33, 96, generator=g).half(), (torch.randn(4, 96, 70, generator=g) * 0.1).half()
+    assert_close(torch.bmm(ab.to(DEV), bb.to(DEV)).cpu(), torch.bmm(ab, bb))
+    lin = torch.nn.Linear(256, 192).half()
+    ref = lin(a)
+    assert_close(lin.to(DEV)(a.to(DEV)).cpu(), ref)                       # tests/test_modules.py:69-87
+    bias = torch.randn(128, generator=g).half()
+    assert_close(torch.addmm(bias.to(DEV), a.to(DEV), b.to(DEV)).cpu(), torch.addmm(bias, a, b))
+    assert_close(torch.addmm(bias.to(DEV), a.to(DEV), b.to(DEV), beta=0.5, alpha=2).cpu(),
+                 torch.addmm(bias, a, b, beta=0.5, alpha=2))
+    # attention block of tests/_inductor/test_building_blocks.py:67-89, run eagerly
+    q, k, v = (torch.randn(256, 128, generator=g).half() for _ in range(3))
+    qs, ks, vs = q.to(DEV), k.to(DEV), v.to(DEV)
+    got = torch.softmax((qs @ ks.t()) * (128 ** -0.5), -1) @ vs
+    assert_close(got.cpu(), torch.softmax((q @ k.t()) * (128 ** -0.5), -1) @ v)
+
+
+def test_device_module_on_gpu():
+    assert torch.spyre.is_available()
+    assert torch.spyre.device_count() >= 1
+    assert torch.spyre.current_device() == 0
+    torch.spyre.synchronize()

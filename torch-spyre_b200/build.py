@@ -65,5 +65,37 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
     return LIB_PATH
 
 
+EXT_SRC = os.path.join(CSRC, "ext")
+EXT_BUILD = os.path.join(HERE, "build", "ext")
+EXT_PATH = os.path.join(HERE, "torch_spyre", "_C.so")
+
+
+def build_extension(force: bool = False) -> str:
+    """Builds torch_spyre/_C.so: the `spyre` (PrivateUse1) device glue and pybind module.
+    It links against libspyre_b200.so (rpath $ORIGIN/lib) and PyTorch's CUDA libraries."""
+    import shutil
+
+    from torch.utils import cpp_extension
+
+    build_library()
+    sources = sorted(os.path.join(EXT_SRC, f) for f in os.listdir(EXT_SRC) if f.endswith(".cpp"))
+    deps = sources + [os.path.join(EXT_SRC, f) for f in os.listdir(EXT_SRC) if f.endswith(".h")]
+    deps.append(os.path.join(INCLUDE, "spyre_b200.h"))
+    if not force and os.path.exists(EXT_PATH) and not _newer(sources[0], EXT_PATH, deps):
+        return EXT_PATH
+    os.makedirs(EXT_BUILD, exist_ok=True)
+    cpp_extension.load(
+        name="_C", sources=sources, build_directory=EXT_BUILD, is_python_module=False,
+        with_cuda=True, verbose=False,
+        extra_cflags=["-O2", "-std=c++17", "-DTORCH_EXTENSION_NAME=_C"],
+        extra_ldflags=[f"-L{LIB_DIR}", "-lspyre_b200", "-Wl,-rpath,\\$$ORIGIN/lib", "-Wl,-rpath,\\$$ORIGIN/../../torch_spyre/lib"],
+        extra_include_paths=[INCLUDE])
+    shutil.copyfile(os.path.join(EXT_BUILD, "_C.so"), EXT_PATH)
+    return EXT_PATH
+
+
 if __name__ == "__main__":
+    if "--ext" in sys.argv:
+        print(build_extension(force="--force" in sys.argv))
+        sys.exit(0)
     print(build_library(force="--force" in sys.argv, verbose_ptxas="--verbose-ptxas" in sys.argv))

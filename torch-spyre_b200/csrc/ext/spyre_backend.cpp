@@ -6,6 +6,7 @@
 // flex runtime replaced by CUDA: `spyre:N` is CUDA device N, streams and events are
 // the CUDA ones PyTorch manages.
 #include <ATen/cuda/CUDAContext.h>
+#include <ATen/detail/CUDAHooksInterface.h>
 #include <ATen/detail/PrivateUse1HooksInterface.h>
 #include <c10/core/impl/DeviceGuardImplInterface.h>
 #include <c10/cuda/CUDACachingAllocator.h>
@@ -165,6 +166,13 @@ struct SpyreHooks final : at::PrivateUse1HooksInterface {
   bool isBuilt() const override { return true; }
   bool isAvailable() const override { return c10::cuda::device_count() > 0; }
   bool hasPrimaryContext(c10::DeviceIndex) const override { return true; }
+  // pinned host memory is CUDA's
+  at::Allocator* getPinnedMemoryAllocator() const override {
+    return at::detail::getCUDAHooks().getPinnedMemoryAllocator();
+  }
+  bool isPinnedPtr(const void* data) const override {
+    return at::detail::getCUDAHooks().isPinnedPtr(data);
+  }
   at::Device getDeviceFromPtr(void* data) const override {
     cudaPointerAttributes attr{};
     C10_CUDA_CHECK(cudaPointerGetAttributes(&attr, data));

@@ -1,0 +1,441 @@
+"""aten kernels for ``spyre`` tensors, registered on the PrivateUse1 dispatch key.
+
+The reference generates one C++ wrapper per op from codegen/inputs/Metadata.yaml
+(codegen/templates/base.jinja2:16-241) and hand-writes mm / bmm / addmm / mean /
+fill_ / clone (codegen/inputs/spyre_torch_ops.cpp:214-601); each wrapper builds a
+sendnn graph and runs it.  Here each op marshals its arguments and calls one entry
+point of the kernel library.  Results follow torch CPU eager semantics; where the
+reference's wrappers deviate from them (addmm ignoring beta, mean dividing per dim,
+layer norm returning its input) the CPU semantics win.
+
+fp16 is the compute dtype of the device.  Comparison ops return fp16 0/1 tensors, as
+the reference's do (tests/test_ops.py:141-152 cast them with .bool()).
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from . import _C, stick_ops as K
+from .stick_ops import Chain, StickTensor
+
+_lib = torch.library.Library("aten", "IMPL")
+_KEY = "PrivateUse1"
+_registered: List[str] = []
+
+
+def _impl(name: str):
+    def deco(fn):
+        _lib.impl(name, fn, _KEY)
+        _registered.append(name)
+        return fn
+
+    return deco
+
+
+def registered_ops() -> List[str]:
+    return list(_registered)
+
+
+def _check_fp16(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if t.dtype != torch.float16:
+            raise NotImplementedError(
+                f"spyre kernels compute in float16; got {t.dtype} (convert on the host first)")
+
+
+def _canonical(t: torch.Tensor) -> torch.Tensor:
+    """The tensor itself if its storage is its own stick image, else a fresh copy that is."""
+    if _C.is_canonical(t):
+        return t
+    out = torch.empty(t.shape, dtype=t.dtype, device=t.device)
+    out.copy_(t)
+    return out
+
+
+def _st(t: torch.Tensor) -> StickTensor:
+    t = _canonical(t)
+    shape = tuple(t.shape) if t.dim() else (1,)
+    st = StickTensor(_C.storage_as_cuda_bytes(t), shape, t.dtype)
+    st.owner = t  # keeps a temporary copy alive for the launch
+    return st
+
+
+def _new(shape: Sequence[int], like: torch.Tensor) -> torch.Tensor:
+    return torch.empty(tuple(shape), dtype=like.dtype, device=like.device)
+
+
+def _is_number(x) -> bool:
+    return isinstance(x, (int, float, bool)) or (isinstance(x, torch.Tensor) and x.device.type == "cpu"
+                                                 and x.dim() == 0)
+
+
+def _number(x) -> float:
+    return float(x.item()) if isinstance(x, torch.Tensor) else float(x)
+
+
+def _with_device(t: torch.Tensor):
+    return torch.cuda.device(t.device.index if t.device.index is not None else 0)
+
+
+# ---- pointwise -------------------------------------------------------------------------
+
+def _unary(op: str, x: torch.Tensor) -> torch.Tensor:
+    _check_fp16(x)
+    out = _new(x.shape, x)
+    if x.numel() == 0:
+        return out
+    with _with_device(x):
+        c = Chain()
+        c.emit("LOAD", c.tensor(_st(x))).emit(op).store(0)
+        K.run_chain(c, x.shape, outputs=[_st(out)])
+    return out
+
+
+def _operand(c: Chain, x, like: torch.Tensor):
+    if _is_number(x):
+        return c.imm(_number(x))
+    if x.device != like.device:
+        raise RuntimeError(f"expected all tensors on {like.device}, got {x.device}")
+    _check_fp16(x)
+    return c.tensor(_st(x))
+
+
+def _binary(op: str, a, b, rop: Optional[str] = None, alpha=1) -> torch.Tensor:
+    """a <op> (alpha * b); `rop` is the opcode to use when a is the scalar."""
+    if _is_number(a):
+        if rop is None:
+            raise NotImplementedError(f"scalar {op} tensor")
+        a, b, op = b, a, rop
+    _check_fp16(a)
+    shape_b = () if _is_number(b) else tuple(b.shape)
+    shape = torch.broadcast_shapes(tuple(a.shape), shape_b)
+    out = _new(shape, a)
+    if out.numel() == 0:
+        return out
+    with _with_device(a):
+        c = Chain()
+        if alpha != 1 and not _is_number(b):
+            c.emit("LOAD", _operand(c, b, a)).emit("MUL", c.imm(alpha)).save(0)
+            c.emit("LOAD", c.tensor(_st(a))).emit(op, c.saved(0)).store(0)
+        else:
+            rhs = c.imm(_number(b) * alpha) if _is_number(b) else None
+            c.emit("LOAD", c.tensor(_st(a)))
+            c.emit(op, rhs if rhs is not None else _operand(c, b, a)).store(0)
+        K.run_chain(c, shape, outputs=[_st(out)])
+    return out
+
+
+_UNARY_OPS = {
+    "abs": "ABS", "neg": "NEG", "exp": "EXP", "log": "LOG", "sqrt": "SQRT", "rsqrt": "RSQRT",
+    "reciprocal": "RECIP", "sigmoid": "SIGMOID", "tanh": "TANH", "relu": "RELU", "silu": "SILU",
+    "sin": "SIN", "cos": "COS", "erf": "ERF", "floor": "FLOOR", "ceil": "CEIL", "sign": "SIGN",
+    "log1p": "LOG1P", "expm1": "EXPM1", "mish": "MISH", "logical_not": "LOGICAL_NOT",
+}
+
+
+def _copy_into(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    dst.copy_(src)
+    return dst
+
+
+def _register_unary(name: str, opcode: str) -> None:
+    _impl(name)(lambda x: _unary(opcode, x))
+    _impl(name + ".out")(lambda x, *, out: _copy_into(out, _unary(opcode, x)))
+    _impl(name + "_")(lambda x: _copy_into(x, _unary(opcode, x)))
+
+
+for _name, _opcode in _UNARY_OPS.items():
+    _register_unary(_name, _opcode)
+
+
+@_impl("gelu")
+def _gelu(x, *, approximate="none"):
+    return _unary("GELU_TANH" if approximate == "tanh" else "GELU", x)
+
+
+@_impl("softplus")
+def _softplus(x, beta=1, threshold=20):
+    if float(beta) != 1.0 or float(threshold) != 20.0:
+        raise NotImplementedError("softplus with beta != 1 or threshold != 20")
+    return _unary("SOFTPLUS", x)
+
+
+def _register_binary(name: str, opcode: str, rop: Optional[str], with_alpha: bool) -> None:
+    if with_alpha:
+        fn_t = lambda a, b, *, alpha=1: _binary(opcode, a, b, rop, alpha)  # noqa: E731
+    else:
+        fn_t = lambda a, b: _binary(opcode, a, b, rop)  # noqa: E731
+    _impl(name + ".Tensor")(fn_t)
+    _impl(name + ".Scalar")(fn_t)
+    if with_alpha:
+        _impl(name + ".out")(lambda a, b, *, alpha=1, out: _copy_into(out, fn_t(a, b, alpha=alpha)))
+        _impl(name + "_.Tensor")(lambda a, b, *, alpha=1: _copy_into(a, fn_t(a, b, alpha=alpha)))
+        _impl(name + "_.Scalar")(lambda a, b, alpha=1: _copy_into(a, fn_t(a, b, alpha=alpha)))
+    else:
+        _impl(name + ".out")(lambda a, b, *, out: _copy_into(out, fn_t(a, b)))
+        _impl(name + "_.Tensor")(lambda a, b: _copy_into(a, fn_t(a, b)))
+        _impl(name + "_.Scalar")(lambda a, b: _copy_into(a, fn_t(a, b)))
+
+
+_register_binary("add", "ADD", "ADD", True)
+_register_binary("sub", "SUB", "RSUB", True)
+_register_binary("mul", "MUL", "MUL", False)
+_register_binary("div", "DIV", "RDIV", False)
+
+for _name, _opcode in {"eq": "EQ", "ne": "NE", "lt": "LT", "le": "LE", "gt": "GT", "ge": "GE"}.items():
+    _impl(_name + ".Tensor")(lambda a, b, _o=_opcode: _binary(_o, a, b))
+    _impl(_name + ".Scalar")(lambda a, b, _o=_opcode: _binary(_o, a, b))
+
+_impl("maximum")(lambda a, b: _binary("MAX", a, b, "MAX"))
+_impl("minimum")(lambda a, b: _binary("MIN", a, b, "MIN"))
+_impl("pow.Tensor_Scalar")(lambda a, b: _binary("POW", a, b))
+_impl("pow.Tensor_Tensor")(lambda a, b: _binary("POW", a, b))
+_impl("rsub.Scalar")(lambda a, b, alpha=1: _binary("RSUB", a, _number(b)))
+
+
+@_impl("where.self")
+def _where(cond, a, b):
+    _check_fp16(cond)
+    like = cond
+    shape = torch.broadcast_shapes(tuple(cond.shape), () if _is_number(a) else tuple(a.shape),
+                                   () if _is_number(b) else tuple(b.shape))
+    out = _new(shape, like)
+    with _with_device(like):
+        c = Chain()
+        c.emit("LOAD", c.tensor(_st(cond)))
+        c.emit("WHERE", _operand(c, a, like), _operand(c, b, like)).store(0)
+        K.run_chain(c, shape, outputs=[_st(out)])
+    return out
+
+
+@_impl("fill_.Scalar")
+def _fill(x, value):
+    _check_fp16(x)
+    if x.numel() == 0:
+        return x
+    target = x if _C.is_canonical(x) else _new(x.shape, x)
+    with _with_device(x):
+        c = Chain()
+        c.emit("LOAD", c.imm(_number(value))).store(0)
+        K.run_chain(c, target.shape if target.dim() else (1,), outputs=[_st(target)])
+    if target is not x:
+        x.copy_(target)
+    return x
+
+
+@_impl("zero_")
+def _zero(x):
+    return _fill(x, 0.0)
+
+
+@_impl("clone")
+def _clone(x, *, memory_format=None):
+    out = _new(x.shape, x)
+    out.copy_(x)
+    return out
+
+
+# ---- reductions ------------------------------------------------------------------------
+
+def _reduce_one(x: torch.Tensor, dim: int, op: str, keepdim: bool, scale: float = 1.0) -> torch.Tensor:
+    nd = x.dim()
+    dim = dim % nd if nd else 0
+    shape = list(x.shape) if nd else [1]
+    out_shape = shape[:dim] + ([1] if keepdim else []) + shape[dim + 1:]
+    if not out_shape:
+        out_shape = [1]
+    out = _new(out_shape, x)
+    if x.numel() == 0:
+        return out
+    with _with_device(x):
+        sx = _st(x)
+        if dim == len(shape) - 1:
+            c = Chain()
+            c.emit("LOAD", c.tensor(sx))
+            K.run_chain(c, shape, n_outputs=0, reduce=op, reduce_scale=scale, keepdim=keepdim,
+                        red_out=_st(out))
+        else:
+            outer, red, inner = K._mid_view(shape, dim)
+            nbytes = K._abi.lib().ts_reduce_mid_scratch_bytes(outer, red, inner)
+            scratch = torch.empty(max(int(nbytes), 0), dtype=torch.uint8, device=sx.image.device) \
+                if nbytes else None
+            rc = K._abi.lib().ts_reduce_mid(sx.ptr(), _st(out).ptr(), outer, red, inner, K.RED[op],
+                                            scale, scratch.data_ptr() if scratch is not None else None,
+                                            K._stream())
+            K._abi.check(rc, "ts_reduce_mid")
+    return out
+
+
+def _reduce(x: torch.Tensor, dims, op: str, keepdim: bool, mean: bool = False) -> torch.Tensor:
+    _check_fp16(x)
+    nd = max(x.dim(), 1)
+    if dims is None or (isinstance(dims, (list, tuple)) and len(dims) == 0):
+        dims = list(range(nd))
+    if isinstance(dims, int):
+        dims = [dims]
+    dims = sorted({d % nd for d in dims}, reverse=True)
+    count = 1
+    for d in dims:
+        count *= x.shape[d] if x.dim() else 1
+    out = x
+    for i, d in enumerate(dims):  # innermost first, so earlier results keep their positions
+        last = i == len(dims) - 1
+        out = _reduce_one(out, d, op, keepdim, (1.0 / count) if (mean and last) else 1.0)
+    return out
+
+
+@_impl("sum.dim_IntList")
+def _sum_dim(x, dim, keepdim=False, *, dtype=None):
+    return _reduce(x, dim, "sum", keepdim)
+
+
+@_impl("sum")
+def _sum_all(x, *, dtype=None):
+    return _reduce(x, None, "sum", False)
+
+
+@_impl("mean.dim")
+def _mean_dim(x, dim, keepdim=False, *, dtype=None):
+    return _reduce(x, dim, "sum", keepdim, mean=True)
+
+
+@_impl("mean")
+def _mean_all(x, *, dtype=None):
+    return _reduce(x, None, "sum", False, mean=True)
+
+
+@_impl("amax")
+def _amax(x, dim=(), keepdim=False):
+    return _reduce(x, list(dim), "max", keepdim)
+
+
+@_impl("amin")
+def _amin(x, dim=(), keepdim=False):
+    return _reduce(x, list(dim), "min", keepdim)
+
+
+# ---- softmax / norms -------------------------------------------------------------------
+
+def _softmax_impl(x, dim, log):
+    _check_fp16(x)
+    out = _new(x.shape, x)
+    if x.numel() == 0:
+        return out
+    with _with_device(x):
+        sx, so = _st(x), _st(out)
+        nd = max(x.dim(), 1)
+        d = dim % nd
+        if d == nd - 1:
+            K.softmax_rows(sx, log, out=so)
+        else:
+            outer, red, inner = K._mid_view(sx.shape, d)
+            rc = K._abi.lib().ts_softmax_mid(sx.ptr(), so.ptr(), outer, red, inner, int(log), K._stream())
+            K._abi.check(rc, "ts_softmax_mid")
+    return out
+
+
+@_impl("_softmax")
+def _softmax(x, dim, half_to_float):
+    if half_to_float:
+        raise NotImplementedError("softmax with half_to_float")
+    return _softmax_impl(x, dim, False)
+
+
+@_impl("_log_softmax")
+def _log_softmax(x, dim, half_to_float):
+    if half_to_float:
+        raise NotImplementedError("log_softmax with half_to_float")
+    return _softmax_impl(x, dim, True)
+
+
+@_impl("native_layer_norm")
+def _native_layer_norm(x, normalized_shape, weight, bias, eps):
+    _check_fp16(x)
+    if len(normalized_shape) != 1 or normalized_shape[0] != x.shape[-1]:
+        raise NotImplementedError("layer_norm over more than the last dim")
+    out = _new(x.shape, x)
+    with _with_device(x):
+        K.layernorm_rows(_st(x), _st(weight) if weight is not None else None,
+                         _st(bias) if bias is not None else None, float(eps), out=_st(out))
+    stat_shape = list(x.shape[:-1]) + [1]
+    # mean / rstd are only consumed by a backward pass, which this device does not run
+    return out, _new(stat_shape, x), _new(stat_shape, x)
+
+
+def rms_norm(x: torch.Tensor, weight: Optional[torch.Tensor], eps: float,
+             round_before_weight: bool = True) -> torch.Tensor:
+    """Fused RMSNorm over the last dim (module semantics by default: the normalised value is
+    rounded to fp16 before the fp16 multiply by weight)."""
+    _check_fp16(x)
+    out = _new(x.shape, x)
+    with _with_device(x):
+        K.rmsnorm_rows(_st(x), _st(weight) if weight is not None else None, float(eps),
+                       round_before_weight, out=_st(out))
+    return out
+
+
+# ---- matmul ----------------------------------------------------------------------------
+
+def _weight_operand(b: torch.Tensor) -> Tuple[StickTensor, bool]:
+    """(stick tensor, b_kmajor): a transposed view of a canonical [.., N, K] tensor is used in
+    place, as the K-major operand of a @ b^T; anything else is laid out as [.., K, N]."""
+    if b.dim() >= 2 and not _C.is_canonical(b):
+        bt = b.transpose(-1, -2)
+        if _C.is_canonical(bt):
+            return _st(bt), True
+    return _st(b), False
+
+
+def _matmul(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _check_fp16(a, b)
+    if a.shape[-1] != b.shape[-2]:
+        raise RuntimeError(f"mat1 and mat2 shapes cannot be multiplied ({tuple(a.shape)} and {tuple(b.shape)})")
+    out = _new(tuple(a.shape[:-1]) + (b.shape[-1],), a)
+    if out.numel() == 0:
+        return out
+    if a.shape[-1] == 0:
+        return _fill(out, 0.0)
+    with _with_device(a):
+        sb, kmajor = _weight_operand(b)
+        K.matmul(_st(a), sb, bias=_st(bias) if bias is not None else None, b_kmajor=kmajor,
+                 out=_st(out))
+    return out
+
+
+@_impl("mm")
+def _mm(a, b):
+    return _matmul(a, b)
+
+
+@_impl("bmm")
+def _bmm(a, b):
+    return _matmul(a, b)
+
+
+@_impl("addmm")
+def _addmm(bias, a, b, *, beta=1, alpha=1):
+    if float(beta) == 1.0 and float(alpha) == 1.0 and bias.dim() == 1 and bias.shape[0] == b.shape[-1]:
+        return _matmul(a, b, bias)
+    prod = _matmul(a, b)
+    if float(alpha) != 1.0:
+        prod = _binary("MUL", prod, float(alpha))
+    if float(beta) == 0.0:
+        return prod
+    return _binary("ADD", prod, bias, alpha=float(beta))
+
+
+@_impl("_to_copy")
+def _to_copy(x, *, dtype=None, layout=None, device=None, pin_memory=None, non_blocking=False,
+             memory_format=None):
+    device = torch.device(device) if device is not None else x.device
+    dtype = dtype or x.dtype
+    if dtype != x.dtype:
+        # dtype conversion happens on the host: the device copy path moves bits only
+        host = x.to("cpu") if x.device.type != "cpu" else x
+        host = host.to(dtype)
+        return host if device.type == "cpu" else host.to(device)
+    out = torch.empty(x.shape, dtype=dtype, device=device)
+    out.copy_(x)
+    return out

@@ -289,7 +289,8 @@ def broadcast_shape4(out_shape: Sequence[int], in_shape: Sequence[int]) -> List[
 
 def prepare_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
                   reduce: Optional[str] = None, reduce_scale: float = 1.0,
-                  keepdim: bool = False, outputs: Optional[List[StickTensor]] = None):
+                  keepdim: bool = False, outputs: Optional[List[StickTensor]] = None,
+                  red_out: Optional[StickTensor] = None):
     """Allocates outputs and marshals every argument once.  Returns (launch, outputs,
     reduced output); launch() enqueues the kernel on the current stream."""
     out_shape = tuple(out_shape) if len(out_shape) else (1,)
@@ -297,21 +298,27 @@ def prepare_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
         shape4 = [1] * (4 - len(out_shape)) + list(out_shape)
     else:
         shape4 = broadcast_shape4(out_shape, out_shape)
-    dev = chain.inputs[0].image.device if chain.inputs else torch.device("cuda")
+    if chain.inputs:
+        dev = chain.inputs[0].image.device
+    elif outputs:
+        dev = outputs[0].image.device
+    else:
+        dev = torch.device("cuda")
     if outputs is None:
         outputs = [empty(out_shape, torch.float16, dev) for _ in range(n_outputs)]
     in_shapes: List[int] = []
     for t in chain.inputs:
         in_shapes += broadcast_shape4(out_shape, t.shape)
-    red_out = None
     red_inner = 1
     if reduce is not None:
         lead = list(out_shape[:-1])
         if keepdim:
-            red_out = empty(lead + [1], torch.float16, dev)
+            red_out = red_out or empty(lead + [1], torch.float16, dev)
         else:
-            red_out = empty(lead if lead else [1], torch.float16, dev)
+            red_out = red_out or empty(lead if lead else [1], torch.float16, dev)
             red_inner = lead[-1] if lead else 1
+    else:
+        red_out = None
     insns = (PwInsn * len(chain.insns))(*chain.insns)
     args = (insns, len(chain.insns), _abi.ptrs([t.ptr() for t in chain.inputs]),
             _abi.i64(in_shapes), len(chain.inputs), _abi.ptrs([o.ptr() for o in outputs]),
@@ -331,11 +338,12 @@ def prepare_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
 
 def run_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
               reduce: Optional[str] = None, reduce_scale: float = 1.0,
-              keepdim: bool = False, outputs: Optional[List[StickTensor]] = None
+              keepdim: bool = False, outputs: Optional[List[StickTensor]] = None,
+              red_out: Optional[StickTensor] = None
               ) -> Tuple[List[StickTensor], Optional[StickTensor]]:
     """Launches the chain over `out_shape`.  Returns (full-shape outputs, reduced output)."""
     launch, outs, red = prepare_chain(chain, out_shape, n_outputs, reduce, reduce_scale, keepdim,
-                                      outputs)
+                                      outputs, red_out)
     launch()
     return outs, red
 
