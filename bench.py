@@ -145,6 +145,50 @@ def make_workload(name: str, dev, scale_rows=None):
                     cpu_step=cpu_step, sample="full [8192,8192] graph per CPU step",
                     check=lambda: math_ref.assert_close(step_e2e().clone(), cpu_step()))
 
+    if name == "pointwise":
+        rows = cols = 8192
+        x, a, b = math_ref.fused_inputs(rows, cols)
+        xp = x.pin_memory()
+        sb = K.copy_host_to_sticks(b.pin_memory())
+        ring = 3
+        xs = [K.copy_host_to_sticks(xp)]
+        for _ in range(ring - 1):
+            xs.append(K.StickTensor(xs[0].image.clone(), xs[0].shape))
+        outs = [K.empty((rows, cols)) for _ in range(ring)]
+
+        def chain_on(sx):
+            c = K.Chain()
+            c.emit("LOAD", c.tensor(sx)).emit("ADD", c.tensor(sb)).store(0)
+            return c
+
+        launches = [K.prepare_chain(chain_on(sx), (rows, cols), outputs=[o])[0] for sx, o in zip(xs, outs)]
+        state = {"i": 0}
+
+        def step_dev():
+            launches[state["i"] % ring]()
+            state["i"] += 1
+
+        staging = torch.empty(rows * cols * 2, dtype=torch.uint8, device=dev)
+        sx_e = K.empty((rows, cols))
+        y_host = torch.empty(rows, cols, dtype=torch.float16).pin_memory()
+
+        def step_e2e():
+            K.copy_host_to_sticks(xp, sx_e, staging)
+            (o,), _ = K.run_chain(chain_on(sx_e), (rows, cols), outputs=[outs[0]])
+            K.copy_sticks_to_host(o, y_host, staging)
+            torch.cuda.current_stream().synchronize()
+            return y_host
+
+        def cpu_step():
+            return x + b
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=2 * rows * cols * 2 + cols * 2,
+                    h2d=rows * cols * 2, d2h=rows * cols * 2, launches=1,
+                    desc=f"pointwise x + b (b broadcast along rows), fp16 [{rows},{cols}]",
+                    l2=f"ring of {ring} input and output buffers ({2 * ring * rows * cols * 2 >> 20} MiB) > L2",
+                    cpu_step=cpu_step, sample="full [8192,8192] add per CPU step",
+                    check=lambda: math_ref.assert_close(step_e2e().clone(), cpu_step()))
+
     if name in ("softmax", "softmax_scaled"):
         rows, cols = (256, 4096) if name == "softmax" else (scale_rows or 65536, 4096)
         x = math_ref.softmax_inputs(256, cols)
@@ -354,6 +398,50 @@ def make_workload_cpu(name):
         return dict(cpu_step=lambda: math_ref.fused_ref(x, a, b), alg_bytes=134266880,
                     desc="exp(x*a+b).sum(-1), x fp16 [8192,8192] (BASELINE configs[1])",
                     sample="full [8192,8192] graph per CPU step")
+    if name == "pointwise":
+        rows = cols = 8192
+        x, a, b = math_ref.fused_inputs(rows, cols)
+        xp = x.pin_memory()
+        sb = K.copy_host_to_sticks(b.pin_memory())
+        ring = 3
+        xs = [K.copy_host_to_sticks(xp)]
+        for _ in range(ring - 1):
+            xs.append(K.StickTensor(xs[0].image.clone(), xs[0].shape))
+        outs = [K.empty((rows, cols)) for _ in range(ring)]
+
+        def chain_on(sx):
+            c = K.Chain()
+            c.emit("LOAD", c.tensor(sx)).emit("ADD", c.tensor(sb)).store(0)
+            return c
+
+        launches = [K.prepare_chain(chain_on(sx), (rows, cols), outputs=[o])[0] for sx, o in zip(xs, outs)]
+        state = {"i": 0}
+
+        def step_dev():
+            launches[state["i"] % ring]()
+            state["i"] += 1
+
+        staging = torch.empty(rows * cols * 2, dtype=torch.uint8, device=dev)
+        sx_e = K.empty((rows, cols))
+        y_host = torch.empty(rows, cols, dtype=torch.float16).pin_memory()
+
+        def step_e2e():
+            K.copy_host_to_sticks(xp, sx_e, staging)
+            (o,), _ = K.run_chain(chain_on(sx_e), (rows, cols), outputs=[outs[0]])
+            K.copy_sticks_to_host(o, y_host, staging)
+            torch.cuda.current_stream().synchronize()
+            return y_host
+
+        def cpu_step():
+            return x + b
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=2 * rows * cols * 2 + cols * 2,
+                    h2d=rows * cols * 2, d2h=rows * cols * 2, launches=1,
+                    desc=f"pointwise x + b (b broadcast along rows), fp16 [{rows},{cols}]",
+                    l2=f"ring of {ring} input and output buffers ({2 * ring * rows * cols * 2 >> 20} MiB) > L2",
+                    cpu_step=cpu_step, sample="full [8192,8192] add per CPU step",
+                    check=lambda: math_ref.assert_close(step_e2e().clone(), cpu_step()))
+
     if name in ("softmax", "softmax_scaled"):
         rows = 256 if name == "softmax" else 65536
         x = math_ref.softmax_inputs(256, 4096).repeat(rows // 256, 1)

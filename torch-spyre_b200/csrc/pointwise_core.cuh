@@ -51,6 +51,7 @@ struct Params {
   uint32_t rows, nsticks, cols, total_sticks;
   FastDiv div_rows, div_d2, div_d1;
   int need_index;  // some input is not flat
+  uint32_t opaque_zero;  // always 0, but only known at run time (see fetch)
   int ragged;      // cols is not a stick multiple
   int red_keepdim, ws_log;
   float red_scale;
@@ -223,6 +224,17 @@ __device__ __forceinline__ void fetch(const Ctx& ctx, Regs<U>& R, int kind, int 
   if (kind == TS_PW_TENSOR) {
 #pragma unroll
     for (int u = 0; u < U; ++u) ctx.tensor(idx, u, v[u]);
+    if (U > 1) {
+      // Make every item's value depend on all U loads (through a mask that is zero at
+      // run time), so that the U loads are issued back to back instead of each one
+      // being scheduled next to its own use, which would leave one load in flight.
+      uint32_t m = 0;
+#pragma unroll
+      for (int u = 0; u < U; ++u) m ^= *reinterpret_cast<const uint32_t*>(&v[u][0]);
+      m &= ctx.P.opaque_zero;
+#pragma unroll
+      for (int u = 0; u < U; ++u) *reinterpret_cast<uint32_t*>(&v[u][0]) ^= m;
+    }
   } else if (kind == TS_PW_IMM) {
     const __half2 x = __float2half2_rn(imm);
 #pragma unroll
@@ -461,6 +473,12 @@ __global__ void __launch_bounds__(kThreads) flat_kernel(const __grid_constant__ 
   run_program<Prog, U>(P, R, ctx);
 }
 
+// acc + float(h) in one instruction (mixed-precision add, sm_100).
+__device__ __forceinline__ float add_f16(float acc, __half h) {
+  asm("add.rn.f32.f16 %0, %1, %0;" : "+f"(acc) : "h"(__half_as_ushort(h)));
+  return acc;
+}
+
 template <int RED>
 __device__ __forceinline__ float red_identity() {
   return RED == TS_RED_SUM ? 0.f : (RED == TS_RED_MAX ? -INFINITY : INFINITY);
@@ -581,18 +599,24 @@ __global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant_
       if (!FULL && !ctx.live[u]) continue;
       const uint32_t col = ctx.s[u] * kStickHalfs + ctx.lv * 8;
       float t = red_identity<RED>();
+      if (RED == TS_RED_SUM && !kFuseTail && FULL) {
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 x = __half22float2(R.acc[u][j]);
-        if (kFuseTail) {
-          x.x = unary_f32(kLastOp, x.x);
-          x.y = unary_f32(kLastOp, x.y);
+        for (int j = 0; j < 4; ++j)
+          t = add_f16(add_f16(t, __low2half(R.acc[u][j])), __high2half(R.acc[u][j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 x = __half22float2(R.acc[u][j]);
+          if (kFuseTail) {
+            x.x = unary_f32(kLastOp, x.x);
+            x.y = unary_f32(kLastOp, x.y);
+          }
+          if (!FULL && P.ragged) {
+            if (col + 2 * j >= P.cols) x.x = red_identity<RED>();
+            if (col + 2 * j + 1 >= P.cols) x.y = red_identity<RED>();
+          }
+          t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
         }
-        if (!FULL && P.ragged) {
-          if (col + 2 * j >= P.cols) x.x = red_identity<RED>();
-          if (col + 2 * j + 1 >= P.cols) x.y = red_identity<RED>();
-        }
-        t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
       }
       partial = red_combine<RED>(partial, t);
     }
@@ -610,6 +634,9 @@ __global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant_
 constexpr int kChunk = 4;          // stick columns per stage (= items per step)
 constexpr int kChunkBytes = 512;   // 4 rows x one stick
 constexpr int kMaxStreams = 2;
+// Measured slower than the register path on B200 for the benchmark shapes (more
+// instructions per byte); kept selectable for shapes where occupancy is the limit.
+constexpr bool kUseStreamKernels = false;
 
 static __device__ int g_stream_error;  // sticky: a bounded wait gave up (one copy per source file)
 
@@ -831,9 +858,9 @@ void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
     int nflat = 0;
     for (int t = 0; t < P.n_in; ++t) nflat += P.in[t].flat ? 1 : 0;
     const bool full = rows_full(P, U);
-    if (full && U == kChunk && nflat == 1) {
+    if (kUseStreamKernels && full && U == kChunk && nflat == 1) {
       launch_stream<Prog, RED, 1>(P, blocks, st);
-    } else if (full && U == kChunk && nflat == 2) {
+    } else if (kUseStreamKernels && full && U == kChunk && nflat == 2) {
       launch_stream<Prog, RED, 2>(P, blocks, st);
     } else if (full) {
       rowred_kernel<Prog, RED, U, true><<<blocks, kThreads, 0, st>>>(P);
