@@ -212,6 +212,29 @@ int ts_reduce_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t in
 int ts_softmax_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
                    int log_softmax, void* stream);
 
+/* ts_reduce_mid for callers that cannot supply scratch memory.  This entry point has
+ * no counterpart in the reference.  It exists for users of the library that own no
+ * device allocator: a plug-in that only ever receives input and output pointers from
+ * the application hosting it, or a caller in a latency-critical loop that must stay
+ * away from cudaMalloc because an allocation can stall the whole device.
+ *
+ * Same arguments and result as ts_reduce_mid, minus `scratch`: when the launch splits
+ * `red` over several thread blocks, the fp32 partials go to a fixed array inside the
+ * library image, ts_reduce_mid_static_max_bytes() bytes (512 KiB) on every GPU that loads
+ * the library, held until the process exits.  The call itself allocates nothing, on the
+ * host or on the device.  A request whose partials
+ * (ts_reduce_mid_scratch_bytes(outer, red, inner)) do not fit returns TS_ERR_TOO_LARGE.
+ *
+ * The first call on each device looks up the array's device address (with that device
+ * current); make that first call outside any stream capture.  All calls on a device
+ * share the one array and it keeps whatever the previous call left there; nothing in
+ * it needs to start at zero, since every partial is written before it is read, but two
+ * calls whose kernels overlap on the GPU (different streams) would overwrite each
+ * other's partials: run them on one stream or order them with events. */
+int ts_reduce_mid_static(const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
+                         int reduce_op, float scale, void* stream);
+int64_t ts_reduce_mid_static_max_bytes(void);
+
 /* ---- fp16 matmul / batched matmul on the tcgen05 tensor cores ----------------
  *
  * c[batch, M, N] = a[batch, M, K] x B (+ bias[N]), fp32 accumulation, fp16 result;

@@ -11,6 +11,7 @@
 // gridDim.z blocks, which leave fp32 partials in caller-provided scratch for a
 // second, small kernel to combine.
 #include <algorithm>
+#include <atomic>
 
 #include "common.cuh"
 
@@ -254,3 +255,75 @@ extern "C" int ts_softmax_mid(const void* x, void* y, int64_t outer, int64_t red
   TSB_CHECK_LAUNCH();
   return TS_OK;
 }
+
+// ---- ts_reduce_mid for callers that cannot provide scratch ---------------------------
+//
+// Some users of this library have no way to hand it a scratch buffer: a plug-in that is
+// only ever given input and output device pointers by its host application (the
+// application owns the device memory and offers the plug-in no allocator), or a caller
+// inside a latency-critical loop that must not touch the CUDA allocator because an
+// allocation may synchronise the whole device.  For them the split-reduction partials
+// live in a fixed array that is part of the library image: every GPU that loads the
+// library carries these kReduceStaticBytes until the process exits.
+namespace tsb {
+namespace {
+
+constexpr size_t kReduceStaticBytes = 512u << 10;  // 512 KiB of fp32 partials
+static __device__ __align__(256) unsigned char g_reduce_static_scratch[kReduceStaticBytes];
+
+constexpr int kMaxDevices = 64;
+std::atomic<void*> g_reduce_static_ptr[kMaxDevices];  // device address of the array, per GPU
+
+// In host code the array's name is only a handle, not an address the GPU can use; the
+// real device address has to be asked for, once per device, with that device current.
+int reduce_static_scratch(void** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TS_ERR_CUDA;
+  void* p = g_reduce_static_ptr[dev].load(std::memory_order_acquire);
+  if (!p) {
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_reduce_static_scratch);
+    if (e != cudaSuccess || !p) {
+      note_cuda_error(e);
+      return TS_ERR_CUDA;
+    }
+    g_reduce_static_ptr[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return TS_OK;
+}
+
+}  // namespace
+}  // namespace tsb
+
+extern "C" int ts_reduce_mid_static(const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
+                                    int reduce_op, float scale, void* stream) {
+  if (reduce_op < TS_RED_SUM || reduce_op > TS_RED_MIN) return TS_ERR_INVALID;
+  MidParams P;
+  const int rc = plan_mid(outer, red, inner, P, true);
+  if (rc != TS_OK) return rc;
+  if (outer == 0 || inner == 0) return TS_OK;
+  if (!x || !y) return TS_ERR_INVALID;
+  if (((uintptr_t)x | (uintptr_t)y) % 16) return TS_ERR_ALIGNMENT;
+  const size_t need = P.splits > 1 ? (size_t)P.splits * outer * inner * sizeof(float) : 0;
+  if (need > kReduceStaticBytes) return TS_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int src = reduce_static_scratch(&scratch);
+  if (src != TS_OK) return src;
+  P.x = (const __half*)x;
+  P.y = (__half*)y;
+  P.scratch = (float*)scratch;
+  P.op = reduce_op;
+  P.scale = scale;
+  cudaStream_t st = (cudaStream_t)stream;
+  dim3 grid((uint32_t)ceil_div(P.inner_vecs, 1 << P.tx_log), P.outer, P.splits);
+  reduce_mid_kernel<<<grid, kThreads, 0, st>>>(P);
+  TSB_CHECK_LAUNCH();
+  if (P.splits > 1) {
+    const int64_t nvec = (int64_t)P.outer * P.inner_vecs;
+    reduce_mid_finish<<<(uint32_t)ceil_div(nvec, kThreads), kThreads, 0, st>>>(P);
+    TSB_CHECK_LAUNCH();
+  }
+  return TS_OK;
+}
+
+extern "C" int64_t ts_reduce_mid_static_max_bytes(void) { return (int64_t)tsb::kReduceStaticBytes; }

@@ -66,6 +66,9 @@ SIGNATURES = {
     "ts_reduce_mid_scratch_bytes": (ctypes.c_int64, [ctypes.c_int64] * 3),
     "ts_reduce_mid": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                      ctypes.c_int, ctypes.c_float, vp, vp]),
+    "ts_reduce_mid_static": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                            ctypes.c_int, ctypes.c_float, vp]),
+    "ts_reduce_mid_static_max_bytes": (ctypes.c_int64, []),
     "ts_gemm_f16": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                    ctypes.c_int64, ctypes.c_int, ctypes.c_int, vp]),
     "ts_gemm_error_state": (ctypes.c_int, []),
