@@ -5,6 +5,7 @@
 // torch_spyre/csrc/spyre_hooks.cpp:33-259 hooks and stream/event methods), with the
 // flex runtime replaced by CUDA: `spyre:N` is CUDA device N, streams and events are
 // the CUDA ones PyTorch manages.
+#include <ATen/Context.h>
 #include <ATen/cuda/CUDAContext.h>
 #include <ATen/detail/CUDAHooksInterface.h>
 #include <ATen/detail/PrivateUse1HooksInterface.h>
@@ -52,6 +53,8 @@ void delete_ctx(void* ctx_void) {
 
 struct SpyreAllocator final : public at::Allocator {
   at::DataPtr allocate(size_t nbytes) override {
+    // PyTorch brings CUDA (and its caching allocator) up lazily; make sure it has.
+    at::globalContext().lazyInitDevice(c10::DeviceType::CUDA);
     const c10::DeviceIndex dev = c10::cuda::current_device();
     const c10::Device device(c10::DeviceType::PrivateUse1, dev);
     auto* ctx = new StorageCtx();
