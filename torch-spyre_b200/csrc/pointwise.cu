@@ -112,13 +112,26 @@ extern "C" int ts_pointwise_chain(const ts_pw_insn* insns, int n_insns, const vo
   P.div_d2.init((uint32_t)shape[2]);
   P.div_d1.init((uint32_t)shape[1]);
 
-  // A pre-instantiated program with the same code words?
+  // Operand classes of this call (two bits per input; unused inputs count as generic).
+  uint32_t cls = kClsAllGeneric;
+  for (int t = 0; t < n_inputs; ++t) {
+    const TensorDesc& d = P.in[t];
+    int c = kClsGeneric;
+    if (d.flat) c = kClsFlat;
+    else if (!d.col_bcast && d.m0 == 0 && d.m1 == 0 && d.m2 == 0) c = kClsRowVec;
+    cls = (cls & ~(3u << (2 * t))) | ((uint32_t)c << (2 * t));
+  }
+  // A pre-instantiated program with the same code words?  Prefer one compiled for exactly
+  // these operand classes, else one compiled for any.
   const StaticEntry* hit = nullptr;
   for (const StaticEntry& e : registry()) {
     if (e.red != reduce_op || e.n != n_insns) continue;
+    if (e.cls != cls && e.cls != kClsAllGeneric) continue;
     bool same = true;
     for (int i = 0; i < n_insns && same; ++i) same = e.codes[i] == P.code[i];
-    if (same) { hit = &e; break; }
+    if (!same) continue;
+    if (!hit || e.cls == cls) hit = &e;
+    if (e.cls == cls) break;
   }
   const int items = hit ? hit->items : kDynU;
 

@@ -152,40 +152,64 @@ struct ItemCtx {
 // Row kernels with a compile-time program: all items of a thread lie in one row, so
 // each tensor needs one base pointer and one stride per stick column, set up once.
 // FULL: no item is ever out of range and cols is a stick multiple.
-template <int U, bool FULL>
+// Operand classes, two bits per input tensor, fixed at compile time per instantiation:
+// how a tensor is addressed decides how many instructions each fetch costs.
+constexpr int kClsFlat = 0;     // same shape as the iteration space
+constexpr int kClsRowVec = 1;   // [cols] vector broadcast along rows
+constexpr int kClsGeneric = 2;  // anything else: resolved from the run-time descriptor
+constexpr uint32_t kClsAllGeneric = 0xAAAAu;
+__host__ __device__ constexpr int cls_of(uint32_t mask, int t) { return (int)((mask >> (2 * t)) & 3u); }
+
+template <int U, bool FULL, int RG, uint32_t CLS>
 struct RowCtx {
+  // U items = RG row groups (rows 4 apart) x U/RG stick columns; item i belongs to row
+  // group i / (U/RG).  A row vector is fetched once for all RG rows (same address).
+  static constexpr int kPerGroup = U / RG;
   const Params& P;
-  const __half* base[TS_PW_MAX_INPUTS];
-  int64_t sstride[TS_PW_MAX_INPUTS];
-  __half2 bval[TS_PW_MAX_INPUTS];
-  int64_t out_base;   // element offset of this thread's vector in stick column 0 of an output
-  int64_t out_stride;
+  int64_t flat_base;    // element offset of (row, lane vector) in stick column 0 of a flat image
+  int64_t flat_stride;  // elements between stick columns of a flat image
+  const __half* gbase[TS_PW_MAX_INPUTS][RG];   // generic operands only
+  int64_t gstride[TS_PW_MAX_INPUTS];
+  __half2 bval[TS_PW_MAX_INPUTS][RG];
   uint32_t lv, s[U];
   bool live[U];
   __device__ __forceinline__ RowCtx(const Params& p, uint32_t row, uint32_t lane_vec, bool row_live)
       : P(p), lv(lane_vec) {
-    Item it;
-    it.r = row;
-    it.i0 = it.i1 = it.i2 = 0;
-    if (p.need_index && row_live) {
-      uint32_t q;
-      p.div_d2.divmod(row, q, it.i2);
-      p.div_d1.divmod(q, it.i0, it.i1);
-    }
-    out_base = (int64_t)row * kStickHalfs + lane_vec * 8;
-    out_stride = (int64_t)p.rows * kStickHalfs;
+    flat_base = (int64_t)row * kStickHalfs + lane_vec * 8;
+    flat_stride = (int64_t)p.rows * kStickHalfs;
 #pragma unroll
     for (int t = 0; t < TS_PW_MAX_INPUTS; ++t) {
-      base[t] = nullptr;
-      sstride[t] = 0;
-      bval[t] = __float2half2_rn(0.f);
-      if (t < p.n_in) {
-        const TensorDesc& d = p.in[t];
-        const uint32_t trow = d.flat ? row : it.i0 * (uint32_t)d.m0 + it.i1 * (uint32_t)d.m1 +
-                                                 it.i2 * (uint32_t)d.m2;
-        base[t] = d.ptr + (int64_t)trow * kStickHalfs + (d.col_bcast ? 0 : lane_vec * 8);
-        sstride[t] = d.col_bcast ? 0 : d.stick_stride;
-        if (d.col_bcast && row_live) bval[t] = __half2half2(__ldg(base[t]));
+      gstride[t] = 0;
+#pragma unroll
+      for (int g = 0; g < RG; ++g) {
+        gbase[t][g] = nullptr;
+        bval[t][g] = __float2half2_rn(0.f);
+      }
+    }
+    bool any_generic = false;
+#pragma unroll
+    for (int t = 0; t < TS_PW_MAX_INPUTS; ++t) any_generic = any_generic || cls_of(CLS, t) == kClsGeneric;
+    if (any_generic) {
+#pragma unroll
+      for (int g = 0; g < RG; ++g) {
+        const uint32_t r = row + 4 * g;
+        uint32_t i0 = 0, i1 = 0, i2 = 0;
+        if (p.need_index && row_live) {
+          uint32_t q;
+          p.div_d2.divmod(r, q, i2);
+          p.div_d1.divmod(q, i0, i1);
+        }
+#pragma unroll
+        for (int t = 0; t < TS_PW_MAX_INPUTS; ++t) {
+          if (cls_of(CLS, t) == kClsGeneric && t < p.n_in) {
+            const TensorDesc& d = p.in[t];
+            const uint32_t trow = d.flat ? r : i0 * (uint32_t)d.m0 + i1 * (uint32_t)d.m1 +
+                                                   i2 * (uint32_t)d.m2;
+            gbase[t][g] = d.ptr + (int64_t)trow * kStickHalfs + (d.col_bcast ? 0 : lane_vec * 8);
+            gstride[t] = d.col_bcast ? 0 : d.stick_stride;
+            if (d.col_bcast && row_live) bval[t][g] = __half2half2(__ldg(gbase[t][g]));
+          }
+        }
       }
     }
   }
@@ -194,12 +218,22 @@ struct RowCtx {
       set_all(v, __float2half2_rn(0.f));
       return;
     }
-    if (P.in[t].col_bcast) {
-      set_all(v, bval[t]);
-      return;
-    }
+    const int g = u / kPerGroup;
+    const int cls = cls_of(CLS, t);
     Vec8h x;
-    x.u = ld_stream_v4(base[t] + (int64_t)s[u] * sstride[t]);
+    if (cls == kClsFlat) {
+      x.u = ld_stream_v4(P.in[t].ptr + flat_base + (int64_t)(4 * g) * kStickHalfs +
+                         (int64_t)s[u] * flat_stride);
+    } else if (cls == kClsRowVec) {
+      x.u = ld_global_v4(P.in[t].ptr + s[u] * kStickHalfs + lv * 8);
+    } else {
+      if (P.in[t].col_bcast) {
+        set_all(v, bval[t][g]);
+        return;
+      }
+      const __half* p = gbase[t][g] + (int64_t)s[u] * gstride[t];
+      x.u = P.in[t].flat ? ld_stream_v4(p) : ld_global_v4(p);
+    }
 #pragma unroll
     for (int j = 0; j < 4; ++j) v[j] = x.h2[j];
   }
@@ -214,7 +248,8 @@ struct RowCtx {
       for (int e = 0; e < 8; ++e)
         if (col + e >= P.cols) t.h[e] = __float2half(0.f);
     }
-    st_global_v4(P.out[o] + out_base + (int64_t)s[u] * out_stride, t.u);
+    const int g = u / kPerGroup;
+    st_global_v4(P.out[o] + flat_base + (int64_t)(4 * g) * kStickHalfs + (int64_t)s[u] * flat_stride, t.u);
   }
 };
 
@@ -573,24 +608,27 @@ __global__ void __launch_bounds__(kThreads) rowred_dyn_kernel(const __grid_const
 // Compile-time program.  When the program ends in a unary op evaluated in fp32, that
 // op's fp32 results feed the reduction directly, skipping the fp16 round trip (the
 // reduction accumulates in fp32 either way).
-template <class Prog, int RED, int U, bool FULL>
-__global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant__ Params P) {
+template <class Prog, int RED, int U, bool FULL, int RG, uint32_t CLS>
+__global__ void __launch_bounds__(kThreads, (CLS == kClsAllGeneric ? 1 : 4)) rowred_kernel(const __grid_constant__ Params P) {
   __shared__ float part[8][4];
   constexpr int kLastOp = code_op(Prog::template at<Prog::n - 1>());
   constexpr bool kFuseTail = is_unary_f32(kLastOp);
+  constexpr int kPerGroup = U / RG;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int ws = 1 << P.ws_log;
   const int ws_idx = warp & (ws - 1);
   const uint32_t group = blockIdx.x * (8 >> P.ws_log) + (warp >> P.ws_log);
-  const uint32_t row = group * 4 + (lane >> 3);
-  const bool row_live = FULL || row < P.rows;
-  RowCtx<U, FULL> ctx(P, row, lane & 7, row_live);
-  float partial = red_identity<RED>();
+  const uint32_t row = group * (4 * RG) + (lane >> 3);
+  const bool row_live = FULL || row < P.rows;   // RG > 1 is only used with FULL
+  RowCtx<U, FULL, RG, CLS> ctx(P, row, lane & 7, row_live);
+  float partial[RG];
+#pragma unroll
+  for (int g = 0; g < RG; ++g) partial[g] = red_identity<RED>();
   Regs<U> R;
-  for (uint32_t s0 = ws_idx; s0 < P.nsticks; s0 += ws * U) {
+  for (uint32_t s0 = ws_idx; s0 < P.nsticks; s0 += ws * kPerGroup) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      ctx.s[u] = s0 + u * ws;
+      ctx.s[u] = s0 + (u % kPerGroup) * ws;
       ctx.live[u] = FULL || (row_live && ctx.s[u] < P.nsticks);
     }
     run_program<Prog, U, (kFuseTail ? Prog::n - 1 : Prog::n)>(P, R, ctx);
@@ -618,10 +656,14 @@ __global__ void __launch_bounds__(kThreads) rowred_kernel(const __grid_constant_
           t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
         }
       }
-      partial = red_combine<RED>(partial, t);
+      partial[u / kPerGroup] = red_combine<RED>(partial[u / kPerGroup], t);
     }
   }
-  finish_row<RED>(P, partial, row, row_live, lane, warp, ws, ws_idx, part);
+#pragma unroll
+  for (int g = 0; g < RG; ++g) {
+    if (g > 0) __syncthreads();   // `part` is reused
+    finish_row<RED>(P, partial[g], row + 4 * g, row_live, lane, warp, ws, ws_idx, part);
+  }
 }
 
 // ---- the same reduction with its full-shape inputs streamed by bulk async copies ----
@@ -829,6 +871,7 @@ struct StaticEntry {
   int n;
   int red;  // TS_RED_*
   int items;  // work items per thread per step (U)
+  uint32_t cls;  // operand classes the instance was compiled for (kClsAllGeneric = any)
   LaunchFn fn;
 };
 void register_static(const StaticEntry& e);  // pointwise.cu
@@ -848,7 +891,7 @@ void launch_stream(const Params& P, uint32_t blocks, cudaStream_t st) {
   rowred_stream_kernel<Prog, RED, NSTREAM><<<blocks, kThreads, kBytes, st>>>(P);
 }
 
-template <class Prog, int RED, int U>
+template <class Prog, int RED, int U, uint32_t CLS = kClsAllGeneric>
 void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
   if constexpr (RED == TS_RED_NONE) {
     flat_kernel<Prog, U><<<blocks, kThreads, 0, st>>>(P);
@@ -858,23 +901,28 @@ void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
     int nflat = 0;
     for (int t = 0; t < P.n_in; ++t) nflat += P.in[t].flat ? 1 : 0;
     const bool full = rows_full(P, U);
+    const uint32_t groups_per_block = 8u >> P.ws_log;
     if (kUseStreamKernels && full && U == kChunk && nflat == 1) {
       launch_stream<Prog, RED, 1>(P, blocks, st);
     } else if (kUseStreamKernels && full && U == kChunk && nflat == 2) {
       launch_stream<Prog, RED, 2>(P, blocks, st);
+    } else if (full && P.rows % (8 * groups_per_block) == 0) {
+      // two row groups per warp step: operands broadcast along rows are fetched once for both
+      rowred_kernel<Prog, RED, 2 * U, true, 2, CLS><<<P.rows / (8 * groups_per_block), kThreads, 0, st>>>(P);
     } else if (full) {
-      rowred_kernel<Prog, RED, U, true><<<blocks, kThreads, 0, st>>>(P);
+      rowred_kernel<Prog, RED, U, true, 1, CLS><<<blocks, kThreads, 0, st>>>(P);
     } else {
-      rowred_kernel<Prog, RED, U, false><<<blocks, kThreads, 0, st>>>(P);
+      rowred_kernel<Prog, RED, U, false, 1, CLS><<<blocks, kThreads, 0, st>>>(P);
     }
   }
 }
 
-template <int RED, int U, uint32_t... C>
+template <int RED, int U, uint32_t CLS, uint32_t... C>
 struct Registrar {
   Registrar() {
     static const uint32_t codes[] = {C...};
-    register_static(StaticEntry{codes, (int)sizeof...(C), RED, U, &launch_instance<Fixed<C...>, RED, U>});
+    register_static(StaticEntry{codes, (int)sizeof...(C), RED, U, CLS,
+                                &launch_instance<Fixed<C...>, RED, U, CLS>});
   }
 };
 

@@ -15,7 +15,9 @@ constexpr int UR = 4;  // ... for programs ending in a row reduction
 
 #define PW_CAT2(a, b) a##b
 #define PW_CAT(a, b) PW_CAT2(a, b)
-#define PW_REG(red, u, ...) static Registrar<red, u, __VA_ARGS__> PW_CAT(reg_, __COUNTER__);
+#define PW_REG(red, u, ...) static Registrar<red, u, kClsAllGeneric, __VA_ARGS__> PW_CAT(reg_, __COUNTER__);
+#define PW_REG_CLS(red, u, cls, ...) static Registrar<red, u, cls, __VA_ARGS__> PW_CAT(reg_, __COUNTER__);
+constexpr uint32_t cls3(int a, int b, int c) { return (uint32_t)a | ((uint32_t)b << 2) | ((uint32_t)c << 4) | 0xAA80u; }
 
 #define PW_UNARY(op) PW_REG(TS_RED_NONE, UP, LD0, enc(op), ST0)
 #define PW_BINARY(op)                                          \
@@ -49,11 +51,16 @@ PW_REG(TS_RED_NONE, UP, LD0, enc(TS_PW_MUL, I, 0), enc(TS_PW_ADD, I, 0), ST0)
 PW_REG(TS_RED_SUM, UR, LD0)
 PW_REG(TS_RED_MAX, UR, LD0)
 PW_REG(TS_RED_MIN, UR, LD0)
+PW_REG_CLS(TS_RED_SUM, UR, cls3(kClsFlat, kClsGeneric, kClsGeneric), LD0)
+PW_REG_CLS(TS_RED_MAX, UR, cls3(kClsFlat, kClsGeneric, kClsGeneric), LD0)
+PW_REG_CLS(TS_RED_MIN, UR, cls3(kClsFlat, kClsGeneric, kClsGeneric), LD0)
 PW_REG(TS_RED_SUM, UR, LD0, enc(TS_PW_SQUARE))
 PW_REG(TS_RED_MAX, UR, LD0, enc(TS_PW_ABS))
 PW_REG(TS_RED_SUM, UR, LD0, enc(TS_PW_EXP))
-// exp(x * a + b).sum(-1)
+// exp(x * a + b).sum(-1): generic operands, and x full-shape with a, b row vectors
 PW_REG(TS_RED_SUM, UR, LD0, enc(TS_PW_MUL, T, 1), enc(TS_PW_ADD, T, 2), enc(TS_PW_EXP))
+PW_REG_CLS(TS_RED_SUM, UR, cls3(kClsFlat, kClsRowVec, kClsRowVec), LD0, enc(TS_PW_MUL, T, 1),
+           enc(TS_PW_ADD, T, 2), enc(TS_PW_EXP))
 // exp(x - rowmax) and its row sum (softmax pieces when not taken by the fused kernel)
 PW_REG(TS_RED_SUM, UR, LD0, enc(TS_PW_SUB, T, 1), enc(TS_PW_EXP))
 
