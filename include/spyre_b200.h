@@ -187,6 +187,13 @@ int ts_stream_error_state(void);
 #define TS_ROW_MAX_COLS 8192
 int ts_softmax_rows(const void* x, void* y, int64_t rows, int64_t cols, int log_softmax,
                     void* stream);
+/* Softmax of scale * x along the stick dim under a causal mask: row r sees columns
+ * 0 .. (r % period); masked positions come out as exact zeros and are not read.  x, y:
+ * stick images of [rows, cols] attention scores (rows = batch * heads * period).  This is
+ * the masked softmax inside scaled-dot-product attention, which the reference would get as
+ * Inductor's mul / add-mask / softmax decomposition (torch_spyre/_inductor/__init__.py:81-84). */
+int ts_softmax_rows_causal(const void* x, void* y, int64_t rows, int64_t cols, int64_t period,
+                           float scale, void* stream);
 int ts_layernorm_rows(const void* x, const void* weight, const void* bias, void* y, int64_t rows,
                       int64_t cols, float eps, void* stream);
 int ts_rmsnorm_rows(const void* x, const void* weight, void* y, int64_t rows, int64_t cols,
@@ -254,6 +261,27 @@ int64_t ts_reduce_mid_static_max_bytes(void);
 int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch, int64_t M,
                 int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream);
 int ts_gemm_error_state(void);
+
+/* ts_gemm_f16 with explicit image strides and an extra "heads" dim, so that the per-head
+ * matmuls of attention read Q / K / V straight out of the packed [batch, seq, heads*128]
+ * images and write O straight into one: for every head h and batch entry b,
+ *   c_h[b] = a_h[b] x b_h[b]   (same operand conventions as ts_gemm_f16)
+ * where operand X's stick column s of head h starts at X + h*X_head_stride + s*X_stick_stride
+ * (elements) and holds [batch][rows][64].  A stride <= 0 selects the default of a dense
+ * [batch, rows, cols] image.  Stands in for the bmm calls of an attention block
+ * (codegen/inputs/spyre_torch_ops.cpp:297-377). */
+int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_head_stride,
+                   const void* b, int64_t b_stick_stride, int64_t b_head_stride,
+                   const void* bias, void* c, int64_t c_stick_stride, int64_t c_head_stride,
+                   int64_t heads, int64_t batch, int64_t M, int64_t N, int64_t K,
+                   int b_kmajor, int b_batched, void* stream);
+
+/* Rotary position embedding: y = x*cos + rotate_half(x)*sin per head, x / y stick images of
+ * [batch*seq, heads*head_dim], cos / sin stick images of [seq, head_dim]; head_dim must be
+ * 128.  One pass instead of the mul / neg / slice / cat / add programs the reference would
+ * emit (torch_spyre/_inductor/opfuncs.py:49-72, codegen/data_ops.py:490-630). */
+int ts_rotary_f16(const void* x, const void* cos_table, const void* sin_table, void* y,
+                  int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,90 @@
+"""CPU oracle for the Llama-style decoder layer of the benchmark (d_model 4096, 32 heads of
+128, SwiGLU FFN 11008, RMSNorm, rotary, causal attention), written in plain torch from that
+description.  TEST INFRASTRUCTURE ONLY.
+
+It is pinned against the decoder layer class the reference's own (skipped) test names,
+transformers' LlamaDecoderLayer (tests/test_modules.py:28-33,179-211 of the reference), by
+tests/test_llama_oracle_cpu.py: same weights, same input, same output within fp16 tolerance.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass
+class LayerConfig:
+    d_model: int = 4096
+    heads: int = 32
+    ffn: int = 11008
+    eps: float = 1e-5
+    rope_theta: float = 10000.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.d_model // self.heads
+
+
+def make_weights(cfg: LayerConfig, seed: int = 0, dtype=torch.float16):
+    """Random init N(0, 0.02) for the projections, ones (+ N(0,0.02)) for the norm weights."""
+    g = torch.Generator().manual_seed(seed)
+    d, f = cfg.d_model, cfg.ffn
+
+    def w(*shape):
+        return (torch.randn(*shape, generator=g) * 0.02).to(dtype)
+
+    return {
+        "q": w(d, d), "k": w(d, d), "v": w(d, d), "o": w(d, d),
+        "gate": w(f, d), "up": w(f, d), "down": w(d, f),
+        "norm1": (1.0 + torch.randn(d, generator=g) * 0.02).to(dtype),
+        "norm2": (1.0 + torch.randn(d, generator=g) * 0.02).to(dtype),
+    }
+
+
+def rope_tables(seq: int, head_dim: int, theta: float = 10000.0, dtype=torch.float16):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    ang = torch.arange(seq, dtype=torch.float32)[:, None] * inv[None, :]
+    emb = torch.cat((ang, ang), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+def rms_norm(x, weight, eps):
+    xf = x.float()
+    return weight * (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def rotate_half(x):
+    h = x.shape[-1] // 2
+    return torch.cat((-x[..., h:], x[..., :h]), dim=-1)
+
+
+def layer_forward(x: torch.Tensor, w: dict, cfg: LayerConfig) -> torch.Tensor:
+    b, s, d = x.shape
+    hd, nh = cfg.head_dim, cfg.heads
+    cos, sin = rope_tables(s, hd, cfg.rope_theta, x.dtype)
+    h = rms_norm(x, w["norm1"], cfg.eps)
+    q = F.linear(h, w["q"]).view(b, s, nh, hd).transpose(1, 2)
+    k = F.linear(h, w["k"]).view(b, s, nh, hd).transpose(1, 2)
+    v = F.linear(h, w["v"]).view(b, s, nh, hd).transpose(1, 2)
+    c, sn = cos[None, None], sin[None, None]
+    q = q * c + rotate_half(q) * sn
+    k = k * c + rotate_half(k) * sn
+    scores = torch.matmul(q, k.transpose(2, 3)) * (1.0 / math.sqrt(hd))
+    mask = torch.full((s, s), float("-inf"), dtype=torch.float32).triu(1)
+    probs = torch.softmax(scores.float() + mask, dim=-1).to(x.dtype)
+    attn = torch.matmul(probs, v).transpose(1, 2).reshape(b, s, d)
+    x = x + F.linear(attn, w["o"])
+    h = rms_norm(x, w["norm2"], cfg.eps)
+    return x + F.linear(F.silu(F.linear(h, w["gate"])) * F.linear(h, w["up"]), w["down"])
+
+
+def layer_flops(batch: int, seq: int, cfg: LayerConfig, causal: bool = True) -> float:
+    d, f, hd, nh = cfg.d_model, cfg.ffn, cfg.head_dim, cfg.heads
+    tokens = batch * seq
+    proj = 2.0 * tokens * d * d * 4
+    ffn = 2.0 * tokens * d * f * 3
+    attn = 2.0 * 2.0 * batch * nh * seq * seq * hd * (0.5 if causal else 1.0)
+    return proj + ffn + attn

@@ -43,7 +43,8 @@ __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
 struct GemmParams {
   __half* c;
   const __half* bias;   // [N] stick image or null
-  uint32_t M, N, K, batch;
+  uint32_t M, N, K, batch, heads;
+  int64_t c_stick_stride, c_head_stride;   // elements
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
@@ -96,7 +97,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (uint32_t tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
         const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
-        const uint32_t b = tile / (P.tiles_n * P.tiles_m);
+        const uint32_t bh = tile / (P.tiles_n * P.tiles_m);
+        const uint32_t b = bh % P.batch, h = bh / P.batch;
         const int bb = P.b_batched ? (int)b : 0;
         for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
@@ -105,14 +107,14 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t full = ptx::smem_u32(&bars->full[s]);
           ptx::mbar_arrive_expect_tx(full, kStageBytes);
           const uint32_t sa = tiles + s * kStageBytes, sb = sa + kABytes;
-          ptx::tma_load_4d(sa, &map_a, full, 0, (int)(tm * BM), (int)b, (int)kb);
+          ptx::tma_load_5d(sa, &map_a, full, 0, (int)(tm * BM), (int)b, (int)kb, (int)h);
           if (P.b_kmajor) {
-            ptx::tma_load_4d(sb, &map_b, full, 0, (int)(tn * BN), bb, (int)kb);
+            ptx::tma_load_5d(sb, &map_b, full, 0, (int)(tn * BN), bb, (int)kb, (int)h);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              ptx::tma_load_4d(sb + j * (BK * 128), &map_b, full, 0, (int)(kb * BK), bb,
-                               (int)(tn * (BN / 64) + j));
+              ptx::tma_load_5d(sb + j * (BK * 128), &map_b, full, 0, (int)(kb * BK), bb,
+                               (int)(tn * (BN / 64) + j), (int)h);
           }
         }
       }
@@ -167,7 +169,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t c_sticks = (P.N + 63) / 64;
     for (uint32_t tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
       const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
-      const uint32_t b = tile / (P.tiles_n * P.tiles_m);
+      const uint32_t bh = tile / (P.tiles_n * P.tiles_m);
+      const uint32_t b = bh % P.batch, h = bh / P.batch;
       const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
@@ -188,7 +191,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
             for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + v * 8);
           }
-          __half* dst = P.c + (((int64_t)stick * P.batch + b) * P.M + row) * kStickHalfs + (col & 63);
+          __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
+                        ((int64_t)b * P.M + row) * kStickHalfs + (col & 63);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             Vec8h o;
@@ -240,17 +244,20 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-// Tensor map over the stick image [sticks][batch][rows][64] of a [batch, rows, cols] fp16
-// tensor; the box is 64 lanes x box_rows rows of one stick column of one batch entry.
+// Tensor map over a stick image addressed as [heads][sticks][batch][rows][64 lanes]: rows are
+// 128 bytes apart, batch entries rows*128 bytes, stick columns and heads at the given element
+// strides.  The box is 64 lanes x box_rows rows of one stick column of one (batch, head).
 bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t batch, uint64_t sticks,
-              uint32_t box_rows) {
+              uint64_t heads, int64_t stick_stride, int64_t head_stride, uint32_t box_rows) {
   EncodeFn fn = encode_fn();
   if (!fn) return false;
-  const cuuint64_t dims[4] = {64, rows, batch, sticks};
-  const cuuint64_t strides[3] = {128, rows * 128, batch * rows * 128};
-  const cuuint32_t box[4] = {64, box_rows, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<void*>(base), dims, strides, box,
+  const cuuint64_t dims[5] = {64, rows, batch, sticks, heads};
+  // a dim of extent 1 still needs a legal stride (multiple of 16 bytes)
+  const cuuint64_t strides[4] = {128, rows * 128, (cuuint64_t)stick_stride * 2,
+                                 (cuuint64_t)(heads > 1 ? head_stride : stick_stride) * 2};
+  const cuuint32_t box[5] = {64, box_rows, 1, 1, 1};
+  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box,
             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -262,50 +269,77 @@ int g_sm_count = 0;
 
 using namespace tsb;
 
-extern "C" int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch,
-                           int64_t M, int64_t N, int64_t K, int b_kmajor, int b_batched,
-                           void* stream) {
-  if (batch < 0 || M < 0 || N < 0 || K < 0) return TS_ERR_INVALID;
-  if (batch == 0 || M == 0 || N == 0) return TS_OK;
+extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_head_stride,
+                              const void* b, int64_t b_stick_stride, int64_t b_head_stride,
+                              const void* bias, void* c, int64_t c_stick_stride,
+                              int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
+                              int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream) {
+  if (heads < 0 || batch < 0 || M < 0 || N < 0 || K < 0) return TS_ERR_INVALID;
+  if (heads == 0 || batch == 0 || M == 0 || N == 0) return TS_OK;
   if (!a || !b || !c) return TS_ERR_INVALID;
   if (((uintptr_t)a | (uintptr_t)b | (uintptr_t)c | (uintptr_t)bias) % 128) return TS_ERR_ALIGNMENT;
   if (K == 0) return TS_ERR_UNSUPPORTED;
-  if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31) || batch >= (1ll << 31))
+  if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31) || batch * heads >= (1ll << 31))
     return TS_ERR_TOO_LARGE;
+  const int64_t ks = ceil_div(K, BK), ns = ceil_div(N, 64);
+  const int64_t bb = b_batched ? batch : 1;
+  // default strides: each operand is the whole stick image of its own [batch, rows, cols] tensor
+  if (a_stick_stride <= 0) a_stick_stride = batch * M * kStickHalfs;
+  if (b_stick_stride <= 0) b_stick_stride = bb * (b_kmajor ? N : K) * kStickHalfs;
+  if (c_stick_stride <= 0) c_stick_stride = batch * M * kStickHalfs;
+  if (heads > 1 && (a_head_stride <= 0 || b_head_stride < 0 || c_head_stride <= 0)) return TS_ERR_INVALID;
+  if ((a_stick_stride | a_head_stride | b_stick_stride | b_head_stride | c_stick_stride | c_head_stride) % 8)
+    return TS_ERR_ALIGNMENT;
   GemmParams P{};
   P.c = (__half*)c;
   P.bias = (const __half*)bias;
-  P.M = (uint32_t)M; P.N = (uint32_t)N; P.K = (uint32_t)K; P.batch = (uint32_t)batch;
+  P.M = (uint32_t)M; P.N = (uint32_t)N; P.K = (uint32_t)K;
+  P.batch = (uint32_t)batch; P.heads = (uint32_t)heads;
+  P.c_stick_stride = c_stick_stride;
+  P.c_head_stride = c_head_stride;
   P.tiles_m = (uint32_t)ceil_div(M, BM);
   P.tiles_n = (uint32_t)ceil_div(N, BN);
-  const int64_t tiles = (int64_t)P.tiles_m * P.tiles_n * batch;
+  const int64_t tiles = (int64_t)P.tiles_m * P.tiles_n * batch * heads;
   if (tiles >= (1ll << 31)) return TS_ERR_TOO_LARGE;
   P.num_tiles = (uint32_t)tiles;
-  P.k_blocks = (uint32_t)ceil_div(K, BK);
+  P.k_blocks = (uint32_t)ks;
   P.b_kmajor = b_kmajor ? 1 : 0;
   P.b_batched = b_batched ? 1 : 0;
 
   CUtensorMap map_a, map_b;
-  const uint64_t bb = b_batched ? (uint64_t)batch : 1;
-  if (!make_map(&map_a, a, (uint64_t)M, (uint64_t)batch, P.k_blocks, BM)) return TS_ERR_CUDA;
-  const bool okb = b_kmajor ? make_map(&map_b, b, (uint64_t)N, bb, P.k_blocks, BN)
-                            : make_map(&map_b, b, (uint64_t)K, bb, (uint64_t)ceil_div(N, 64), BK);
+  if (!make_map(&map_a, a, (uint64_t)M, (uint64_t)batch, (uint64_t)ks, (uint64_t)heads, a_stick_stride,
+                a_head_stride, BM))
+    return TS_ERR_CUDA;
+  // a head stride of 0 shares one B between all heads
+  const uint64_t b_heads = (heads > 1 && b_head_stride > 0) ? (uint64_t)heads : 1;
+  const bool okb = b_kmajor ? make_map(&map_b, b, (uint64_t)N, (uint64_t)bb, (uint64_t)ks, b_heads,
+                                       b_stick_stride, b_head_stride, BN)
+                            : make_map(&map_b, b, (uint64_t)K, (uint64_t)bb, (uint64_t)ns, b_heads,
+                                       b_stick_stride, b_head_stride, BK);
   if (!okb) return TS_ERR_CUDA;
+  if (b_heads == 1 && heads > 1) return TS_ERR_UNSUPPORTED;  // kernel indexes B by head
 
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    kSmemBytes);
     int dev = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   });
+  attr_err = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kSmemBytes);  // per device, idempotent
   if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }
   const uint32_t grid = (uint32_t)std::min<int64_t>(tiles, g_sm_count > 0 ? g_sm_count : 148);
   gemm_f16_kernel<<<grid, kThreads, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, P);
   TSB_CHECK_LAUNCH();
   return TS_OK;
+}
+
+extern "C" int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch,
+                           int64_t M, int64_t N, int64_t K, int b_kmajor, int b_batched,
+                           void* stream) {
+  return ts_gemm_f16_ex(a, 0, 0, b, 0, 0, bias, c, 0, 0, 1, batch, M, N, K, b_kmajor, b_batched,
+                        stream);
 }
 
 // Synchronises the device and reports (and clears) the sticky error word the GEMM

@@ -20,7 +20,7 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 
-enum RowOp { kSoftmax = 0, kLogSoftmax = 1, kLayerNorm = 2, kRmsNorm = 3 };
+enum RowOp { kSoftmax = 0, kLogSoftmax = 1, kLayerNorm = 2, kRmsNorm = 3, kCausalSoftmax = 4 };
 
 struct RowParams {
   const __half* x;
@@ -31,6 +31,9 @@ struct RowParams {
   int ws_log;
   float eps;
   int round_before_weight;
+  // causal softmax: row r attends to columns 0 .. (r % period) of scale * x
+  uint32_t period;
+  float scale;
 };
 
 struct RowCtx {
@@ -71,7 +74,8 @@ __device__ __forceinline__ float ex2_f(float x) {
 template <int K, int OP, bool FULL>
 __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ RowParams P) {
   __shared__ float part[kWarps][4];
-  constexpr bool kSoft = OP == kSoftmax || OP == kLogSoftmax;
+  constexpr bool kSoft = OP == kSoftmax || OP == kLogSoftmax || OP == kCausalSoftmax;
+  constexpr bool kCausal = OP == kCausalSoftmax;
   constexpr float kLog2e = 1.4426950408889634f;
   RowCtx c;
   c.lane = threadIdx.x & 31;
@@ -87,14 +91,21 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
   const int64_t row_off = (int64_t)c.row * kStickHalfs + lv * 8;
   const int64_t stick_stride = (int64_t)P.rows * kStickHalfs;
 
+  const uint32_t qpos = kCausal ? c.row % P.period : 0u;  // last column this row may see
   Vec8h raw[K];
 #pragma unroll
   for (int k = 0; k < K; ++k) {
     const uint32_t s = c.ws_idx + k * c.ws;
-    const bool have = FULL || (c.live && s < P.nsticks);
+    bool have = FULL || (c.live && s < P.nsticks);
+    if (kCausal) have = have && s * 64 <= qpos;           // sticks wholly above the diagonal are not read
     raw[k].u = make_uint4(0, 0, 0, 0);
     if (have) raw[k].u = ld_stream_v4(P.x + s * stick_stride + row_off);
-    if (!FULL) {
+    if (kCausal) {
+      const __half ninf = __ushort_as_half((unsigned short)0xFC00);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (!have || s * 64 + lv * 8 + e > qpos) raw[k].h[e] = ninf;
+    } else if (!FULL) {
       const __half fill = kSoft ? __ushort_as_half((unsigned short)0xFC00) : __float2half(0.f);
 #pragma unroll
       for (int e = 0; e < 8; ++e)
@@ -113,16 +124,17 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
       for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, raw[k].h2[j]);
     float m = fmaxf(__low2float(m2), __high2float(m2));
     m = row_allreduce<true>(m, c, part);
-    const float ml = m * kLog2e;
+    const float kmul = kCausal ? P.scale * kLog2e : kLog2e;   // scale > 0: max commutes with it
+    const float ml = m * kmul;
     float sum = 0.f;
 #pragma unroll
     for (int k = 0; k < K; ++k)
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float2 f = __half22float2(raw[k].h2[j]);
-        const float e0 = ex2_f(fmaf(f.x, kLog2e, -ml)), e1 = ex2_f(fmaf(f.y, kLog2e, -ml));
+        const float e0 = ex2_f(fmaf(f.x, kmul, -ml)), e1 = ex2_f(fmaf(f.y, kmul, -ml));
         sum += e0 + e1;
-        if (OP == kSoftmax) {
+        if (OP == kSoftmax || OP == kCausalSoftmax) {
           v[k][2 * j] = e0;
           v[k][2 * j + 1] = e1;
         } else {
@@ -186,7 +198,7 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float r0, r1;
-      if (OP == kSoftmax) {
+      if (OP == kSoftmax || OP == kCausalSoftmax) {
         r0 = v[k][2 * j] * scale;
         r1 = v[k][2 * j + 1] * scale;
       } else if (OP == kLogSoftmax) {
@@ -299,4 +311,15 @@ extern "C" int ts_rmsnorm_rows(const void* x, const void* weight, void* y, int64
   P.eps = eps;
   P.round_before_weight = round_before_weight;
   return launch_rows<kRmsNorm>(P, (cudaStream_t)stream);
+}
+
+extern "C" int ts_softmax_rows_causal(const void* x, void* y, int64_t rows, int64_t cols,
+                                      int64_t period, float scale, void* stream) {
+  RowParams P;
+  const int rc = check_rows(x, y, rows, cols, P);
+  if (rc != TS_OK) return rc > 0 ? TS_OK : rc;
+  if (period < 1 || period > cols || !(scale > 0.f)) return TS_ERR_INVALID;
+  P.period = (uint32_t)period;
+  P.scale = scale;
+  return launch_rows<kCausalSoftmax>(P, (cudaStream_t)stream);
 }

@@ -59,6 +59,8 @@ SIGNATURES = {
     "ts_pointwise_static_count": (ctypes.c_int, []),
     "ts_stream_error_state": (ctypes.c_int, []),
     "ts_softmax_rows": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, vp]),
+    "ts_softmax_rows_causal": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                              ctypes.c_float, vp]),
     "ts_layernorm_rows": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_float, vp]),
     "ts_rmsnorm_rows": (ctypes.c_int, [vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_float,
@@ -72,6 +74,12 @@ SIGNATURES = {
     "ts_gemm_f16": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                    ctypes.c_int64, ctypes.c_int, ctypes.c_int, vp]),
     "ts_gemm_error_state": (ctypes.c_int, []),
+    "ts_gemm_f16_ex": (ctypes.c_int, [vp, ctypes.c_int64, ctypes.c_int64, vp, ctypes.c_int64,
+                                      ctypes.c_int64, vp, vp, ctypes.c_int64, ctypes.c_int64,
+                                      ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                      ctypes.c_int64, ctypes.c_int, ctypes.c_int, vp]),
+    "ts_rotary_f16": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                     ctypes.c_int64, vp]),
     "ts_softmax_mid": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                       ctypes.c_int, vp]),
 }

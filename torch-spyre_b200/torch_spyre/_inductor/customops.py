@@ -98,3 +98,75 @@ def layernormnorm(x: torch.Tensor, mean: torch.Tensor, norm_mean: torch.Tensor,
 @layernormnorm.register_fake
 def _(x, mean, norm_mean, weight=None, bias=None):
     return x.new_empty(x.size())
+
+
+# ---- fused building blocks of a decoder layer -------------------------------------------
+# On spyre tensors these run the fused kernels; on any other device they are defined by the
+# plain torch formula, so a graph naming them means the same thing everywhere.
+
+def _on_spyre(t: torch.Tensor) -> bool:
+    return t.device.type == "spyre"
+
+
+@torch.library.custom_op("spyre::rms_norm", mutates_args=())
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if _on_spyre(x):
+        from .. import ops
+
+        return ops.rms_norm(x, weight, eps, round_before_weight=True)
+    xf = x.float()
+    normed = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return weight * normed.to(x.dtype)
+
+
+@rms_norm.register_fake
+def _(x, weight, eps):
+    return x.new_empty(x.size())
+
+
+@torch.library.custom_op("spyre::rotary", mutates_args=())
+def rotary(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, heads: int) -> torch.Tensor:
+    """x: [batch, seq, heads*head_dim]; cos, sin: [seq, head_dim]."""
+    b, s, width = x.shape
+    hd = width // heads
+    if _on_spyre(x):
+        from .. import ops, stick_ops as K
+
+        out = torch.empty_like(x)
+        with torch.cuda.device(x.device.index or 0):
+            K.rotary(ops._st(x), ops._st(cos), ops._st(sin), b, s, heads, hd, out=ops._st(out))
+        return out
+    xh = x.view(b, s, heads, hd)
+    rot = torch.cat((-xh[..., hd // 2:], xh[..., : hd // 2]), dim=-1)
+    c, sn = cos.view(1, s, 1, hd), sin.view(1, s, 1, hd)
+    return (xh * c + rot * sn).reshape(b, s, width)
+
+
+@rotary.register_fake
+def _(x, cos, sin, heads):
+    return x.new_empty(x.size())
+
+
+@torch.library.custom_op("spyre::causal_attention", mutates_args=())
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int,
+                     scale: float) -> torch.Tensor:
+    """Causal softmax(q k^T * scale) v per head; q, k, v: [batch, seq, heads*head_dim]."""
+    b, s, width = q.shape
+    hd = width // heads
+    if _on_spyre(q):
+        from .. import ops, stick_ops as K
+
+        out = torch.empty_like(q)
+        with torch.cuda.device(q.device.index or 0):
+            K.causal_attention(ops._st(q), ops._st(k), ops._st(v), b, s, heads, scale, out=ops._st(out))
+        return out
+    qh, kh, vh = (t.view(b, s, heads, hd).transpose(1, 2) for t in (q, k, v))
+    scores = torch.matmul(qh, kh.transpose(2, 3)) * scale
+    mask = torch.full((s, s), float("-inf"), dtype=torch.float32).triu(1)
+    probs = torch.softmax(scores.float() + mask, dim=-1).to(q.dtype)
+    return torch.matmul(probs, vh).transpose(1, 2).reshape(b, s, width)
+
+
+@causal_attention.register_fake
+def _(q, k, v, heads, scale):
+    return q.new_empty(q.size())

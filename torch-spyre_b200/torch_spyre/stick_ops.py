@@ -383,3 +383,46 @@ def matmul(a: StickTensor, b: StickTensor, bias: Optional[StickTensor] = None,
                                 _stream())
     _abi.check(rc, "ts_gemm_f16")
     return out
+
+
+# ---- attention pieces -------------------------------------------------------------
+
+def rotary(x: StickTensor, cos: StickTensor, sin: StickTensor, batch: int, seq: int, heads: int,
+           head_dim: int = 128, out: Optional[StickTensor] = None) -> StickTensor:
+    """x: [batch, seq, heads*head_dim]; cos / sin: [seq, head_dim]."""
+    out = out or empty(x.shape, x.dtype, x.image.device)
+    rc = _abi.lib().ts_rotary_f16(x.ptr(), cos.ptr(), sin.ptr(), out.ptr(), batch, seq, heads,
+                                  head_dim, _stream())
+    _abi.check(rc, "ts_rotary_f16")
+    return out
+
+
+def causal_attention(q: StickTensor, k: StickTensor, v: StickTensor, batch: int, seq: int,
+                     heads: int, scale: float, out: Optional[StickTensor] = None,
+                     scores: Optional[torch.Tensor] = None) -> StickTensor:
+    """Causal scaled-dot-product attention over packed [batch, seq, heads*128] q / k / v images.
+
+    Three launches for all heads together: scores = q k^T (tcgen05 GEMM reading the heads out
+    of the packed images), masked softmax in place, out = probs v written straight into the
+    packed output image.  `scores` is scratch of heads*batch*seq*seq fp16 elements."""
+    hd = 128
+    dev = q.image.device
+    rows = batch * seq
+    out = out or empty((batch, seq, heads * hd), torch.float16, dev)
+    if scores is None:
+        scores = torch.empty(heads * rows * seq, dtype=torch.float16, device=dev)
+    packed_stick, packed_head = rows * 64, 2 * rows * 64          # q / k / v / out images
+    sc_stick, sc_head = heads * rows * 64, rows * 64              # scores as [heads*batch*seq, seq]
+    lib = _abi.lib()
+    rc = lib.ts_gemm_f16_ex(q.ptr(), packed_stick, packed_head, k.ptr(), packed_stick, packed_head,
+                            None, scores.data_ptr(), sc_stick, sc_head, heads, batch, seq, seq, hd,
+                            1, 1, _stream())
+    _abi.check(rc, "ts_gemm_f16_ex (q k^T)")
+    rc = lib.ts_softmax_rows_causal(scores.data_ptr(), scores.data_ptr(), heads * rows, seq, seq,
+                                    float(scale), _stream())
+    _abi.check(rc, "ts_softmax_rows_causal")
+    rc = lib.ts_gemm_f16_ex(scores.data_ptr(), sc_stick, sc_head, v.ptr(), packed_stick, packed_head,
+                            None, out.ptr(), packed_stick, packed_head, heads, batch, seq, hd, seq,
+                            0, 1, _stream())
+    _abi.check(rc, "ts_gemm_f16_ex (probs v)")
+    return out
