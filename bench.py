@@ -326,6 +326,57 @@ def make_workload(name: str, dev, scale_rows=None):
                     l2="operands 1.5 GiB, far larger than L2", cpu_step=cpu_step,
                     sample="one batch entry [1,2048,4096]x[1,4096,4096] per CPU step (1/32 of the job)",
                     check=check)
+    if name == "llama_layer":
+        import torch_spyre  # noqa: F401
+        from examples.llama_layer import LlamaStyleLayer
+        from oracle import llama_ref as LR
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        cfg = LR.LayerConfig()
+        batch, seq = max(1, (scale_rows or 8) // world), 2048   # the batch of 8 is sharded over the ranks
+        w = LR.make_weights(cfg)
+        cos, sin = LR.rope_tables(seq, cfg.head_dim)
+        sdev = torch.device("spyre", dev.index)
+        layer = LlamaStyleLayer({k: v.to(sdev) for k, v in w.items()}, cfg.heads, cfg.eps,
+                                cos.to(sdev), sin.to(sdev))
+        compiled = torch.compile(layer)
+        x1 = (torch.randn(1, seq, cfg.d_model, generator=torch.Generator().manual_seed(0))).half()
+        xh = x1.repeat(batch, 1, 1).pin_memory()
+        xd = xh.to(sdev)
+        compiled(xd)  # compile once, outside every timed region
+
+        def step_dev():
+            compiled(xd)
+
+        def step_e2e():
+            return compiled(xh.to(sdev)).cpu()
+
+        def cpu_step():
+            return LR.layer_forward(x1[:, :512], w, cfg)
+
+        def check():
+            got = step_e2e()[batch - 1, :64]
+            want = LR.layer_forward(x1[:, :64], w, cfg)[0]      # causal: a prefix depends on itself only
+            # A whole layer at full width (K up to 11008, ~10 fp16 roundings deep): two fp16
+            # evaluations that round in different places agree to a few fp16 ulps of the
+            # output scale, not element by element at atol 1e-3.  Require that all but 1 % of
+            # the elements meet rtol 1e-2 / atol 5e-3 and that none is off by more than 3e-2.
+            diff = (got.float() - want.float()).abs()
+            bad = diff > (5e-3 + 1e-2 * want.float().abs())
+            if bad.float().mean() > 0.01 or diff.max() > 3e-2:
+                raise AssertionError(f"layer parity: {bad.float().mean():.4f} of elements out of "
+                                     f"tolerance, max abs diff {diff.max():.4f}")
+            if K._abi.lib().ts_gemm_error_state() != 0:
+                raise AssertionError("GEMM kernel gave up on an internal wait")
+
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0,
+                    flops=LR.layer_flops(batch, seq, cfg, causal=True),
+                    cpu_flops=LR.layer_flops(1, 512, cfg, causal=True), scaling="strong",
+                    h2d=xh.numel() * 2, d2h=xh.numel() * 2, launches=20,
+                    desc=f"Llama-style decoder layer through torch.compile on spyre: d_model 4096, 32 heads x 128, "
+                         f"SwiGLU 11008, RMSNorm, rotary, causal attention, batch {batch} x seq {seq} per GPU, "
+                         "causal-useful flops (BASELINE configs[4])",
+                    l2="activations and weights (> 1 GiB) far larger than L2", cpu_step=cpu_step,
+                    sample="oracle layer on [1, 512, 4096] per CPU step", check=check)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -579,7 +630,8 @@ def main():
             "metric": ("fp16 GEMM TFLOP/s" if is_flops else "achieved GB/s (algorithmic bytes / time)"),
             "value": per_gpu * world,
             "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True,
+            "scaling": wl.get("scaling", "weak"),
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": wl["desc"], "l2": wl["l2"],
                        "launch": ("CUDA graph of one ring period" if (wl.get("graph_period") and not args.no_graph)
@@ -599,7 +651,8 @@ def main():
         if not args.no_cpu_baseline and world == 1:
             med, n = time_cpu(wl["cpu_step"])
             scale = wl.get("cpu_scale", 1.0)
-            line["cpu_baseline"] = {"value": work / scale / med / 1e9, "unit": unit,
+            cpu_work = wl["cpu_flops"] / 1e3 if "cpu_flops" in wl else work / scale
+            line["cpu_baseline"] = {"value": cpu_work / med / 1e9, "unit": unit,
                                     "cores": torch.get_num_threads(),
                                     "kind": wl.get("cpu_kind", "reference"),
                                     "sample": f"{wl['sample']}; median of {n} runs; "
