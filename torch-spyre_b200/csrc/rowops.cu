@@ -135,8 +135,10 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
         const float e0 = ex2_f(fmaf(f.x, kmul, -ml)), e1 = ex2_f(fmaf(f.y, kmul, -ml));
         sum += e0 + e1;
         if (OP == kSoftmax || OP == kCausalSoftmax) {
-          v[k][2 * j] = e0;
-          v[k][2 * j + 1] = e1;
+          // keep exp(x - max) packed in fp16 in place of x: half the registers of an fp32
+          // copy, hence twice the resident warps; costs one extra fp16 rounding (the result
+          // is within 1 ulp of rounding once)
+          raw[k].h2[j] = __floats2half2_rn(e0, e1);
         } else {
           v[k][2 * j] = f.x - m;
           v[k][2 * j + 1] = f.y - m;
@@ -199,8 +201,9 @@ __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ R
     for (int j = 0; j < 4; ++j) {
       float r0, r1;
       if (OP == kSoftmax || OP == kCausalSoftmax) {
-        r0 = v[k][2 * j] * scale;
-        r1 = v[k][2 * j + 1] * scale;
+        const float2 e = __half22float2(raw[k].h2[j]);
+        r0 = e.x * scale;
+        r1 = e.y * scale;
       } else if (OP == kLogSoftmax) {
         r0 = v[k][2 * j] - lse;
         r1 = v[k][2 * j + 1] - lse;
