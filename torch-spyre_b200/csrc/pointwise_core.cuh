@@ -514,6 +514,28 @@ __device__ __forceinline__ float add_f16(float acc, __half h) {
   return acc;
 }
 
+// Two fp32 lanes per instruction (sm_100 packed fp32): halves the issue slots the
+// multiply by log2(e) and the accumulation cost.
+__device__ __forceinline__ float2 mul_f32x2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;"
+      : "=l"(reinterpret_cast<uint64_t&>(d))
+      : "l"(reinterpret_cast<const uint64_t&>(a)), "l"(reinterpret_cast<const uint64_t&>(b)));
+  return d;
+}
+__device__ __forceinline__ float ex2_f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 template <int RED>
 __device__ __forceinline__ float red_identity() {
   return RED == TS_RED_SUM ? 0.f : (RED == TS_RED_MAX ? -INFINITY : INFINITY);
@@ -637,7 +659,19 @@ __global__ void __launch_bounds__(kThreads, (CLS == kClsAllGeneric ? 1 : 4)) row
       if (!FULL && !ctx.live[u]) continue;
       const uint32_t col = ctx.s[u] * kStickHalfs + ctx.lv * 8;
       float t = red_identity<RED>();
-      if (RED == TS_RED_SUM && !kFuseTail && FULL) {
+      if (RED == TS_RED_SUM && kFuseTail && kLastOp == TS_PW_EXP && FULL) {
+        // sum of e^x: same values as the generic branch below, added pairwise
+        float2 t2 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float2 x = mul_f32x2(__half22float2(R.acc[u][j]),
+                               make_float2(1.4426950408889634f, 1.4426950408889634f));
+          x.x = ex2_f(x.x);
+          x.y = ex2_f(x.y);
+          t2 = add_f32x2(t2, x);
+        }
+        t = t2.x + t2.y;
+      } else if (RED == TS_RED_SUM && !kFuseTail && FULL) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           t = add_f16(add_f16(t, __low2half(R.acc[u][j])), __high2half(R.acc[u][j]));

@@ -42,6 +42,8 @@ struct CopyPlan {
   // walks kUnitsPerThread steps of `kstep` indices along dim `kd`.
   int log_t0, log_t1, kd;
   uint32_t kstep;
+  // transpose_tiles: which of dims 0 / 1 the CTA walks its kSubTiles tiles along
+  int sub_dim;
 };
 
 template <int UNIT>
@@ -149,8 +151,8 @@ copy_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src, cha
 }
 
 // ---------------------------------------------------------------------------
-// 64x64 tiles of 2-byte elements; a CTA walks kSubTiles of them along dim 0.  smem
-// holds a tile as [row = dim-1 index][col = dim-0 index], 32-bit words, pitch 33 words
+// 64x64 tiles of 2-byte elements; a CTA takes kSubTiles of them along the longer of
+// dims 0 and 1.  smem holds a tile as [row = dim-1 index][col = dim-0 index], 32-bit words, pitch 33 words
 // so that both phases are free of bank conflicts.
 constexpr int kTT = 64;
 constexpr int kSubTiles = 4;
@@ -176,13 +178,13 @@ __device__ __forceinline__ int valid_run(const CopyPlan& p, const int64_t* vsum,
 }
 
 template <bool TO_DEVICE, bool VEC_IN, bool VEC_OUT, bool CHECKS>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src,
                 char* __restrict__ dst) {
-  __shared__ uint32_t tile[2][kTT * kPitchWords];
+  __shared__ uint32_t tile[kSubTiles][kTT * kPitchWords];
   const TileBase b = decode_tile<CHECKS>(p, blockIdx.x);
-  const int rem_b = (int)min((uint32_t)kTT, p.size[1] - b.o1);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int sd = p.sub_dim;
   // phase 1 role: row (dim 1) and 16-byte vector (dim 0)
   const int row1 = threadIdx.x >> 3, vec1 = threadIdx.x & 7;
   // phase 2 role: word column (two dim-0 indices) and group of 8 dim-1 indices
@@ -191,18 +193,21 @@ transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src
   const char* sp0 = src + b.soff + (int64_t)row1 * p.sbytes[1] + vec1 * 16;
   const int64_t srow32 = 32 * p.sbytes[1];
   char* dp0 = dst + b.doff + (int64_t)(2 * pcol) * p.dbytes[0] + grp * 16;
+  // byte and index steps from one sub-tile to the next
+  const int64_t sub_s = (int64_t)kTT * p.sbytes[sd], sub_d = (int64_t)kTT * p.dbytes[sd];
+  const int step_a = sd == 0 ? kTT : 0, step_b = sd == 1 ? kTT : 0;
+  // extent left in this CTA's first sub-tile (may exceed one tile)
+  const int left_a = (int)(p.size[0] - b.o0), left_b = (int)(p.size[1] - b.o1);
 
-#pragma unroll 1
+  // Phase 1: every load of the CTA's sub-tiles is issued before the first use, so the
+  // sub-tiles' rows (adjacent in memory when they lie along dim 0) reach DRAM together.
+  uint32_t w[kSubTiles][2][4];
+#pragma unroll
   for (int sub = 0; sub < kSubTiles; ++sub) {
-    const uint32_t a0 = b.o0 + sub * kTT;
-    if (a0 >= p.size[0]) break;
-    const int rem_a = (int)min((uint32_t)kTT, p.size[0] - a0);
-    uint32_t* tl = tile[sub & 1];
-    // Phase 1: rows along dim 1, 16-byte vectors along dim 0.
+    const int rem_a = left_a - sub * step_a, rem_b = left_b - sub * step_b;
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const int row = row1 + k * 32;
-      uint32_t w[4] = {0, 0, 0, 0};
       int na = rem_a - vec1 * 8;
       na = na < 0 ? 0 : (na > 8 ? 8 : na);
       if (row >= rem_b) na = 0;
@@ -210,31 +215,44 @@ transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src
         int64_t vs[kMaxChecks];
 #pragma unroll
         for (int c = 0; c < kMaxChecks; ++c)
-          vs[c] = b.v[c] + (int64_t)row * p.vmul[c][1] + (int64_t)(sub * kTT + vec1 * 8) * p.vmul[c][0];
+          vs[c] = b.v[c] + (int64_t)(sub * step_b + row) * p.vmul[c][1] +
+                  (int64_t)(sub * step_a + vec1 * 8) * p.vmul[c][0];
         na = min(na, valid_run(p, vs, 0));
       }
-      const char* sp = sp0 + k * srow32 + (int64_t)sub * (kTT * 2);
+      const char* sp = sp0 + k * srow32 + sub * sub_s;
+      uint32_t(&q)[4] = w[sub][k];
+      q[0] = q[1] = q[2] = q[3] = 0;
       if (VEC_IN && na == 8) {
-        const uint4 q = ld_stream_v4(sp);
-        w[0] = q.x; w[1] = q.y; w[2] = q.z; w[3] = q.w;
+        const uint4 v = ld_stream_v4(sp);
+        q[0] = v.x; q[1] = v.y; q[2] = v.z; q[3] = v.w;
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           if (j < na) {
             const uint32_t e = *reinterpret_cast<const uint16_t*>(sp + 2 * j);
-            w[j >> 1] |= e << ((j & 1) * 16);
+            q[j >> 1] |= e << ((j & 1) * 16);
           }
         }
       }
-      uint32_t* tp = &tl[row * kPitchWords + vec1 * 4];
-      tp[0] = w[0]; tp[1] = w[1]; tp[2] = w[2]; tp[3] = w[3];
     }
-    __syncthreads();  // (the other smem buffer is still being read by slower warps)
-
-    // Phase 2: output rows along dim 0 (two per thread), 8 consecutive dim-1 indices each.
-    uint32_t w[8];
+  }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) w[j] = tl[(8 * grp + j) * kPitchWords + pcol];
+  for (int sub = 0; sub < kSubTiles; ++sub) {
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      uint32_t* tp = &tile[sub][(row1 + k * 32) * kPitchWords + vec1 * 4];
+      tp[0] = w[sub][k][0]; tp[1] = w[sub][k][1]; tp[2] = w[sub][k][2]; tp[3] = w[sub][k][3];
+    }
+  }
+  __syncthreads();
+
+  // Phase 2: output rows along dim 0 (two per thread), 8 consecutive dim-1 indices each.
+#pragma unroll
+  for (int sub = 0; sub < kSubTiles; ++sub) {
+    const int rem_a = left_a - sub * step_a, rem_b = left_b - sub * step_b;
+    uint32_t t[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) t[j] = tile[sub][(8 * grp + j) * kPitchWords + pcol];
     int nb = rem_b - grp * 8;
     nb = nb < 0 ? 0 : (nb > 8 ? 8 : nb);
 #pragma unroll
@@ -246,16 +264,17 @@ transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src
         int64_t vs[kMaxChecks];
 #pragma unroll
         for (int c = 0; c < kMaxChecks; ++c)
-          vs[c] = b.v[c] + (int64_t)(sub * kTT + a) * p.vmul[c][0] + (int64_t)(grp * 8) * p.vmul[c][1];
+          vs[c] = b.v[c] + (int64_t)(sub * step_a + a) * p.vmul[c][0] +
+                  (int64_t)(sub * step_b + grp * 8) * p.vmul[c][1];
         n = min(n, valid_run(p, vs, 1));
       }
       const uint32_t sel = half ? 0x7632u : 0x5410u;
       uint4 q;
-      q.x = __byte_perm(w[0], w[1], sel);
-      q.y = __byte_perm(w[2], w[3], sel);
-      q.z = __byte_perm(w[4], w[5], sel);
-      q.w = __byte_perm(w[6], w[7], sel);
-      char* dp = dp0 + (int64_t)(sub * kTT + half) * p.dbytes[0];
+      q.x = __byte_perm(t[0], t[1], sel);
+      q.y = __byte_perm(t[2], t[3], sel);
+      q.z = __byte_perm(t[4], t[5], sel);
+      q.w = __byte_perm(t[6], t[7], sel);
+      char* dp = dp0 + sub * sub_d + (int64_t)half * p.dbytes[0];
       if (VEC_OUT && n == 8) {
         st_global_v4(dp, q);
       } else {
@@ -455,8 +474,9 @@ int run(const Request& rq, cudaStream_t st) {
       if (k != 0 && plan.sbytes[k] % 16) vin = false;
       if (k != 1 && plan.dbytes[k] % 16) vout = false;
     }
-    plan.tile[0] = kTT * kSubTiles;
-    plan.tile[1] = kTT;
+    plan.sub_dim = plan.size[0] >= plan.size[1] ? 0 : 1;   // walk along the longer tiled dim
+    plan.tile[0] = kTT * (plan.sub_dim == 0 ? kSubTiles : 1);
+    plan.tile[1] = kTT * (plan.sub_dim == 1 ? kSubTiles : 1);
     uint64_t ntiles;
     if (!count_tiles(ntiles)) return TS_ERR_TOO_LARGE;
     return rq.to_device
