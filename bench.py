@@ -136,6 +136,8 @@ def make_workload(name: str, dev, scale_rows=None):
 
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=alg,
                     h2d=rows * cols * 2 + 2 * cols * 2, d2h=rows * 2, launches=1,
+                    # ncu, one launch at this size: 134,266,112 B read + 4,761,600 B written
+                    traffic=139027712 if (rows, cols) == (8192, 8192) else None,
                     graph_period=ring,
                     desc=f"exp(x*a+b).sum(-1), x fp16 [{rows},{cols}] (BASELINE configs[1])",
                     l2=f"ring of {ring} x buffers ({ring * rows * cols * 2 >> 20} MiB) > L2",
@@ -181,6 +183,9 @@ def make_workload(name: str, dev, scale_rows=None):
 
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=2 * rows * cols * 2 + cols * 2,
                     h2d=rows * cols * 2, d2h=rows * cols * 2, launches=1,
+                    # ncu, one launch at this size: 134,248,704 B read + 77,152,000 B written
+                    # (the rest of the output was still in L2 when the kernel ended)
+                    traffic=211400704 if (rows, cols) == (8192, 8192) else None,
                     graph_period=ring,
                     desc=f"pointwise x + b (b broadcast along rows), fp16 [{rows},{cols}]",
                     l2=f"ring of {ring} input and output buffers ({2 * ring * rows * cols * 2 >> 20} MiB) > L2",
@@ -222,6 +227,9 @@ def make_workload(name: str, dev, scale_rows=None):
 
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=2 * rows * cols * 2,
                     h2d=rows * cols * 2, d2h=rows * cols * 2, launches=1,
+                    # ncu at [16384, 4096]: 134,235,648 B read + 79,373,312 B written (part of
+                    # the output still in L2), scaled by rows
+                    traffic=int(213608960 * rows / 16384) if cols == 4096 else None,
                     graph_period=ring if rows == 256 else 0,
                     desc=f"softmax(dim=-1) fp16 [{rows},{cols}]" +
                          (" (BASELINE configs[0])" if rows == 256 else " (configs[0] scaled along rows)"),
@@ -278,6 +286,9 @@ def make_workload(name: str, dev, scale_rows=None):
 
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=4 * nbytes,
                     h2d=nbytes, d2h=nbytes, launches=2,
+                    # ncu at [16, 2048, 4096], one direction: 268.45 MB read + 213.6 MB written
+                    # (contiguous) / 213.3 MB (permuted), scaled by the outer extent
+                    traffic=int((482078208 if not permuted else 481772544) * shape[0] / 16),
                     desc=f"stick relayout fp16 {list(shape)} host strides {list(host.stride())}, "
                          "to sticks and back (BASELINE configs[2])",
                     l2="1 GiB tensors, far larger than L2", cpu_step=cpu_step, cpu_scale=8.0,
@@ -321,6 +332,8 @@ def make_workload(name: str, dev, scale_rows=None):
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0,
                     flops=2.0 * batch * m * k * n, cpu_scale=float(batch),
                     h2d=(ah.numel() + bh.numel()) * 2, d2h=ch.numel() * 2, launches=1,
+                    # ncu at batch 4: 281,354,752 B read + 50,876,416 B written, scaled by batch
+                    traffic=int(332231168 * batch / 4) if (m, k, n) == (2048, 4096, 4096) else None,
                     desc=f"bmm fp16 [{batch},{m},{k}] x [{batch},{k},{n}], fp32 accumulate "
                          "(BASELINE configs[3])",
                     l2="operands 1.5 GiB, far larger than L2", cpu_step=cpu_step,
@@ -458,7 +471,7 @@ def run_reference(args, rank, world):
             "ms_per_step": dt * 1e3 * scale, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f16", "data": "synthetic",
             "config": {"workload": wl["desc"]},
-            "cpu_baseline": {"value": gbs, "unit": unit, "cores": cores, "kind": "reference",
+            "cpu_baseline": {"value": gbs, "unit": unit, "cores": cores, "kind": "port",
                              "sample": wl["sample"] + "; torch CPU eager / C oracle on host cores"},
             "e2e": {"value": gbs, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -511,6 +524,9 @@ def make_workload_cpu(name):
 
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=2 * rows * cols * 2 + cols * 2,
                     h2d=rows * cols * 2, d2h=rows * cols * 2, launches=1,
+                    # ncu, one launch at this size: 134,248,704 B read + 77,152,000 B written
+                    # (the rest of the output was still in L2 when the kernel ended)
+                    traffic=211400704 if (rows, cols) == (8192, 8192) else None,
                     graph_period=ring,
                     desc=f"pointwise x + b (b broadcast along rows), fp16 [{rows},{cols}]",
                     l2=f"ring of {ring} input and output buffers ({2 * ring * rows * cols * 2 >> 20} MiB) > L2",
@@ -639,7 +655,8 @@ def main():
                        "sharding": f"{world} x the per-GPU workload, rows sharded, no collective"},
             "roofline": {"bound": "tensor" if is_flops else "hbm", "achieved": per_gpu,
                          "peak": tflops_peak if is_flops else hbm, "unit": unit,
-                         "frac": per_gpu / (tflops_peak if is_flops else hbm), "traffic": None,
+                         "frac": per_gpu / (tflops_peak if is_flops else hbm),
+                         "traffic": wl.get("traffic"),
                          "peak_source": which + (" (bf16 cuBLAS burst)" if is_flops else " (copy)")},
             "gpu_launches": wl["launches"] * args.steps,
             "clocks": clocks,
@@ -654,7 +671,7 @@ def main():
             cpu_work = wl["cpu_flops"] / 1e3 if "cpu_flops" in wl else work / scale
             line["cpu_baseline"] = {"value": cpu_work / med / 1e9, "unit": unit,
                                     "cores": torch.get_num_threads(),
-                                    "kind": wl.get("cpu_kind", "reference"),
+                                    "kind": wl.get("cpu_kind", "port"),
                                     "sample": f"{wl['sample']}; median of {n} runs; "
                                               "torch CPU eager / C oracle on the host cores"}
         print(json.dumps(line))
