@@ -283,6 +283,20 @@ int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_head_stride,
 int ts_rotary_f16(const void* x, const void* cos_table, const void* sin_table, void* y,
                   int64_t batch, int64_t seq, int64_t heads, int64_t head_dim, void* stream);
 
+/* Causal scaled-dot-product attention in one kernel: out = softmax(q k^T * scale + causal mask) v
+ * per head.  q, k, v, out are the packed stick images of [batch*seq, heads*head_dim] that the
+ * projection GEMMs produce / consume (head h = stick columns 2h, 2h+1); head_dim must be 128 and
+ * seq a multiple of 128 (TS_ERR_UNSUPPORTED otherwise: use ts_gemm_f16_ex +
+ * ts_softmax_rows_causal).  The score matrix stays on the SM.  The reference has no attention
+ * kernel; this stands in for the bmm / where / _softmax / bmm programs its compiled path would
+ * emit for torch.nn.functional.scaled_dot_product_attention (tests/test_modules.py:178-211 is
+ * the skipped test that would exercise them).
+ *
+ * ts_attention_error_state: like ts_gemm_error_state, for this kernel's bounded waits. */
+int ts_attention_causal_f16(const void* q, const void* k, const void* v, void* out, int64_t batch,
+                            int64_t seq, int64_t heads, int64_t head_dim, float scale, void* stream);
+int ts_attention_error_state(void);
+
 #ifdef __cplusplus
 }
 #endif

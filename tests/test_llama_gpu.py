@@ -33,16 +33,55 @@ def test_rotary(b, s, heads):
     assert_close(got, torch.ops.spyre.rotary(x, cos, sin, heads))
 
 
-@pytest.mark.parametrize("b,s,heads", [(1, 64, 1), (2, 256, 4), (1, 200, 2), (2, 320, 3)])
+@pytest.mark.parametrize("b,s,heads", [(1, 64, 1), (2, 256, 4), (1, 200, 2), (2, 320, 3),
+                                       (1, 128, 1), (1, 384, 2), (3, 1024, 5), (1, 2048, 2)])
 def test_causal_attention(b, s, heads):
     q, k, v = rnd(b, s, heads * 128, seed=1), rnd(b, s, heads * 128, seed=2), rnd(b, s, heads * 128, seed=3)
     scale = 1 / math.sqrt(128)
     got = torch.ops.spyre.causal_attention(q.to(DEV), k.to(DEV), v.to(DEV), heads, scale).cpu()
     torch.cuda.synchronize()
     assert _abi.lib().ts_gemm_error_state() == 0
+    assert _abi.lib().ts_attention_error_state() == 0
     qh, kh, vh = (t.view(b, s, heads, 128).transpose(1, 2).float() for t in (q, k, v))
     ref = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale)
     assert_close(got, ref.transpose(1, 2).reshape(b, s, -1).half(), atol=2e-3)
+
+
+def test_fused_attention_peaked_scores():
+    """Scores large enough that the running maximum changes from key tile to key tile and the
+    softmax is nearly one-hot.  The one-kernel path keeps scores in fp32, so it must meet the
+    oracle's tolerance; the three-launch path (fp16 scores in memory) is only required to be
+    no closer to the fp32 reference than that rounding allows."""
+    from torch_spyre import stick_ops as K
+
+    b, s, heads = 2, 512, 3
+    q, k, v = rnd(b, s, heads * 128, seed=4, scale=3.0), rnd(b, s, heads * 128, seed=5, scale=3.0), \
+        rnd(b, s, heads * 128, seed=6)
+    scale = 1 / math.sqrt(128)
+    args = [t.to(DEV) for t in (q, k, v)]
+    fused = torch.ops.spyre.causal_attention(*args, heads, scale).cpu()
+    K.fused_attention = False
+    try:
+        unfused = torch.ops.spyre.causal_attention(*args, heads, scale).cpu()
+    finally:
+        K.fused_attention = True
+    assert _abi.lib().ts_attention_error_state() == 0
+    qh, kh, vh = (t.view(b, s, heads, 128).transpose(1, 2).float() for t in (q, k, v))
+    ref = torch.nn.functional.scaled_dot_product_attention(qh, kh, vh, is_causal=True, scale=scale)
+    ref = ref.transpose(1, 2).reshape(b, s, -1)
+    assert_close(fused, ref.half(), atol=2e-3)
+    assert (fused.float() - ref).abs().max() <= (unfused.float() - ref).abs().max() + 1e-3
+
+
+def test_attention_rejects_unsupported_shapes():
+    lib = _abi.lib()
+    buf = torch.zeros(1 << 16, dtype=torch.float16, device="cuda")
+    p = buf.data_ptr()
+    assert lib.ts_attention_causal_f16(p, p, p, p, 1, 100, 1, 128, 0.1, None) == _abi.TS_ERR_UNSUPPORTED
+    assert lib.ts_attention_causal_f16(p, p, p, p, 1, 128, 1, 64, 0.1, None) == _abi.TS_ERR_UNSUPPORTED
+    assert lib.ts_attention_causal_f16(p, None, p, p, 1, 128, 1, 128, 0.1, None) == _abi.TS_ERR_INVALID
+    assert lib.ts_attention_causal_f16(p + 2, p, p, p, 1, 128, 1, 128, 0.1, None) == _abi.TS_ERR_ALIGNMENT
+    assert lib.ts_attention_causal_f16(p, p, p, p, 0, 128, 1, 128, 0.1, None) == 0
 
 
 def test_rms_norm_op():

@@ -1,0 +1,404 @@
+// Causal scaled-dot-product attention as one kernel on the 5th-generation tensor cores:
+// the score matrix never leaves the SM (tensor memory -> registers -> shared memory).
+//
+// Operands are the packed stick images the projection GEMMs write, [batch*seq, heads*128]:
+// head h owns stick columns 2h and 2h+1, so a 128-row x 128-wide tile of Q, K or V is two
+// 128-row x 128-byte boxes, which TMA drops into shared memory in exactly the swizzled form
+// tcgen05.mma reads (Q, K: K-major; V: MN-major).  The reference has no attention kernel
+// (its decoder-layer test, tests/test_modules.py:178-211, is skipped); this stands in for the
+// bmm / where / _softmax / bmm sequence its compiled path would emit.
+//
+// One CTA works on one (batch, head, 128-query tile) at a time and walks the key tiles up to
+// the diagonal.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 (one thread per query row)
+// run the online softmax:
+//     S_j = Q K_j^T            (tensor memory, two buffers so S_{j+1} is computed during softmax j)
+//     m' = max(m, rowmax S_j); P_j = exp2((S_j - m') c) -> fp16 -> shared memory
+//     R  = (R + PV_{j-1}) * exp2((m - m') c)             (running output, registers)
+//     PV_j = P_j V_j           (tensor memory)
+// and at the end O = (R + PV_last) / rowsum.  Every wait is bounded; on a timeout the CTA
+// raises a flag, every role leaves its loops, tensor memory is released and a sticky error
+// word is set.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_map.cuh"
+
+namespace tsb {
+namespace {
+
+constexpr int kTile = 128;                      // queries per tile = keys per tile = head dim
+constexpr int kAttnThreads = 192;
+constexpr int kBlockBytes = kTile * 128;        // one 128-row x 64-lane box: 16 KiB
+constexpr int kTileBytes = 2 * kBlockBytes;     // 32 KiB
+constexpr int kKvStages = 2;
+// Q | K stages | V stages | P
+constexpr int kAttnSmem = (2 + 2 * kKvStages) * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kAttnTmemCols = 512;         // S0 | S1 | PV | (unused)
+constexpr long long kAttnWaitLimit = 4000000000ll;  // ~2 s of SM clocks
+
+__device__ int g_attn_error;  // sticky: set when a bounded wait gave up
+
+struct AttnParams {
+  __half* out;
+  uint32_t batch, seq, heads, q_tiles, num_items;
+  int64_t stick_stride;   // elements between stick columns of the packed images
+  float scale_log2;       // softmax scale * log2(e)
+};
+
+struct AttnBars {
+  uint64_t q_full, q_empty, k_full[kKvStages], k_empty[kKvStages], v_full[kKvStages],
+      v_empty[kKvStages], s_full[2], p_full, pv_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// Heaviest tiles (most key tiles) first, so that the static round-robin over CTAs balances.
+__device__ __forceinline__ void decode_item(const AttnParams& P, uint32_t item, uint32_t& qt,
+                                            uint32_t& b, uint32_t& h) {
+  const uint32_t bh_count = P.batch * P.heads;
+  qt = P.q_tiles - 1 - item / bh_count;
+  const uint32_t bh = item % bh_count;
+  b = bh % P.batch;
+  h = bh / P.batch;
+}
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t sq = base, sk = base + kTileBytes, sv = sk + kKvStages * kTileBytes,
+                 sp = sv + kKvStages * kTileBytes;
+  uint8_t* gen_p = gen_base + (sp - base);
+  AttnBars* bars = reinterpret_cast<AttnBars*>(gen_base + (2 + 2 * kKvStages) * kTileBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 1);
+    for (int s = 0; s < kKvStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->k_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->k_empty[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->v_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->v_empty[s]), 1);
+    }
+    ptx::mbar_init(ptx::smem_u32(&bars->s_full[0]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->s_full[1]), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->p_full), 4);   // one arrival per softmax warp
+    ptx::mbar_init(ptx::smem_u32(&bars->pv_full), 1);
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kAttnTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t g = 0, item_n = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x, ++item_n) {
+        uint32_t qt, b, h;
+        decode_item(P, item, qt, b, h);
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_empty), (item_n & 1) ^ 1, abort_flag,
+                                    kAttnWaitLimit)) break;
+        const uint32_t qf = ptx::smem_u32(&bars->q_full);
+        ptx::mbar_arrive_expect_tx(qf, kTileBytes);
+        ptx::tma_load_5d(sq, &map_q, qf, 0, (int)(qt * kTile), (int)b, (int)(2 * h), 0);
+        ptx::tma_load_5d(sq + kBlockBytes, &map_q, qf, 0, (int)(qt * kTile), (int)b, (int)(2 * h + 1), 0);
+        for (uint32_t j = 0; j <= qt; ++j, ++g) {
+          const uint32_t s = g % kKvStages, ph = (g / kKvStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_empty[s]), ph ^ 1, abort_flag,
+                                      kAttnWaitLimit)) { ok = false; break; }
+          const uint32_t kf = ptx::smem_u32(&bars->k_full[s]);
+          ptx::mbar_arrive_expect_tx(kf, kTileBytes);
+          ptx::tma_load_5d(sk + s * kTileBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sk + s * kTileBytes + kBlockBytes, &map_k, kf, 0, (int)(j * kTile), (int)b,
+                           (int)(2 * h + 1), 0);
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_empty[s]), ph ^ 1, abort_flag,
+                                      kAttnWaitLimit)) { ok = false; break; }
+          const uint32_t vf = ptx::smem_u32(&bars->v_full[s]);
+          ptx::mbar_arrive_expect_tx(vf, kTileBytes);
+          ptx::tma_load_5d(sv + s * kTileBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sv + s * kTileBytes + kBlockBytes, &map_v, vf, 0, (int)(j * kTile), (int)b,
+                           (int)(2 * h + 1), 0);
+        }
+      }
+      // Let copies still in flight land before the CTA can exit (matters after an abort only:
+      // otherwise the MMA warp has consumed every tile).
+      if (*abort_flag) {
+        const uint32_t issued = g < (uint32_t)kKvStages ? g : (uint32_t)kKvStages;
+        for (uint32_t k = 0; k < issued; ++k) {
+          const uint32_t t = g - 1 - k, s = t % kKvStages, ph = (t / kKvStages) & 1;
+          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_full[s]), ph, abort_flag, kAttnWaitLimit / 16);
+          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_full[s]), ph, abort_flag, kAttnWaitLimit / 16);
+        }
+        if (item_n > 0)
+          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, abort_flag,
+                                 kAttnWaitLimit / 16);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc_s = ptx::idesc_f16_f32(kTile, kTile, 0, 0);    // Q K^T: both K-major
+      const uint32_t idesc_pv = ptx::idesc_f16_f32(kTile, kTile, 0, 1);   // P V: V is MN-major
+      uint32_t g = 0, item_n = 0;
+      bool ok = true;
+      // S_t = Q K_t^T into score buffer t & 1
+      auto issue_scores = [&](uint32_t t) -> bool {
+        const uint32_t s = t % kKvStages, ph = (t / kKvStages) & 1;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_full[s]), ph, abort_flag, kAttnWaitLimit))
+          return false;
+        ptx::tc_fence_after_sync();
+        const uint32_t kb = sk + s * kTileBytes;
+#pragma unroll
+        for (int k16 = 0; k16 < kTile / 16; ++k16) {
+          const uint32_t off = (k16 >> 2) * kBlockBytes + (k16 & 3) * 32;
+          ptx::umma_f16(tmem_base + (t & 1) * kTile, ptx::smem_desc_sw128(sq + off, 16, 1024),
+                        ptx::smem_desc_sw128(kb + off, 16, 1024), idesc_s, k16 != 0);
+        }
+        ptx::umma_commit(ptx::smem_u32(&bars->s_full[t & 1]));
+        ptx::umma_commit(ptx::smem_u32(&bars->k_empty[s]));
+        return true;
+      };
+      for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x, ++item_n) {
+        uint32_t qt, b, h;
+        decode_item(P, item, qt, b, h);
+        const uint32_t n = qt + 1;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), item_n & 1, abort_flag,
+                                    kAttnWaitLimit)) break;
+        ptx::tc_fence_after_sync();
+        if (!issue_scores(g)) break;
+        if (n == 1) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
+        for (uint32_t j = 0; j < n; ++j) {
+          const uint32_t t = g + j;
+          if (j + 1 < n) {
+            if (!issue_scores(t + 1)) { ok = false; break; }
+            if (j + 2 == n) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
+          }
+          const uint32_t s = t % kKvStages, ph = (t / kKvStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->p_full), t & 1, abort_flag, kAttnWaitLimit) ||
+              !ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_full[s]), ph, abort_flag, kAttnWaitLimit)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t vb = sv + s * kTileBytes;
+#pragma unroll
+          for (int k16 = 0; k16 < kTile / 16; ++k16) {
+            // P, K-major: 16 keys = 32 bytes along the swizzled row, 64-key blocks 16 KiB apart.
+            // V, MN-major: 16 keys = 16 rows = 2048 bytes; the two 64-wide d blocks are 16 KiB
+            // apart (leading offset), 8-row groups 1024 bytes apart.
+            const uint64_t da = ptx::smem_desc_sw128(sp + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
+            const uint64_t db = ptx::smem_desc_sw128(vb + k16 * 2048, kBlockBytes, 1024);
+            ptx::umma_f16(tmem_base + 2 * kTile, da, db, idesc_pv, k16 != 0);
+          }
+          ptx::umma_commit(ptx::smem_u32(&bars->pv_full));
+          ptx::umma_commit(ptx::smem_u32(&bars->v_empty[s]));
+        }
+        g += n;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax + output (warps 2..5)
+    const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
+    const uint32_t row = quarter * 32 + lane;       // query row within the tile
+    const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
+    const float c = P.scale_log2;
+    uint8_t* prow = gen_p + row * 128;
+    uint32_t g = 0;
+    bool ok = true;
+    for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x) {
+      uint32_t qt, b, h;
+      decode_item(P, item, qt, b, h);
+      const uint32_t n = qt + 1;
+      float R[kTile];
+#pragma unroll
+      for (int i = 0; i < kTile; ++i) R[i] = 0.f;
+      float m = -1e30f, l = 0.f;
+      for (uint32_t j = 0; j < n; ++j) {
+        const uint32_t t = g + j;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->s_full[t & 1]), (t >> 1) & 1, abort_flag,
+                                    kAttnWaitLimit)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t ts = lane_addr + (t & 1) * kTile;
+        const bool diag = j == qt;
+        // pass 1: row maximum
+        float mx = m;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(ts + ch * 32, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float s = __uint_as_float(r[i]);
+            if (!diag || (uint32_t)(ch * 32 + i) <= row) mx = fmaxf(mx, s);
+          }
+        }
+        const float alpha = ex2f((m - mx) * c);
+        const float mc = mx * c;
+        // running output: fold in the previous key tile's P V, rescale to the new maximum
+        if (j > 0) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->pv_full), (t - 1) & 1, abort_flag,
+                                      kAttnWaitLimit)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(lane_addr + 2 * kTile + ch * 32, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) R[ch * 32 + i] = (R[ch * 32 + i] + __uint_as_float(r[i])) * alpha;
+          }
+        }
+        l *= alpha;
+        // pass 2: P = exp2(S c - m c) as fp16 into the swizzled K-major operand tile
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(ts + ch * 32, r);
+          ptx::tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2f(fmaf(__uint_as_float(r[i]), c, -mc));
+            float p1 = ex2f(fmaf(__uint_as_float(r[i + 1]), c, -mc));
+            if (diag) {
+              if ((uint32_t)(ch * 32 + i) > row) p0 = 0.f;
+              if ((uint32_t)(ch * 32 + i + 1) > row) p1 = 0.f;
+            }
+            l += p0 + p1;
+            const __half2 hp = __floats2half2_rn(p0, p1);
+            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+          uint8_t* blk = prow + (ch >> 1) * kBlockBytes;
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint32_t chunk = (uint32_t)((ch & 1) * 4 + v) ^ (row & 7);
+            *reinterpret_cast<uint4*>(blk + chunk * 16) =
+                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
+          }
+        }
+        m = mx;
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full));
+      }
+      if (!ok) break;
+      // last key tile's P V, normalisation, store into the packed output image
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->pv_full), (g + n - 1) & 1, abort_flag,
+                                  kAttnWaitLimit)) break;
+      ptx::tc_fence_after_sync();
+      const float inv = 1.f / l;
+      const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(lane_addr + 2 * kTile + ch * 32, r);
+        ptx::tmem_ld_wait();
+        __half* dst = P.out + (int64_t)(2 * h + (ch >> 1)) * P.stick_stride + grow * kStickHalfs +
+                      (ch & 1) * 32;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          Vec8h o;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = v * 8 + 2 * e;
+            o.h2[e] = __floats2half2_rn((R[ch * 32 + i] + __uint_as_float(r[i])) * inv,
+                                        (R[ch * 32 + i + 1] + __uint_as_float(r[i + 1])) * inv);
+          }
+          st_global_v4(dst + v * 8, o.u);
+        }
+      }
+      ptx::tc_fence_before_sync();
+      g += n;
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kAttnTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
+}
+
+int g_attn_sm_count = 0;
+
+}  // namespace
+}  // namespace tsb
+
+using namespace tsb;
+
+extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void* v, void* out,
+                                       int64_t batch, int64_t seq, int64_t heads, int64_t head_dim,
+                                       float scale, void* stream) {
+  if (batch < 0 || seq < 0 || heads < 0) return TS_ERR_INVALID;
+  if (batch == 0 || seq == 0 || heads == 0) return TS_OK;
+  if (!q || !k || !v || !out) return TS_ERR_INVALID;
+  if (head_dim != kTile || seq % kTile != 0) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 128) return TS_ERR_ALIGNMENT;
+  if (!(scale > 0.f)) return TS_ERR_INVALID;
+  const int64_t rows = batch * seq, q_tiles = seq / kTile;
+  const int64_t items = q_tiles * batch * heads;
+  if (rows >= (1ll << 31) || items >= (1ll << 31) || heads * 2 >= (1ll << 31)) return TS_ERR_TOO_LARGE;
+  AttnParams P{};
+  P.out = (__half*)out;
+  P.batch = (uint32_t)batch; P.seq = (uint32_t)seq; P.heads = (uint32_t)heads;
+  P.q_tiles = (uint32_t)q_tiles; P.num_items = (uint32_t)items;
+  P.stick_stride = rows * kStickHalfs;
+  P.scale_log2 = scale * 1.4426950408889634f;
+  CUtensorMap mq, mk, mv;
+  if (!make_stick_map(&mq, q, (uint64_t)seq, (uint64_t)batch, (uint64_t)(2 * heads), 1, P.stick_stride, 0, kTile) ||
+      !make_stick_map(&mk, k, (uint64_t)seq, (uint64_t)batch, (uint64_t)(2 * heads), 1, P.stick_stride, 0, kTile) ||
+      !make_stick_map(&mv, v, (uint64_t)seq, (uint64_t)batch, (uint64_t)(2 * heads), 1, P.stick_stride, 0, kTile))
+    return TS_ERR_CUDA;
+  if (g_attn_sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_attn_sm_count = n;
+  }
+  const cudaError_t e = cudaFuncSetAttribute(attention_causal_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+  if (e != cudaSuccess) { note_cuda_error(e); return TS_ERR_CUDA; }
+  const uint32_t grid = (uint32_t)std::min<int64_t>(items, g_attn_sm_count > 0 ? g_attn_sm_count : 148);
+  attention_causal_kernel<<<grid, kAttnThreads, kAttnSmem, (cudaStream_t)stream>>>(mq, mk, mv, P);
+  TSB_CHECK_LAUNCH();
+  return TS_OK;
+}
+
+// Synchronises the device and reports (and clears) the sticky error word the attention kernel
+// sets when one of its bounded waits gave up.  Returns 0, 1 or an error code.
+extern "C" int ts_attention_error_state(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return TS_ERR_CUDA;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+  }
+  return v;
+}

@@ -24,6 +24,7 @@
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
+#include "tma_map.cuh"
 
 namespace tsb {
 namespace {
@@ -226,42 +227,6 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 // ---- host side --------------------------------------------------------------------
 
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-EncodeFn encode_fn() {
-  static EncodeFn fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeFn)p;
-  });
-  return fn;
-}
-
-// Tensor map over a stick image addressed as [heads][sticks][batch][rows][64 lanes]: rows are
-// 128 bytes apart, batch entries rows*128 bytes, stick columns and heads at the given element
-// strides.  The box is 64 lanes x box_rows rows of one stick column of one (batch, head).
-bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t batch, uint64_t sticks,
-              uint64_t heads, int64_t stick_stride, int64_t head_stride, uint32_t box_rows) {
-  EncodeFn fn = encode_fn();
-  if (!fn) return false;
-  const cuuint64_t dims[5] = {64, rows, batch, sticks, heads};
-  // a dim of extent 1 still needs a legal stride (multiple of 16 bytes)
-  const cuuint64_t strides[4] = {128, rows * 128, (cuuint64_t)stick_stride * 2,
-                                 (cuuint64_t)(heads > 1 ? head_stride : stick_stride) * 2};
-  const cuuint32_t box[5] = {64, box_rows, 1, 1, 1};
-  const cuuint32_t estr[5] = {1, 1, 1, 1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<void*>(base), dims, strides, box,
-            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
 int g_sm_count = 0;
 
 }  // namespace
@@ -307,14 +272,14 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
   P.b_batched = b_batched ? 1 : 0;
 
   CUtensorMap map_a, map_b;
-  if (!make_map(&map_a, a, (uint64_t)M, (uint64_t)batch, (uint64_t)ks, (uint64_t)heads, a_stick_stride,
+  if (!make_stick_map(&map_a, a, (uint64_t)M, (uint64_t)batch, (uint64_t)ks, (uint64_t)heads, a_stick_stride,
                 a_head_stride, BM))
     return TS_ERR_CUDA;
   // a head stride of 0 shares one B between all heads
   const uint64_t b_heads = (heads > 1 && b_head_stride > 0) ? (uint64_t)heads : 1;
-  const bool okb = b_kmajor ? make_map(&map_b, b, (uint64_t)N, (uint64_t)bb, (uint64_t)ks, b_heads,
+  const bool okb = b_kmajor ? make_stick_map(&map_b, b, (uint64_t)N, (uint64_t)bb, (uint64_t)ks, b_heads,
                                        b_stick_stride, b_head_stride, BN)
-                            : make_map(&map_b, b, (uint64_t)K, (uint64_t)bb, (uint64_t)ns, b_heads,
+                            : make_stick_map(&map_b, b, (uint64_t)K, (uint64_t)bb, (uint64_t)ns, b_heads,
                                        b_stick_stride, b_head_stride, BK);
   if (!okb) return TS_ERR_CUDA;
   if (b_heads == 1 && heads > 1) return TS_ERR_UNSUPPORTED;  // kernel indexes B by head

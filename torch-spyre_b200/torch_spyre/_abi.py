@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libspyre_b200.so")
 
 TS_OK = 0
+TS_ERR_INVALID, TS_ERR_UNSUPPORTED, TS_ERR_CUDA, TS_ERR_ALIGNMENT, TS_ERR_TOO_LARGE = -1, -2, -3, -4, -5
 TS_MAX_DIMS = 8
 
 c_i64p = ctypes.POINTER(ctypes.c_int64)
@@ -82,6 +83,9 @@ SIGNATURES = {
                                      ctypes.c_int64, vp]),
     "ts_softmax_mid": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                       ctypes.c_int, vp]),
+    "ts_attention_causal_f16": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64,
+                                               ctypes.c_int64, ctypes.c_int64, ctypes.c_float, vp]),
+    "ts_attention_error_state": (ctypes.c_int, []),
 }
 
 _lib = None

@@ -397,18 +397,28 @@ def rotary(x: StickTensor, cos: StickTensor, sin: StickTensor, batch: int, seq: 
     return out
 
 
+# False routes every shape through the three-launch path (kept for comparison in tests / bench)
+fused_attention = True
+
+
 def causal_attention(q: StickTensor, k: StickTensor, v: StickTensor, batch: int, seq: int,
                      heads: int, scale: float, out: Optional[StickTensor] = None,
                      scores: Optional[torch.Tensor] = None) -> StickTensor:
     """Causal scaled-dot-product attention over packed [batch, seq, heads*128] q / k / v images.
 
-    Three launches for all heads together: scores = q k^T (tcgen05 GEMM reading the heads out
-    of the packed images), masked softmax in place, out = probs v written straight into the
-    packed output image.  `scores` is scratch of heads*batch*seq*seq fp16 elements."""
+    seq a multiple of 128: one fused kernel (scores stay on the SM).  Otherwise three launches
+    for all heads together: scores = q k^T (tcgen05 GEMM reading the heads out of the packed
+    images), masked softmax in place, out = probs v written straight into the packed output
+    image; `scores` is scratch of heads*batch*seq*seq fp16 elements for that path."""
     hd = 128
     dev = q.image.device
     rows = batch * seq
     out = out or empty((batch, seq, heads * hd), torch.float16, dev)
+    if seq % 128 == 0 and fused_attention:
+        rc = _abi.lib().ts_attention_causal_f16(q.ptr(), k.ptr(), v.ptr(), out.ptr(), batch, seq,
+                                                heads, hd, float(scale), _stream())
+        _abi.check(rc, "ts_attention_causal_f16")
+        return out
     if scores is None:
         scores = torch.empty(heads * rows * seq, dtype=torch.float16, device=dev)
     packed_stick, packed_head = rows * 64, 2 * rows * 64          # q / k / v / out images
