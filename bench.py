@@ -6,7 +6,8 @@
 Default workload ("fused"): y = exp(x*a + b).sum(-1), x fp16 [8192, 8192] N(0,1),
 a and b fp16 [8192] U(-1,1), one fused kernel per step over inputs resident in
 HBM as stick images.  A step reads a different x buffer of a ring larger than L2.
-Other workloads: softmax, softmax_scaled, relayout, relayout_permuted.
+Other workloads: softmax, softmax_scaled, pointwise, relayout, relayout_permuted, bmm, attention,
+llama_layer.
 Under torchrun every rank runs the same per-GPU workload on its own shard of
 rows (weak scaling, no collective on the data path).
 """
@@ -384,12 +385,57 @@ def make_workload(name: str, dev, scale_rows=None):
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0,
                     flops=LR.layer_flops(batch, seq, cfg, causal=True),
                     cpu_flops=LR.layer_flops(1, 512, cfg, causal=True), scaling="strong",
-                    h2d=xh.numel() * 2, d2h=xh.numel() * 2, launches=20,
+                    h2d=xh.numel() * 2, d2h=xh.numel() * 2, launches=18,
                     desc=f"Llama-style decoder layer through torch.compile on spyre: d_model 4096, 32 heads x 128, "
                          f"SwiGLU 11008, RMSNorm, rotary, causal attention, batch {batch} x seq {seq} per GPU, "
                          "causal-useful flops (BASELINE configs[4])",
                     l2="activations and weights (> 1 GiB) far larger than L2", cpu_step=cpu_step,
                     sample="oracle layer on [1, 512, 4096] per CPU step", check=check)
+    if name == "attention":
+        # config 5's attention block on its own: packed [B*S, H*128] q / k / v images in, packed out
+        import math
+        batch, seq, heads, hd = scale_rows or 8, 2048, 32, 128
+        g = torch.Generator().manual_seed(0)
+        qh, kh, vh = (torch.randn(batch, seq, heads * hd, generator=g).half().pin_memory() for _ in range(3))
+        scale = 1.0 / math.sqrt(hd)
+        qs, ks, vs = (K.copy_host_to_sticks(t) for t in (qh, kh, vh))
+        out = K.empty((batch, seq, heads * hd), torch.float16, dev)
+        out_host = torch.empty_like(qh).pin_memory()
+
+        def step_dev():
+            K.causal_attention(qs, ks, vs, batch, seq, heads, scale, out=out)
+
+        def step_e2e():
+            q2, k2, v2 = (K.copy_host_to_sticks(t) for t in (qh, kh, vh))
+            o = K.causal_attention(q2, k2, v2, batch, seq, heads, scale)
+            K.copy_sticks_to_host(o, out_host)
+            torch.cuda.synchronize()
+            return out_host
+
+        def ref(nb, nh):
+            q4, k4, v4 = (t[:nb, :, :nh * hd].reshape(nb, seq, nh, hd).transpose(1, 2).float()
+                          for t in (qh, kh, vh))
+            o = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, scale=scale)
+            return o.transpose(1, 2).reshape(nb, seq, nh * hd).half()
+
+        def cpu_step():
+            return ref(1, 4)
+
+        def check():
+            got = step_e2e()[:1, :, :4 * hd]
+            math_ref.assert_close(got, ref(1, 4), atol=2e-3)
+            if K._abi.lib().ts_attention_error_state() != 0:
+                raise AssertionError("attention kernel gave up on an internal wait")
+
+        flops = 4.0 * batch * heads * hd * (seq * (seq + 1) / 2)   # causal-useful: keys <= query
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0, flops=flops,
+                    cpu_flops=flops / (batch * heads / 4), h2d=3 * qh.numel() * 2, d2h=qh.numel() * 2,
+                    launches=1,
+                    desc=f"causal attention fp16, batch {batch} x seq {seq} x {heads} heads x {hd}, "
+                         "causal-useful flops (the attention block of BASELINE configs[4])",
+                    l2="q, k, v, out 512 MiB, larger than L2", cpu_step=cpu_step,
+                    sample="torch CPU scaled_dot_product_attention (fp32) on 1 batch entry x 4 heads",
+                    check=check)
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -558,6 +604,51 @@ def make_workload_cpu(name):
                     cpu_scale=32.0, alg_bytes=0,
                     desc="bmm fp16 [32,2048,4096] x [32,4096,4096] (BASELINE configs[3])",
                     sample="one batch entry per CPU step (1/32 of the job)")
+    if name == "attention":
+        # config 5's attention block on its own: packed [B*S, H*128] q / k / v images in, packed out
+        import math
+        batch, seq, heads, hd = scale_rows or 8, 2048, 32, 128
+        g = torch.Generator().manual_seed(0)
+        qh, kh, vh = (torch.randn(batch, seq, heads * hd, generator=g).half().pin_memory() for _ in range(3))
+        scale = 1.0 / math.sqrt(hd)
+        qs, ks, vs = (K.copy_host_to_sticks(t) for t in (qh, kh, vh))
+        out = K.empty((batch, seq, heads * hd), torch.float16, dev)
+        out_host = torch.empty_like(qh).pin_memory()
+
+        def step_dev():
+            K.causal_attention(qs, ks, vs, batch, seq, heads, scale, out=out)
+
+        def step_e2e():
+            q2, k2, v2 = (K.copy_host_to_sticks(t) for t in (qh, kh, vh))
+            o = K.causal_attention(q2, k2, v2, batch, seq, heads, scale)
+            K.copy_sticks_to_host(o, out_host)
+            torch.cuda.synchronize()
+            return out_host
+
+        def ref(nb, nh):
+            q4, k4, v4 = (t[:nb, :, :nh * hd].reshape(nb, seq, nh, hd).transpose(1, 2).float()
+                          for t in (qh, kh, vh))
+            o = torch.nn.functional.scaled_dot_product_attention(q4, k4, v4, is_causal=True, scale=scale)
+            return o.transpose(1, 2).reshape(nb, seq, nh * hd).half()
+
+        def cpu_step():
+            return ref(1, 4)
+
+        def check():
+            got = step_e2e()[:1, :, :4 * hd]
+            math_ref.assert_close(got, ref(1, 4), atol=2e-3)
+            if K._abi.lib().ts_attention_error_state() != 0:
+                raise AssertionError("attention kernel gave up on an internal wait")
+
+        flops = 4.0 * batch * heads * hd * (seq * (seq + 1) / 2)   # causal-useful: keys <= query
+        return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0, flops=flops,
+                    cpu_flops=flops / (batch * heads / 4), h2d=3 * qh.numel() * 2, d2h=qh.numel() * 2,
+                    launches=1,
+                    desc=f"causal attention fp16, batch {batch} x seq {seq} x {heads} heads x {hd}, "
+                         "causal-useful flops (the attention block of BASELINE configs[4])",
+                    l2="q, k, v, out 512 MiB, larger than L2", cpu_step=cpu_step,
+                    sample="torch CPU scaled_dot_product_attention (fp32) on 1 batch entry x 4 heads",
+                    check=check)
     raise SystemExit(f"unknown workload {name}")
 
 

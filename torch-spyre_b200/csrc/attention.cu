@@ -12,12 +12,14 @@
 // the diagonal.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 (one thread per query row)
 // run the online softmax:
 //     S_j = Q K_j^T            (tensor memory, two buffers so S_{j+1} is computed during softmax j)
-//     m' = max(m, rowmax S_j); P_j = exp2((S_j - m') c) -> fp16 -> shared memory
-//     R  = (R + PV_{j-1}) * exp2((m - m') c)             (running output, registers)
-//     PV_j = P_j V_j           (tensor memory)
-// and at the end O = (R + PV_last) / rowsum.  Every wait is bounded; on a timeout the CTA
-// raises a flag, every role leaves its loops, tensor memory is released and a sticky error
-// word is set.
+//     P_j = exp2((S_j - m) c) -> fp16 -> shared memory (two buffers), l += rowsum P_j
+//     O  += P_j V_j            (accumulated in tensor memory)
+// and at the end out = O / l.  m is the row maximum used as the exponent offset; it is only
+// raised (and O, l rescaled, by the softmax threads through tcgen05.ld/st) when a row's new
+// maximum exceeds it by more than 8 in the exponent, i.e. P stays <= 256, so in steady state
+// the softmax threads never touch O and run a full tile ahead of the P V MMA.  Every wait is
+// bounded; on a timeout the CTA raises a flag, every role leaves its loops, tensor memory is
+// released and a sticky error word is set.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_map.cuh"
@@ -30,9 +32,11 @@ constexpr int kAttnThreads = 192;
 constexpr int kBlockBytes = kTile * 128;        // one 128-row x 64-lane box: 16 KiB
 constexpr int kTileBytes = 2 * kBlockBytes;     // 32 KiB
 constexpr int kKvStages = 2;
-// Q | K stages | V stages | P
-constexpr int kAttnSmem = (2 + 2 * kKvStages) * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
-constexpr uint32_t kAttnTmemCols = 512;         // S0 | S1 | PV | (unused)
+// Q | K stages | V stages | P0 P1
+constexpr int kSmemTiles = 3 + 2 * kKvStages;
+constexpr int kAttnSmem = kSmemTiles * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr uint32_t kAttnTmemCols = 512;         // S0 | S1 | O | (unused)
+constexpr float kRescaleThreshold = 8.f;        // in units of the exponent (log2)
 constexpr long long kAttnWaitLimit = 4000000000ll;  // ~2 s of SM clocks
 
 __device__ int g_attn_error;  // sticky: set when a bounded wait gave up
@@ -46,7 +50,7 @@ struct AttnParams {
 
 struct AttnBars {
   uint64_t q_full, q_empty, k_full[kKvStages], k_empty[kKvStages], v_full[kKvStages],
-      v_empty[kKvStages], s_full[2], p_full, pv_full;
+      v_empty[kKvStages], s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -77,7 +81,7 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const uint32_t sq = base, sk = base + kTileBytes, sv = sk + kKvStages * kTileBytes,
                  sp = sv + kKvStages * kTileBytes;
   uint8_t* gen_p = gen_base + (sp - base);
-  AttnBars* bars = reinterpret_cast<AttnBars*>(gen_base + (2 + 2 * kKvStages) * kTileBytes);
+  AttnBars* bars = reinterpret_cast<AttnBars*>(gen_base + kSmemTiles * kTileBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -90,10 +94,11 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ptx::mbar_init(ptx::smem_u32(&bars->v_full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->v_empty[s]), 1);
     }
-    ptx::mbar_init(ptx::smem_u32(&bars->s_full[0]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->s_full[1]), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->p_full), 4);   // one arrival per softmax warp
-    ptx::mbar_init(ptx::smem_u32(&bars->pv_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->s_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[i]), 4);   // one arrival per softmax warp
+      ptx::mbar_init(ptx::smem_u32(&bars->pv_done[i]), 1);
+    }
     bars->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_q);
@@ -196,7 +201,8 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             if (j + 2 == n) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
           }
           const uint32_t s = t % kKvStages, ph = (t / kKvStages) & 1;
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->p_full), t & 1, abort_flag, kAttnWaitLimit) ||
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->p_full[t & 1]), (t >> 1) & 1, abort_flag,
+                                      kAttnWaitLimit) ||
               !ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_full[s]), ph, abort_flag, kAttnWaitLimit)) {
             ok = false;
             break;
@@ -208,11 +214,12 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             // P, K-major: 16 keys = 32 bytes along the swizzled row, 64-key blocks 16 KiB apart.
             // V, MN-major: 16 keys = 16 rows = 2048 bytes; the two 64-wide d blocks are 16 KiB
             // apart (leading offset), 8-row groups 1024 bytes apart.
-            const uint64_t da = ptx::smem_desc_sw128(sp + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
+            const uint64_t da = ptx::smem_desc_sw128(
+                sp + (t & 1) * kTileBytes + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
             const uint64_t db = ptx::smem_desc_sw128(vb + k16 * 2048, kBlockBytes, 1024);
-            ptx::umma_f16(tmem_base + 2 * kTile, da, db, idesc_pv, k16 != 0);
+            ptx::umma_f16(tmem_base + 2 * kTile, da, db, idesc_pv, (j | (uint32_t)k16) != 0);
           }
-          ptx::umma_commit(ptx::smem_u32(&bars->pv_full));
+          ptx::umma_commit(ptx::smem_u32(&bars->pv_done[t & 1]));
           ptx::umma_commit(ptx::smem_u32(&bars->v_empty[s]));
         }
         g += n;
@@ -224,71 +231,78 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
     const uint32_t row = quarter * 32 + lane;       // query row within the tile
     const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
+    const uint32_t to = lane_addr + 2 * kTile;      // this row of O
     const float c = P.scale_log2;
-    uint8_t* prow = gen_p + row * 128;
+    // the whole warp takes the same decision, since what follows a wait is warp-collective
+    auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag,
+                                                            kAttnWaitLimit)) != 0;
+    };
     uint32_t g = 0;
     bool ok = true;
     for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x) {
       uint32_t qt, b, h;
       decode_item(P, item, qt, b, h);
       const uint32_t n = qt + 1;
-      float R[kTile];
-#pragma unroll
-      for (int i = 0; i < kTile; ++i) R[i] = 0.f;
       float m = -1e30f, l = 0.f;
       for (uint32_t j = 0; j < n; ++j) {
         const uint32_t t = g + j;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->s_full[t & 1]), (t >> 1) & 1, abort_flag,
-                                    kAttnWaitLimit)) { ok = false; break; }
+        if (!warp_wait(&bars->s_full[t & 1], (t >> 1) & 1)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t ts = lane_addr + (t & 1) * kTile;
-        const bool diag = j == qt;
-        // pass 1: row maximum
-        float mx = m;
+        uint32_t r[4][32];
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(ts + ch * 32, r);
-          ptx::tmem_ld_wait();
+        for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld_32x32(ts + ch * 32, r[ch]);
+        ptx::tmem_ld_wait();
+        if (j == qt) {   // diagonal tile: keys after the query do not exist
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float s = __uint_as_float(r[i]);
-            if (!diag || (uint32_t)(ch * 32 + i) <= row) mx = fmaxf(mx, s);
-          }
+          for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if ((uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
         }
-        const float alpha = ex2f((m - mx) * c);
-        const float mc = mx * c;
-        // running output: fold in the previous key tile's P V, rescale to the new maximum
-        if (j > 0) {
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->pv_full), (t - 1) & 1, abort_flag,
-                                      kAttnWaitLimit)) { ok = false; break; }
-          ptx::tc_fence_after_sync();
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[ch][i]));
+        const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        if (j == 0) {
+          m = tile_max;   // O is still empty: nothing to rescale
+        } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
+          // Raise the offset: O and l of this row shrink by alpha.  P V of the previous key
+          // tile must have finished accumulating; the next one starts after our p_full arrival.
+          if (!warp_wait(&bars->pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const float m_new = fmaxf(m, tile_max);
+          const float alpha = ex2f((m - m_new) * c);
+          l *= alpha;
+          m = m_new;
+#pragma unroll 1
           for (int ch = 0; ch < 4; ++ch) {
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(lane_addr + 2 * kTile + ch * 32, r);
+            uint32_t o[32];
+            ptx::tmem_ld_32x32(to + ch * 32, o);
             ptx::tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) R[ch * 32 + i] = (R[ch * 32 + i] + __uint_as_float(r[i])) * alpha;
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ptx::tmem_st_32x32(to + ch * 32, o);
           }
+          ptx::tmem_st_wait();
         }
-        l *= alpha;
-        // pass 2: P = exp2(S c - m c) as fp16 into the swizzled K-major operand tile
+        // the P buffer of this tile was last read by the P V MMA two tiles ago
+        if (!warp_wait(&bars->pv_done[t & 1], ((t >> 1) & 1) ^ 1)) { ok = false; break; }
+        // P = exp2(S c - m c) as fp16 into the swizzled K-major operand tile
+        const float mc = m * c;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        uint8_t* prow = gen_p + (t & 1) * kTileBytes + row * 128;
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(ts + ch * 32, r);
-          ptx::tmem_ld_wait();
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2f(fmaf(__uint_as_float(r[i]), c, -mc));
-            float p1 = ex2f(fmaf(__uint_as_float(r[i + 1]), c, -mc));
-            if (diag) {
-              if ((uint32_t)(ch * 32 + i) > row) p0 = 0.f;
-              if ((uint32_t)(ch * 32 + i + 1) > row) p1 = 0.f;
-            }
-            l += p0 + p1;
+            const float p0 = ex2f(fmaf(__uint_as_float(r[ch][i]), c, -mc));
+            const float p1 = ex2f(fmaf(__uint_as_float(r[ch][i + 1]), c, -mc));
+            sum[(i >> 1) & 3] += p0 + p1;
             const __half2 hp = __floats2half2_rn(p0, p1);
             packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
           }
@@ -300,36 +314,35 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                 make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
           }
         }
-        m = mx;
+        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full));
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[t & 1]));
       }
       if (!ok) break;
-      // last key tile's P V, normalisation, store into the packed output image
-      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->pv_full), (g + n - 1) & 1, abort_flag,
-                                  kAttnWaitLimit)) break;
+      // all key tiles accumulated: normalise and store into the packed output image
+      const uint32_t tl = g + n - 1;
+      if (!warp_wait(&bars->pv_done[tl & 1], (tl >> 1) & 1)) break;
       ptx::tc_fence_after_sync();
       const float inv = 1.f / l;
       const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(lane_addr + 2 * kTile + ch * 32, r);
+        uint32_t o[32];
+        ptx::tmem_ld_32x32(to + ch * 32, o);
         ptx::tmem_ld_wait();
         __half* dst = P.out + (int64_t)(2 * h + (ch >> 1)) * P.stick_stride + grow * kStickHalfs +
                       (ch & 1) * 32;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-          Vec8h o;
+          Vec8h ov;
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const int i = v * 8 + 2 * e;
-            o.h2[e] = __floats2half2_rn((R[ch * 32 + i] + __uint_as_float(r[i])) * inv,
-                                        (R[ch * 32 + i + 1] + __uint_as_float(r[i + 1])) * inv);
+            ov.h2[e] = __floats2half2_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
           }
-          st_global_v4(dst + v * 8, o.u);
+          st_global_v4(dst + v * 8, ov.u);
         }
       }
       ptx::tc_fence_before_sync();
