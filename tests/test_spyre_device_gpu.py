@@ -178,3 +178,44 @@ def test_device_module_on_gpu():
     assert torch.spyre.device_count() >= 1
     assert torch.spyre.current_device() == 0
     torch.spyre.synchronize()
+
+
+def _rnd(*shape, seed=0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)).half()
+
+
+@pytest.mark.parametrize("shapes,dim", [
+    ([(3, 70), (5, 70)], 0), ([(4, 30), (4, 100), (4, 64)], 1), ([(2, 3, 65), (2, 4, 65)], 1),
+    ([(2, 3, 10), (2, 3, 200)], -1), ([(7,), (130,)], 0)])
+def test_cat(shapes, dim):
+    # base-op list of the reference: codegen/inputs/Metadata.yaml (cat), bit-exact data movement
+    ts = [_rnd(*s, seed=i) for i, s in enumerate(shapes)]
+    got = torch.cat([t.to(DEV) for t in ts], dim).cpu()
+    assert torch.equal(got, torch.cat(ts, dim))
+
+
+@pytest.mark.parametrize("dim", [0, 1, 2, -1])
+def test_stack(dim):
+    ts = [_rnd(5, 70, seed=i) for i in range(3)]
+    got = torch.stack([t.to(DEV) for t in ts], dim).cpu()
+    assert torch.equal(got, torch.stack(ts, dim))
+
+
+@pytest.mark.parametrize("shape,diag", [((70, 70), 0), ((3, 40, 100), 1), ((2, 2, 65, 33), -2)])
+def test_tril_triu(shape, diag):
+    x = _rnd(*shape)
+    x[..., 0, -1] = float("inf")          # masked-out values must become exactly zero
+    d = x.to(DEV)
+    assert torch.equal(torch.tril(d, diag).cpu(), torch.tril(x, diag))
+    assert torch.equal(torch.triu(d, diag).cpu(), torch.triu(x, diag))
+
+
+@pytest.mark.parametrize("ord", [2, 1, float("inf")])
+@pytest.mark.parametrize("shape,dim", [((64, 4096), -1), ((5, 70, 33), (1, 2)), ((300, 500), None),
+                                       ((6, 40, 64), 1)])
+def test_vector_norm(ord, shape, dim):
+    x = _rnd(*shape) * (300.0 if ord == 2 and dim == -1 else 1.0)   # squares beyond the fp16 range
+    got = torch.linalg.vector_norm(x.to(DEV), ord, dim).cpu()
+    want = torch.linalg.vector_norm(x.float(), ord, dim)
+    # a fully reduced result is a 1-element 1-D tensor on the device (as 0-dim tensors are)
+    assert_close(got.reshape(want.shape), want.half())

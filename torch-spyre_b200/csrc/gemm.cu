@@ -225,6 +225,200 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_gemm_error, 1);
 }
 
+// ---- the same GEMM on CTA pairs ------------------------------------------------------
+// A cluster of two CTAs computes one 256 x 256 tile: tcgen05.mma cta_group::2 multiplies the
+// 256 rows of A held by the two CTAs (128 each) by a 256-column B tile of which each CTA
+// loads only its half (128 columns), so an SM pulls 32 KiB of operands per 64-k step out of L2
+// instead of 48 KiB, and the ring is 6 stages deep in the same shared memory.  The leader CTA
+// (rank 0) owns the "full" barriers (both CTAs' TMA loads count on them) and issues the MMAs;
+// it signals "stage free" and "accumulator ready" to both CTAs; each CTA drains its own 128
+// accumulator rows.  No multicast anywhere.
+constexpr int kPairStages = 6;
+constexpr int kPairBBytes = (BN / 2) * BK * 2;                 // 16 KiB
+constexpr int kPairStageBytes = kABytes + kPairBBytes;        // 32 KiB per CTA
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+
+struct PairBarriers {
+  uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                     const __grid_constant__ GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t tiles = (raw + 1023u) & ~1023u;
+  uint8_t* gen_tiles = smem_raw + (tiles - raw);
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(gen_tiles + kPairStages * kPairStageBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kPairStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 8);   // 4 epilogue warps in each CTA
+    }
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_a);
+    ptx::prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc_pair(ptx::smem_u32(&bars->tmem_base), kTmemCols);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();   // the peer's barriers are initialised before anything signals them
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+  const uint32_t tiles_m = (P.M + 2 * BM - 1) / (2 * BM);
+  const uint32_t num_tiles = tiles_m * P.tiles_n * P.batch * P.heads;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+        const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % tiles_m;
+        const uint32_t bh = tile / (P.tiles_n * tiles_m);
+        const uint32_t b = bh % P.batch, h = bh / P.batch;
+        const int bb = P.b_batched ? (int)b : 0;
+        for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kPairStages, ph = (it / kPairStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[s]), ph ^ 1, abort_flag,
+                                      kWaitLimit)) { ok = false; break; }
+          const uint32_t full_local = ptx::smem_u32(&bars->full[s]);
+          const uint32_t full_leader = ptx::map_to_cta(full_local, 0);
+          if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * kPairStageBytes);
+          const uint32_t sa = tiles + s * kPairStageBytes, sb = sa + kABytes;
+          ptx::tma_load_5d_pair(sa, &map_a, full_leader, 0, (int)(tm * 2 * BM + rank * BM), (int)b,
+                                (int)kb, (int)h);
+          if (P.b_kmajor) {
+            ptx::tma_load_5d_pair(sb, &map_b, full_leader, 0, (int)(tn * BN + rank * (BN / 2)), bb,
+                                  (int)kb, (int)h);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j)
+              ptx::tma_load_5d_pair(sb + j * (BK * 128), &map_b, full_leader, 0, (int)(kb * BK), bb,
+                                    (int)(tn * (BN / 64) + rank * (BN / 128) + j), (int)h);
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = ptx::idesc_f16_f32(2 * BM, BN, 0, P.b_kmajor ? 0 : 1);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
+        const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_empty[acc]), acc_ph ^ 1, abort_flag,
+                                    kWaitLimit)) break;
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
+          const uint32_t s = it % kPairStages, ph = (it / kPairStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), ph, abort_flag, kWaitLimit)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = tiles + s * kPairStageBytes, sb = sa + kABytes;
+#pragma unroll
+          for (int k16 = 0; k16 < BK / 16; ++k16) {
+            const uint64_t da = ptx::smem_desc_sw128(sa + k16 * 32, 16, 1024);
+            const uint64_t db = P.b_kmajor ? ptx::smem_desc_sw128(sb + k16 * 32, 16, 1024)
+                                           : ptx::smem_desc_sw128(sb + k16 * 2048, BK * 128, 1024);
+            ptx::umma_f16_pair(d_tmem, da, db, idesc, (kb | (uint32_t)k16) != 0);
+          }
+          const uint32_t e = ptx::smem_u32(&bars->empty[s]);
+          ptx::umma_commit_pair(ptx::map_to_cta(e, 0));
+          ptx::umma_commit_pair(ptx::map_to_cta(e, 1));
+        }
+        if (ok) {
+          const uint32_t f = ptx::smem_u32(&bars->acc_full[acc]);
+          ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
+          ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const uint32_t q = warp & 3;
+    uint32_t local_tile = 0;
+    const uint32_t c_sticks = (P.N + 63) / 64;
+    for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+      const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % tiles_m;
+      const uint32_t bh = tile / (P.tiles_n * tiles_m);
+      const uint32_t b = bh % P.batch, h = bh / P.batch;
+      const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
+      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
+                                  kWaitLimit)) break;
+      ptx::tc_fence_after_sync();
+      const uint32_t row = tm * 2 * BM + rank * BM + q * 32 + lane;
+      const bool row_ok = row < P.M;
+      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(taddr + chunk * 32, r);
+        ptx::tmem_ld_wait();
+        const uint32_t col = tn * BN + chunk * 32;
+        const uint32_t stick = col >> 6;
+        if (row_ok && stick < c_sticks) {
+          Vec8h bv[4];
+          if (P.bias) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + v * 8);
+          }
+          __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
+                        ((int64_t)b * P.M + row) * kStickHalfs + (col & 63);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            Vec8h o;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
+              if (P.bias) {
+                x0 += __half2float(bv[v].h[2 * e]);
+                x1 += __half2float(bv[v].h[2 * e + 1]);
+              }
+              o.h2[e] = __floats2half2_rn(x0, x1);
+            }
+            st_global_v4(dst + v * 8, o.u);
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[acc]), 0));
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync_all();   // neither CTA leaves (or frees tensor memory) while the other works
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_gemm_error, 1);
+}
+
 // ---- host side --------------------------------------------------------------------
 
 int g_sm_count = 0;
@@ -271,6 +465,9 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
   P.b_kmajor = b_kmajor ? 1 : 0;
   P.b_batched = b_batched ? 1 : 0;
 
+  // CTA pairs whenever a tile pair has work for both halves
+  static const int pair_env = getenv("TS_GEMM_PAIR") ? atoi(getenv("TS_GEMM_PAIR")) : -1;
+  const bool use_pair = pair_env >= 0 ? pair_env != 0 : M > BM;
   CUtensorMap map_a, map_b;
   if (!make_stick_map(&map_a, a, (uint64_t)M, (uint64_t)batch, (uint64_t)ks, (uint64_t)heads, a_stick_stride,
                 a_head_stride, BM))
@@ -278,7 +475,7 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
   // a head stride of 0 shares one B between all heads
   const uint64_t b_heads = (heads > 1 && b_head_stride > 0) ? (uint64_t)heads : 1;
   const bool okb = b_kmajor ? make_stick_map(&map_b, b, (uint64_t)N, (uint64_t)bb, (uint64_t)ks, b_heads,
-                                       b_stick_stride, b_head_stride, BN)
+                                       b_stick_stride, b_head_stride, use_pair ? BN / 2 : BN)
                             : make_stick_map(&map_b, b, (uint64_t)K, (uint64_t)bb, (uint64_t)ns, b_heads,
                                        b_stick_stride, b_head_stride, BK);
   if (!okb) return TS_ERR_CUDA;
@@ -291,6 +488,17 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
   });
+  if (use_pair) {
+    attr_err = cudaFuncSetAttribute(gemm_f16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kPairSmemBytes);
+    if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }
+    const int64_t tiles2 = (int64_t)ceil_div(M, 2 * BM) * P.tiles_n * batch * heads;
+    const int64_t pairs = std::min<int64_t>(tiles2, (g_sm_count > 0 ? g_sm_count : 148) / 2);
+    gemm_f16_pair_kernel<<<(uint32_t)(2 * pairs), kThreads, kPairSmemBytes, (cudaStream_t)stream>>>(
+        map_a, map_b, P);
+    TSB_CHECK_LAUNCH();
+    return TS_OK;
+  }
   attr_err = cudaFuncSetAttribute(gemm_f16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   kSmemBytes);  // per device, idempotent
   if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }

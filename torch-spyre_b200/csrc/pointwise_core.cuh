@@ -358,7 +358,7 @@ __host__ __device__ constexpr bool is_unary_f32(int op) {
          op == TS_PW_RECIP || op == TS_PW_SIGMOID || op == TS_PW_TANH || op == TS_PW_SILU ||
          op == TS_PW_GELU || op == TS_PW_GELU_TANH || op == TS_PW_SIN || op == TS_PW_COS ||
          op == TS_PW_ERF || op == TS_PW_SIGN || op == TS_PW_LOG1P || op == TS_PW_EXPM1 ||
-         op == TS_PW_SOFTPLUS || op == TS_PW_MISH;
+         op == TS_PW_SOFTPLUS || op == TS_PW_MISH || op == TS_PW_SQUARE;
 }
 __device__ __forceinline__ float unary_f32(int op, float x) {
   switch (op) {
@@ -383,6 +383,7 @@ __device__ __forceinline__ float unary_f32(int op, float x) {
     case TS_PW_EXPM1: return expm1f(x);
     case TS_PW_SOFTPLUS: return softplus_f(x);
     case TS_PW_MISH: return x * tanh_f(softplus_f(x));
+    case TS_PW_SQUARE: return x * x;   // exact in fp32: a sum of squares cannot overflow per term
     default: return x;
   }
 }

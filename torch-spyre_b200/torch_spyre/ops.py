@@ -316,6 +316,119 @@ def _amin(x, dim=(), keepdim=False):
     return _reduce(x, list(dim), "min", keepdim)
 
 
+@_impl("linalg_vector_norm")
+def _vector_norm(x, ord=2, dim=None, keepdim=False, *, dtype=None):
+    """1-, 2- and inf-norms.  fp16 cannot hold the squares of values it can hold, so the 2-norm
+    is taken relative to the largest magnitude: amax * sqrt(mean((x / amax)^2)) * sqrt(N)."""
+    _check_fp16(x)
+    if ord in (float("inf"), 1, 1.0):
+        return _reduce(_unary("ABS", x), dim, "max" if ord == float("inf") else "sum", keepdim)
+    if ord not in (2, 2.0):
+        raise NotImplementedError(f"linalg_vector_norm on spyre: ord={ord}")
+    nd = max(x.dim(), 1)
+    dims = list(range(nd)) if dim is None or len(dim) == 0 else sorted({d % nd for d in dim})
+    shape = list(x.shape) if x.dim() else [1]
+    count = 1
+    for d in dims:
+        count *= shape[d]
+    kept = [1 if i in dims else n for i, n in enumerate(shape)]
+    out_shape = kept if keepdim else ([n for i, n in enumerate(shape) if i not in dims] or [1])
+    if x.numel() == 0 or count == 0:
+        return torch.zeros(out_shape, dtype=x.dtype, device=x.device)
+    x = x if x.dim() else x.reshape(1)
+    amax = _binary("MAX", _reduce(_unary("ABS", x), dims, "max", True), 6e-8)   # never zero
+    rel = _binary("DIV", x, amax)
+    if dims == [nd - 1]:
+        ms = _new(kept, x)
+        with _with_device(x):
+            c = Chain()
+            c.emit("LOAD", c.tensor(_st(rel))).emit("SQUARE")
+            K.run_chain(c, shape, n_outputs=0, reduce="sum", reduce_scale=1.0 / count, keepdim=True,
+                        red_out=_st(ms))
+    else:
+        ms = _reduce(_unary("SQUARE", rel), dims, "sum", True, mean=True)
+    out = _new(kept, x)
+    with _with_device(x):
+        c = Chain()
+        c.emit("LOAD", c.tensor(_st(ms))).emit("SQRT").emit("MUL", c.imm(float(count) ** 0.5))
+        c.emit("MUL", c.tensor(_st(amax))).store(0)
+        K.run_chain(c, kept, outputs=[_st(out)])
+    return out if keepdim else out.reshape(out_shape)
+
+
+# ---- joining and masking ---------------------------------------------------------------
+
+def _cuda_device(t: torch.Tensor) -> torch.device:
+    return torch.device("cuda", t.device.index if t.device.index is not None else 0)
+
+
+@_impl("cat")
+def _cat(tensors, dim=0):
+    """Inputs are unpacked side by side into one row-major scratch tensor (the relayout kernel
+    writes through any strides) which is then laid out as the result: two passes over the data,
+    whatever the number of inputs or the dim."""
+    tensors = [t for t in tensors if not (t.dim() == 1 and t.numel() == 0)]   # legacy empties
+    if not tensors:
+        raise RuntimeError("torch.cat(): expected a non-empty list of Tensors")
+    like = tensors[0]
+    nd = like.dim()
+    if nd == 0:
+        raise RuntimeError("zero-dimensional tensor cannot be concatenated")
+    dim = dim % nd
+    out_shape = list(like.shape)
+    out_shape[dim] = 0
+    for t in tensors:
+        if t.device != like.device or t.dtype != like.dtype:
+            raise RuntimeError("torch.cat on spyre: tensors must share device and dtype")
+        if t.dim() != nd or any(t.shape[i] != like.shape[i] for i in range(nd) if i != dim):
+            raise RuntimeError(f"Sizes of tensors must match except in dimension {dim}")
+        out_shape[dim] += t.shape[dim]
+    out = _new(out_shape, like)
+    if out.numel() == 0:
+        return out
+    with _with_device(like):
+        raw = torch.empty(out_shape, dtype=like.dtype, device=_cuda_device(like))
+        off = 0
+        for t in tensors:
+            n = t.shape[dim]
+            if n:
+                K.from_sticks(_st(t), out=raw.narrow(dim, off, n))
+            off += n
+        K.to_sticks(raw, out=_st(out))
+    return out
+
+
+@_impl("stack")
+def _stack(tensors, dim=0):
+    nd = tensors[0].dim() + 1
+    dim = dim % nd
+    return _cat([t.unsqueeze(dim) for t in tensors], dim)
+
+
+_tri_masks: dict = {}
+
+
+def _tri(x: torch.Tensor, diagonal: int, lower: bool) -> torch.Tensor:
+    """tril / triu as where(mask, x, 0) with a cached fp16 0/1 mask of the last two dims."""
+    _check_fp16(x)
+    if x.dim() < 2:
+        raise RuntimeError("tril / triu: input tensor must have at least 2 dimensions")
+    rows, cols = x.shape[-2], x.shape[-1]
+    key = (rows, cols, int(diagonal), lower, x.device)
+    mask = _tri_masks.get(key)
+    if mask is None:
+        ones = torch.ones(rows, cols, dtype=torch.float16)
+        mask = (torch.tril(ones, diagonal) if lower else torch.triu(ones, diagonal)).to(x.device)
+        if len(_tri_masks) > 16:
+            _tri_masks.clear()
+        _tri_masks[key] = mask
+    return _where(mask, x, 0.0)
+
+
+_impl("tril")(lambda x, diagonal=0: _tri(x, diagonal, True))
+_impl("triu")(lambda x, diagonal=0: _tri(x, diagonal, False))
+
+
 # ---- softmax / norms -------------------------------------------------------------------
 
 def _softmax_impl(x, dim, log):
