@@ -18,6 +18,8 @@
 // TMA->smem ring.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 drain the
 // accumulator (TMEM -> registers -> fp16 -> global).  TMEM holds two 128x256 fp32
 // accumulators so the epilogue of tile i overlaps the main loop of tile i+1.
+// When M > 128 the same roles run on pairs of CTAs (clusters of two, tcgen05
+// cta_group::2, 256 x 256 tiles): see gemm_f16_pair_kernel below.
 // Every wait is bounded; on a timeout the CTA raises a flag, every role leaves its
 // loop, TMEM is released and the host-visible error word is set.
 #include <mutex>
@@ -35,7 +37,8 @@ constexpr int kThreads = 192;
 constexpr int kABytes = BM * BK * 2;          // 16 KiB
 constexpr int kBBytes = BN * BK * 2;          // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kStagingBytes = 4 * 32 * 128;   // epilogue: 32 rows x 128 bytes per warp
+constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
 
@@ -57,6 +60,58 @@ struct Barriers {
   int abort_flag;
 };
 
+// Drains one warp's 32 accumulator rows x BN columns: tensor memory -> registers -> fp16 ->
+// a per-warp shared-memory staging block (32 rows x 128 bytes, 16-byte chunks XOR-swizzled by
+// row so that neither side has bank conflicts) -> global memory with every store instruction
+// covering four whole 128-byte sticks instead of 16 bytes of 32 different ones.
+__device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, uint8_t* stage,
+                                           uint32_t row0, uint32_t col0, uint32_t b, uint32_t h,
+                                           int lane) {
+  const uint32_t c_sticks = (P.N + 63) / 64;
+  const int srow = lane >> 3, piece = lane & 7;
+#pragma unroll 1
+  for (int half = 0; half < BN / 64; ++half) {
+    const uint32_t col = col0 + half * 64;
+    const uint32_t stick = col >> 6;
+    if (stick >= c_sticks) break;   // warp-uniform
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+      uint32_t r[32];
+      ptx::tmem_ld_32x32(taddr + half * 64 + sub * 32, r);
+      ptx::tmem_ld_wait();
+      Vec8h bv[4];
+      if (P.bias) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + sub * 32 + v * 8);
+      }
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        Vec8h o;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
+          if (P.bias) {
+            x0 += __half2float(bv[v].h[2 * e]);
+            x1 += __half2float(bv[v].h[2 * e + 1]);
+          }
+          o.h2[e] = __floats2half2_rn(x0, x1);
+        }
+        *reinterpret_cast<uint4*>(stage + lane * 128 + (((sub * 4 + v) ^ (lane & 7)) * 16)) = o.u;
+      }
+    }
+    __syncwarp();
+    __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
+                  ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + srow;
+      const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
+      if (row0 + rr < P.M) st_global_v4(dst + (int64_t)rr * kStickHalfs, v);
+    }
+    __syncwarp();
+  }
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const __grid_constant__ GemmParams P) {
@@ -64,7 +119,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;               // 1024-byte aligned stage ring
   uint8_t* gen_tiles = smem_raw + (tiles - raw);
-  Barriers* bars = reinterpret_cast<Barriers*>(gen_tiles + kStages * kStageBytes);
+  uint8_t* staging = gen_tiles + kStages * kStageBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(staging + kStagingBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
 
@@ -130,8 +186,20 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
+      // One thread feeds the tensor pipe, so its instruction count per 64-k step matters:
+      // descriptors are kept as a constant high word plus a low word that only ever gets
+      // small offsets added (the address field cannot carry out: shared memory < 256 KiB).
       const uint32_t idesc = ptx::idesc_f16_f32(BM, BN, 0, P.b_kmajor ? 0 : 1);
-      uint32_t it = 0, local_tile = 0;
+      const uint64_t da0 = ptx::smem_desc_sw128(tiles, 16, 1024);
+      const uint64_t db0 = P.b_kmajor ? ptx::smem_desc_sw128(tiles + kABytes, 16, 1024)
+                                      : ptx::smem_desc_sw128(tiles + kABytes, BK * 128, 1024);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      // A and K-major B: 16 k = 32 bytes along the swizzled 128-byte row.  MN-major B: 16 k
+      // rows = 2048 bytes; 64-wide n blocks are BK*128 bytes apart (leading offset), 8-row
+      // groups 1024 apart.
+      const uint32_t b_step = P.b_kmajor ? (32u >> 4) : (2048u >> 4);
+      const uint32_t full0 = ptx::smem_u32(&bars->full[0]), empty0 = ptx::smem_u32(&bars->empty[0]);
+      uint32_t s = 0, ph = 0, local_tile = 0;
       bool ok = true;
       for (uint32_t tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
         const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
@@ -139,25 +207,23 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                     kWaitLimit)) break;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % kStages, ph = (it / kStages) & 1;
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), ph, abort_flag, kWaitLimit)) {
+        for (uint32_t kb = 0; kb < P.k_blocks; ++kb) {
+          if (!ptx::mbar_wait_bounded(full0 + s * 8, ph, abort_flag, kWaitLimit)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t sa = tiles + s * kStageBytes, sb = sa + kABytes;
+          const uint32_t so = s * (kStageBytes >> 4);
+          uint32_t a_lo = (uint32_t)da0 + so, b_lo = (uint32_t)db0 + so;
 #pragma unroll
           for (int k16 = 0; k16 < BK / 16; ++k16) {
-            // A, K-major: 16 k = 32 bytes along the swizzled 128-byte row.
-            const uint64_t da = ptx::smem_desc_sw128(sa + k16 * 32, 16, 1024);
-            // B, K-major: same form.  B, MN-major: 16 k rows = 2048 bytes; 64-wide n
-            // blocks are BK*128 bytes apart (leading offset), 8-row groups 1024 apart.
-            const uint64_t db = P.b_kmajor ? ptx::smem_desc_sw128(sb + k16 * 32, 16, 1024)
-                                           : ptx::smem_desc_sw128(sb + k16 * 2048, BK * 128, 1024);
-            ptx::umma_f16(d_tmem, da, db, idesc, (kb | (uint32_t)k16) != 0);
+            ptx::umma_f16(d_tmem, ((uint64_t)a_hi << 32) | a_lo, ((uint64_t)b_hi << 32) | b_lo, idesc,
+                          k16 ? 1u : kb);
+            a_lo += 32u >> 4;
+            b_lo += b_step;
           }
-          ptx::umma_commit(ptx::smem_u32(&bars->empty[s]));
+          ptx::umma_commit(empty0 + s * 8);
+          if (++s == kStages) { s = 0; ph ^= 1; }
         }
         if (ok) ptx::umma_commit(ptx::smem_u32(&bars->acc_full[acc]));
       }
@@ -167,7 +233,6 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t local_tile = 0;
-    const uint32_t c_sticks = (P.N + 63) / 64;
     for (uint32_t tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
       const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
       const uint32_t bh = tile / (P.tiles_n * P.tiles_m);
@@ -176,40 +241,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
       ptx::tc_fence_after_sync();
-      const uint32_t row = tm * BM + q * 32 + lane;
-      const bool row_ok = row < P.M;
-      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr + chunk * 32, r);
-        ptx::tmem_ld_wait();
-        const uint32_t col = tn * BN + chunk * 32;
-        const uint32_t stick = col >> 6;
-        if (row_ok && stick < c_sticks) {
-          Vec8h bv[4];
-          if (P.bias) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + v * 8);
-          }
-          __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
-                        ((int64_t)b * P.M + row) * kStickHalfs + (col & 63);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            Vec8h o;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
-              if (P.bias) {
-                x0 += __half2float(bv[v].h[2 * e]);
-                x1 += __half2float(bv[v].h[2 * e + 1]);
-              }
-              o.h2[e] = __floats2half2_rn(x0, x1);
-            }
-            st_global_v4(dst + v * 8, o.u);
-          }
-        }
-      }
+      drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
+                 tm * BM + q * 32, tn * BN, b, h, lane);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
@@ -236,7 +269,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 constexpr int kPairStages = 6;
 constexpr int kPairBBytes = (BN / 2) * BK * 2;                 // 16 KiB
 constexpr int kPairStageBytes = kABytes + kPairBBytes;        // 32 KiB per CTA
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kStagingBytes + 1024 + 256;
 
 struct PairBarriers {
   uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
@@ -251,7 +284,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
   uint8_t* gen_tiles = smem_raw + (tiles - raw);
-  PairBarriers* bars = reinterpret_cast<PairBarriers*>(gen_tiles + kPairStages * kPairStageBytes);
+  uint8_t* staging = gen_tiles + kPairStages * kPairStageBytes;
+  PairBarriers* bars = reinterpret_cast<PairBarriers*>(staging + kStagingBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
   const uint32_t pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
@@ -319,8 +353,17 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0) {
+      // (descriptor arithmetic as in the single-CTA kernel: constant high words, small adds)
       const uint32_t idesc = ptx::idesc_f16_f32(2 * BM, BN, 0, P.b_kmajor ? 0 : 1);
-      uint32_t it = 0, local_tile = 0;
+      const uint64_t da0 = ptx::smem_desc_sw128(tiles, 16, 1024);
+      const uint64_t db0 = P.b_kmajor ? ptx::smem_desc_sw128(tiles + kABytes, 16, 1024)
+                                      : ptx::smem_desc_sw128(tiles + kABytes, BK * 128, 1024);
+      const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
+      const uint32_t b_step = P.b_kmajor ? (32u >> 4) : (2048u >> 4);
+      const uint32_t full0 = ptx::smem_u32(&bars->full[0]);
+      const uint32_t empty_c0 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 0);
+      const uint32_t empty_c1 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 1);
+      uint32_t s = 0, ph = 0, local_tile = 0;
       bool ok = true;
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
         const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
@@ -328,24 +371,24 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                     kWaitLimit)) break;
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
-          const uint32_t s = it % kPairStages, ph = (it / kPairStages) & 1;
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->full[s]), ph, abort_flag, kWaitLimit)) {
+        for (uint32_t kb = 0; kb < P.k_blocks; ++kb) {
+          if (!ptx::mbar_wait_bounded(full0 + s * 8, ph, abort_flag, kWaitLimit)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t sa = tiles + s * kPairStageBytes, sb = sa + kABytes;
+          const uint32_t so = s * (kPairStageBytes >> 4);
+          uint32_t a_lo = (uint32_t)da0 + so, b_lo = (uint32_t)db0 + so;
 #pragma unroll
           for (int k16 = 0; k16 < BK / 16; ++k16) {
-            const uint64_t da = ptx::smem_desc_sw128(sa + k16 * 32, 16, 1024);
-            const uint64_t db = P.b_kmajor ? ptx::smem_desc_sw128(sb + k16 * 32, 16, 1024)
-                                           : ptx::smem_desc_sw128(sb + k16 * 2048, BK * 128, 1024);
-            ptx::umma_f16_pair(d_tmem, da, db, idesc, (kb | (uint32_t)k16) != 0);
+            ptx::umma_f16_pair(d_tmem, ((uint64_t)a_hi << 32) | a_lo, ((uint64_t)b_hi << 32) | b_lo,
+                               idesc, k16 ? 1u : kb);
+            a_lo += 32u >> 4;
+            b_lo += b_step;
           }
-          const uint32_t e = ptx::smem_u32(&bars->empty[s]);
-          ptx::umma_commit_pair(ptx::map_to_cta(e, 0));
-          ptx::umma_commit_pair(ptx::map_to_cta(e, 1));
+          ptx::umma_commit_pair(empty_c0 + s * 8);
+          ptx::umma_commit_pair(empty_c1 + s * 8);
+          if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
         if (ok) {
           const uint32_t f = ptx::smem_u32(&bars->acc_full[acc]);
@@ -359,7 +402,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const uint32_t q = warp & 3;
     uint32_t local_tile = 0;
-    const uint32_t c_sticks = (P.N + 63) / 64;
     for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
       const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % tiles_m;
       const uint32_t bh = tile / (P.tiles_n * tiles_m);
@@ -368,40 +410,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
       ptx::tc_fence_after_sync();
-      const uint32_t row = tm * 2 * BM + rank * BM + q * 32 + lane;
-      const bool row_ok = row < P.M;
-      const uint32_t taddr = tmem_base + ((q * 32u) << 16) + acc * BN;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(taddr + chunk * 32, r);
-        ptx::tmem_ld_wait();
-        const uint32_t col = tn * BN + chunk * 32;
-        const uint32_t stick = col >> 6;
-        if (row_ok && stick < c_sticks) {
-          Vec8h bv[4];
-          if (P.bias) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + v * 8);
-          }
-          __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
-                        ((int64_t)b * P.M + row) * kStickHalfs + (col & 63);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            Vec8h o;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
-              if (P.bias) {
-                x0 += __half2float(bv[v].h[2 * e]);
-                x1 += __half2float(bv[v].h[2 * e + 1]);
-              }
-              o.h2[e] = __floats2half2_rn(x0, x1);
-            }
-            st_global_v4(dst + v * 8, o.u);
-          }
-        }
-      }
+      drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
+                 tm * 2 * BM + rank * BM + q * 32, tn * BN, b, h, lane);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
@@ -465,7 +475,8 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
   P.b_kmajor = b_kmajor ? 1 : 0;
   P.b_batched = b_batched ? 1 : 0;
 
-  // CTA pairs whenever a tile pair has work for both halves
+  // CTA pairs whenever a 256-row tile has work for both halves (TS_GEMM_PAIR=0 / 1 in the
+  // environment forces one kernel or the other, for comparisons)
   static const int pair_env = getenv("TS_GEMM_PAIR") ? atoi(getenv("TS_GEMM_PAIR")) : -1;
   const bool use_pair = pair_env >= 0 ? pair_env != 0 : M > BM;
   CUtensorMap map_a, map_b;
