@@ -66,11 +66,16 @@ def test_copy_round_trip(shape):
         assert torch.equal(xt.to(DEV).cpu().view(torch.int16), xt.view(torch.int16))
 
 
-@pytest.mark.parametrize("dtype", [torch.float16, torch.float32, torch.int8, torch.int32, torch.uint8])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32, torch.int8, torch.int32,
+                                   torch.uint8, torch.float8_e4m3fn])
 def test_dtype_round_trips(dtype):
-    # tests/test_spyre.py:121-155 of the reference (bits only: no conversion on the way)
-    x = (torch.randn(64, 64, generator=torch.Generator().manual_seed(2)) * 50).to(dtype)
-    assert torch.equal(x.to(DEV).cpu(), x)
+    # tests/test_spyre.py:121-155 of the reference (bits only: no conversion on the way);
+    # 64 fp16 / bf16, 32 fp32 / int32, 128 int8 / fp8 elements per 128-byte stick
+    x = (torch.randn(64, 200, generator=torch.Generator().manual_seed(2)) * 50).to(dtype)
+    bits = {1: torch.uint8, 2: torch.int16, 4: torch.int32}[x.element_size()]
+    y = x.to(DEV)
+    assert y.dtype == dtype
+    assert torch.equal(y.cpu().view(bits), x.view(bits))
 
 
 def test_dtype_converting_copy_is_refused():

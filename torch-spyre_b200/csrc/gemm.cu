@@ -60,6 +60,22 @@ struct Barriers {
   int abort_flag;
 };
 
+// Tile order within one (batch, head): bands of kBandTiles tile columns, rows fastest across
+// a band, so that the tiles in flight at any time (one per CTA or CTA pair) form a roughly
+// square block and share both their A row panels and their B column panels in L2.
+constexpr uint32_t kBandTiles = 8;
+__device__ __forceinline__ void decode_tile(const GemmParams& P, uint32_t tile, uint32_t tiles_m,
+                                            uint32_t& tm, uint32_t& tn, uint32_t& b, uint32_t& h) {
+  const uint32_t per_bh = P.tiles_n * tiles_m;
+  const uint32_t bh = tile / per_bh, t = tile - bh * per_bh;
+  b = bh % P.batch;
+  h = bh / P.batch;
+  const uint32_t band = t / (kBandTiles * tiles_m), r = t - band * (kBandTiles * tiles_m);
+  const uint32_t width = min(kBandTiles, P.tiles_n - band * kBandTiles);
+  tm = r / width;
+  tn = band * kBandTiles + (r - tm * width);
+}
+
 // Drains one warp's 32 accumulator rows x BN columns: tensor memory -> registers -> fp16 ->
 // a per-warp shared-memory staging block (32 rows x 128 bytes, 16-byte chunks XOR-swizzled by
 // row so that neither side has bank conflicts) -> global memory with every store instruction
@@ -153,9 +169,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
-        const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
-        const uint32_t bh = tile / (P.tiles_n * P.tiles_m);
-        const uint32_t b = bh % P.batch, h = bh / P.batch;
+        uint32_t tm, tn, b, h;
+        decode_tile(P, tile, P.tiles_m, tm, tn, b, h);
         const int bb = P.b_batched ? (int)b : 0;
         for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
           const uint32_t s = it % kStages, ph = (it / kStages) & 1;
@@ -234,9 +249,8 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t local_tile = 0;
     for (uint32_t tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
-      const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % P.tiles_m;
-      const uint32_t bh = tile / (P.tiles_n * P.tiles_m);
-      const uint32_t b = bh % P.batch, h = bh / P.batch;
+      uint32_t tm, tn, b, h;
+      decode_tile(P, tile, P.tiles_m, tm, tn, b, h);
       const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
@@ -323,9 +337,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-        const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % tiles_m;
-        const uint32_t bh = tile / (P.tiles_n * tiles_m);
-        const uint32_t b = bh % P.batch, h = bh / P.batch;
+        uint32_t tm, tn, b, h;
+        decode_tile(P, tile, tiles_m, tm, tn, b, h);
         const int bb = P.b_batched ? (int)b : 0;
         for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
           const uint32_t s = it % kPairStages, ph = (it / kPairStages) & 1;
@@ -403,9 +416,8 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     const uint32_t q = warp & 3;
     uint32_t local_tile = 0;
     for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
-      const uint32_t tn = tile % P.tiles_n, tm = (tile / P.tiles_n) % tiles_m;
-      const uint32_t bh = tile / (P.tiles_n * tiles_m);
-      const uint32_t b = bh % P.batch, h = bh / P.batch;
+      uint32_t tm, tn, b, h;
+      decode_tile(P, tile, tiles_m, tm, tn, b, h);
       const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
