@@ -1,0 +1,77 @@
+"""The graph rewrites that map stock decoder-layer code onto the fused spyre ops, checked on CPU:
+the rewritten graphs must contain the fused nodes and compute what the original graphs compute
+(every spyre custom op has a plain-torch definition off the device)."""
+import pytest
+import torch
+
+import torch_spyre  # noqa: F401  (registers the spyre custom ops)
+from torch_spyre._inductor import patterns
+
+transformers = pytest.importorskip("transformers")
+
+
+def _layer_and_inputs(batch=2, seq=64, heads=2, hidden=256, inter=384):
+    from transformers.models.llama.modeling_llama import (LlamaConfig, LlamaDecoderLayer,
+                                                          LlamaRotaryEmbedding)
+    torch.manual_seed(0)
+    cfg = LlamaConfig(hidden_size=hidden, intermediate_size=inter, num_attention_heads=heads,
+                      num_key_value_heads=heads, num_hidden_layers=1, max_position_embeddings=512,
+                      rms_norm_eps=1e-5, attn_implementation="sdpa")
+    layer = LlamaDecoderLayer(cfg, 0).eval()
+    x = torch.randn(batch, seq, hidden)
+    pos = torch.arange(seq)[None].expand(batch, -1)
+    cos, sin = LlamaRotaryEmbedding(cfg)(x, pos)
+    return layer, x, cos, sin, pos
+
+
+def _targets(gm):
+    return [str(n.target) for n in gm.graph.nodes if n.op == "call_function"]
+
+
+def test_rewrites_on_decoder_layer_graphs():
+    from torch._functorch.aot_autograd import aot_module_simplified
+
+    layer, x, cos, sin, pos = _layer_and_inputs()
+    seen = {}
+
+    def fw_compiler(gm, example_inputs):
+        seen["before"] = _targets(gm)
+        seen["count"] = patterns.rewrite_aten_graph(gm)
+        seen["after"] = _targets(gm)
+        return gm.forward
+
+    def backend(gm, example_inputs):
+        seen["sdpa"] = patterns.rewrite_dynamo_graph(gm)
+        return aot_module_simplified(gm, example_inputs, fw_compiler=fw_compiler)
+
+    def f(x, cos, sin):
+        out = layer(x, position_embeddings=(cos, sin), attention_mask=None, position_ids=pos)
+        return out[0] if isinstance(out, tuple) else out
+
+    # the fp32 layer keeps the RMS-norm casts out of the graph, so trace a half-precision copy
+    layer.half()
+    xh, ch, sh = x.half(), cos.half(), sin.half()
+    with torch.no_grad():
+        want = f(xh, ch, sh)
+        got = torch.compile(f, backend=backend)(xh, ch, sh)
+    assert seen["sdpa"] == 1
+    assert seen["count"] == 4                       # two RMS norms, rotary on q and on k
+    after = seen["after"]
+    assert sum("spyre.rms_norm" in t for t in after) == 2
+    assert sum("spyre.rotary" in t for t in after) == 2
+    assert sum("spyre.sdpa_causal" in t for t in after) == 1
+    assert not any("aten.cat" in t or "aten.pow" in t or "aten.rsqrt" in t for t in after)
+    torch.testing.assert_close(got, want, rtol=1e-2, atol=2e-3)
+
+
+def test_rms_norm_pattern_needs_exclusive_intermediates():
+    """If an intermediate of the idiom is used elsewhere the rewrite must leave the graph alone."""
+    from torch.fx.experimental.proxy_tensor import make_fx
+
+    def f(x, w):
+        x32 = x.float()
+        r = torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + 1e-5)
+        return w * (x32 * r).half(), r
+
+    gm = make_fx(f)(torch.randn(4, 64).half(), torch.ones(64).half())
+    assert patterns.rewrite_aten_graph(gm) == 0

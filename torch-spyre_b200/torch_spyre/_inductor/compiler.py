@@ -144,6 +144,9 @@ class CompiledGraph:
 
 
 def compile_graph(gm: GraphModule, example_inputs) -> Callable:
+    from . import patterns
+
+    patterns.rewrite_aten_graph(gm)
     compiled = CompiledGraph(gm)
 
     def run(args):
@@ -190,6 +193,9 @@ def install_aot_hook() -> None:
             on_spyre = any(isinstance(t, torch.Tensor) and t.device.type == "spyre"
                            for t in example_inputs)
             if on_spyre:
+                from . import patterns
+
+                patterns.rewrite_dynamo_graph(gm)
                 self.kwargs = dict(self.kwargs)
                 self.kwargs["fw_compiler"] = compile_graph
                 self.kwargs["inference_compiler"] = compile_graph

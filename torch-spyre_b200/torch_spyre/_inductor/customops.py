@@ -147,6 +147,26 @@ def _(x, cos, sin, heads):
     return x.new_empty(x.size())
 
 
+@torch.library.custom_op("spyre::sdpa_causal", mutates_args=())
+def sdpa_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
+    """F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale) on [batch, heads, seq,
+    head_dim] tensors.  On spyre the heads are attended in the packed [batch, seq, heads*head_dim]
+    form: when q / k / v are the usual transposed views of projection outputs, that form is the
+    projection output itself and nothing is copied."""
+    b, h, s, d = q.shape
+    if _on_spyre(q):
+        packed = [t.transpose(1, 2).reshape(b, s, h * d) for t in (q, k, v)]
+        out = torch.ops.spyre.causal_attention(packed[0], packed[1], packed[2], h, scale)
+        return out.view(b, s, h, d).transpose(1, 2)
+    return torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale)
+
+
+@sdpa_causal.register_fake
+def _(q, k, v, scale):
+    b, h, s, d = q.shape
+    return q.new_empty((b, s, h, d)).transpose(1, 2)
+
+
 @torch.library.custom_op("spyre::causal_attention", mutates_args=())
 def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int,
                      scale: float) -> torch.Tensor:
