@@ -341,9 +341,8 @@ def make_workload(name: str, dev, scale_rows=None):
                     l2="operands 1.5 GiB, far larger than L2", cpu_step=cpu_step,
                     sample="one batch entry [1,2048,4096]x[1,4096,4096] per CPU step (1/32 of the job)",
                     check=check)
-    if name == "llama_layer":
+    if name in ("llama_layer", "hf_llama_layer"):
         import torch_spyre  # noqa: F401
-        from examples.llama_layer import LlamaStyleLayer
         from oracle import llama_ref as LR
         world = int(os.environ.get("WORLD_SIZE", "1"))
         cfg = LR.LayerConfig()
@@ -351,9 +350,38 @@ def make_workload(name: str, dev, scale_rows=None):
         w = LR.make_weights(cfg)
         cos, sin = LR.rope_tables(seq, cfg.head_dim)
         sdev = torch.device("spyre", dev.index)
-        layer = LlamaStyleLayer({k: v.to(sdev) for k, v in w.items()}, cfg.heads, cfg.eps,
-                                cos.to(sdev), sin.to(sdev))
-        compiled = torch.compile(layer)
+        if name == "llama_layer":
+            from examples.llama_layer import LlamaStyleLayer
+            layer = LlamaStyleLayer({k: v.to(sdev) for k, v in w.items()}, cfg.heads, cfg.eps,
+                                    cos.to(sdev), sin.to(sdev))
+            compiled = torch.compile(layer)
+        else:
+            # the module the reference's own (skipped) test builds, unmodified, same weights
+            import transformers as tf
+            from transformers.models.llama.modeling_llama import LlamaDecoderLayer
+            hc = tf.LlamaConfig(hidden_size=cfg.d_model, num_attention_heads=cfg.heads,
+                                num_key_value_heads=cfg.heads, intermediate_size=cfg.ffn,
+                                rms_norm_eps=cfg.eps, num_hidden_layers=1,
+                                max_position_embeddings=seq, attn_implementation="sdpa")
+            with torch.device("meta"):
+                hf = LlamaDecoderLayer(hc, 0).half().eval()
+            hf = hf.to_empty(device="cpu")
+            hf.load_state_dict({
+                "self_attn.q_proj.weight": w["q"], "self_attn.k_proj.weight": w["k"],
+                "self_attn.v_proj.weight": w["v"], "self_attn.o_proj.weight": w["o"],
+                "mlp.gate_proj.weight": w["gate"], "mlp.up_proj.weight": w["up"],
+                "mlp.down_proj.weight": w["down"], "input_layernorm.weight": w["norm1"],
+                "post_attention_layernorm.weight": w["norm2"]}, strict=False)
+            hf = hf.to(sdev).requires_grad_(False)     # forward only: the fused ops define no backward
+            cos_b = cos.unsqueeze(0).expand(batch, -1, -1).contiguous().to(sdev)
+            sin_b = sin.unsqueeze(0).expand(batch, -1, -1).contiguous().to(sdev)
+            pos = torch.arange(seq)[None].expand(batch, -1)
+
+            def hf_forward(x):
+                out = hf(x, position_embeddings=(cos_b, sin_b), attention_mask=None, position_ids=pos)
+                return out[0] if isinstance(out, tuple) else out
+
+            compiled = torch.compile(hf_forward)
         x1 = (torch.randn(1, seq, cfg.d_model, generator=torch.Generator().manual_seed(0))).half()
         xh = x1.repeat(batch, 1, 1).pin_memory()
         xd = xh.to(sdev)
@@ -387,7 +415,9 @@ def make_workload(name: str, dev, scale_rows=None):
                     flops=LR.layer_flops(batch, seq, cfg, causal=True),
                     cpu_flops=LR.layer_flops(1, 512, cfg, causal=True), scaling="strong",
                     h2d=xh.numel() * 2, d2h=xh.numel() * 2, launches=18,
-                    desc=f"Llama-style decoder layer through torch.compile on spyre: d_model 4096, 32 heads x 128, "
+                    desc=("transformers LlamaDecoderLayer (unmodified)" if name == "hf_llama_layer"
+                          else "Llama-style decoder layer") +
+                         " through torch.compile on spyre: d_model 4096, 32 heads x 128, "
                          f"SwiGLU 11008, RMSNorm, rotary, causal attention, batch {batch} x seq {seq} per GPU, "
                          "causal-useful flops (BASELINE configs[4])",
                     l2="activations and weights (> 1 GiB) far larger than L2", cpu_step=cpu_step,
