@@ -9,8 +9,9 @@
 // bmm / where / _softmax / bmm sequence its compiled path would emit.
 //
 // One CTA works on one (batch, head, 128-query tile) at a time and walks the key tiles up to
-// the diagonal.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 (one thread per query row)
-// run the online softmax:
+// the diagonal.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-9 run the online softmax: two
+// threads per query row, each owning 64 of the tile's 128 key (and output) columns, so that
+// every scheduler has two softmax warps to alternate between:
 //     S_j = Q K_j^T            (tensor memory, two buffers so S_{j+1} is computed during softmax j)
 //     P_j = exp2((S_j - m) c) -> fp16 -> shared memory (two buffers), l += rowsum P_j
 //     O  += P_j V_j            (accumulated in tensor memory)
@@ -28,13 +29,13 @@ namespace tsb {
 namespace {
 
 constexpr int kTile = 128;                      // queries per tile = keys per tile = head dim
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;                // TMA warp, MMA warp, 8 softmax warps
 constexpr int kBlockBytes = kTile * 128;        // one 128-row x 64-lane box: 16 KiB
 constexpr int kTileBytes = 2 * kBlockBytes;     // 32 KiB
 constexpr int kKvStages = 2;
 // Q | K stages | V stages | P0 P1
 constexpr int kSmemTiles = 3 + 2 * kKvStages;
-constexpr int kAttnSmem = kSmemTiles * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int kAttnSmem = kSmemTiles * kTileBytes + 1024 /*align*/ + 1280 /*barriers, exchange*/;
 constexpr uint32_t kAttnTmemCols = 512;         // S0 | S1 | O | (unused)
 constexpr float kRescaleThreshold = 8.f;        // in units of the exponent (log2)
 constexpr long long kAttnWaitLimit = 4000000000ll;  // ~2 s of SM clocks
@@ -53,7 +54,9 @@ struct AttnBars {
       v_empty[kKvStages], s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   int abort_flag;
+  float exchange[2][kTile];   // the two threads of a row swap their partial maximum / sum here
 };
+static_assert(sizeof(AttnBars) <= 1280, "barrier block outgrew its shared-memory reservation");
 
 // Heaviest tiles (most key tiles) first, so that the static round-robin over CTAs balances.
 __device__ __forceinline__ void decode_item(const AttnParams& P, uint32_t item, uint32_t& qt,
@@ -96,7 +99,7 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     for (int i = 0; i < 2; ++i) {
       ptx::mbar_init(ptx::smem_u32(&bars->s_full[i]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[i]), 4);   // one arrival per softmax warp
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[i]), 8);   // one arrival per softmax warp
       ptx::mbar_init(ptx::smem_u32(&bars->pv_done[i]), 1);
     }
     bars->abort_flag = 0;
@@ -227,59 +230,78 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ softmax + output (warps 2..5)
+    // ------------------------------------------------------------ softmax + output (warps 2..9)
     const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
+    const uint32_t half = (uint32_t)(warp - 2) >> 2;   // which 64 of the 128 columns: warps w, w+4 pair up
     const uint32_t row = quarter * 32 + lane;       // query row within the tile
     const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    const uint32_t to = lane_addr + 2 * kTile;      // this row of O
+    const uint32_t to = lane_addr + 2 * kTile + half * 64;      // this thread's part of O
     const float c = P.scale_log2;
     // the whole warp takes the same decision, since what follows a wait is warp-collective
     auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag,
                                                             kAttnWaitLimit)) != 0;
     };
+    // the two threads of a row swap a value (64-thread named barrier of their two warps)
+    auto swap_with_partner = [&](float v) -> float {
+      bars->exchange[half][row] = v;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      const float o = bars->exchange[half ^ 1][row];
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      return o;
+    };
+    // After a wait has given up this warp is "dead": it does no more work, but it still walks
+    // every item and tile and meets its partner at every named barrier, so that no warp is
+    // left waiting at one (a named barrier cannot time out).  The abort flag makes every other
+    // wait in the CTA give up at once, so the walk is short.
     uint32_t g = 0;
-    bool ok = true;
-    for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x) {
+    bool dead = false;
+    for (uint32_t item = blockIdx.x; item < P.num_items; item += gridDim.x) {
       uint32_t qt, b, h;
       decode_item(P, item, qt, b, h);
       const uint32_t n = qt + 1;
-      float m = -1e30f, l = 0.f;
+      float m = -1e30f, l = 0.f;   // m: shared by the row's two threads; l: this thread's columns only
       for (uint32_t j = 0; j < n; ++j) {
         const uint32_t t = g + j;
-        if (!warp_wait(&bars->s_full[t & 1], (t >> 1) & 1)) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        const uint32_t ts = lane_addr + (t & 1) * kTile;
-        uint32_t r[4][32];
+        if (!dead && !warp_wait(&bars->s_full[t & 1], (t >> 1) & 1)) dead = true;
+        uint32_t r[2][32];
+        float own_max = -INFINITY;
+        if (!dead) {
+          ptx::tc_fence_after_sync();
+          const uint32_t ts = lane_addr + (t & 1) * kTile + half * 64;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld_32x32(ts + ch * 32, r[ch]);
-        ptx::tmem_ld_wait();
-        if (j == qt) {   // diagonal tile: keys after the query do not exist
+          for (int ch = 0; ch < 2; ++ch) ptx::tmem_ld_32x32(ts + ch * 32, r[ch]);
+          ptx::tmem_ld_wait();
+          if (j == qt) {   // diagonal tile: keys after the query do not exist
 #pragma unroll
-          for (int ch = 0; ch < 4; ++ch)
+            for (int ch = 0; ch < 2; ++ch)
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if ((uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
+              for (int i = 0; i < 32; ++i)
+                if (half * 64 + (uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
+          }
+          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[ch][i]));
+          own_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         }
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[ch][i]));
-        const float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        const float tile_max = fmaxf(own_max, swap_with_partner(own_max));
+        if (dead) continue;
         if (j == 0) {
           m = tile_max;   // O is still empty: nothing to rescale
         } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
-          // Raise the offset: O and l of this row shrink by alpha.  P V of the previous key
-          // tile must have finished accumulating; the next one starts after our p_full arrival.
-          if (!warp_wait(&bars->pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) { ok = false; break; }
+          // Raise the offset: O and l of this row shrink by alpha (both warps of a pair see the
+          // same maxima and take this branch together).  P V of the previous key tile must have
+          // finished accumulating; the next one starts after our p_full arrival.
+          if (!warp_wait(&bars->pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) { dead = true; continue; }
           ptx::tc_fence_after_sync();
           const float m_new = fmaxf(m, tile_max);
           const float alpha = ex2f((m - m_new) * c);
           l *= alpha;
           m = m_new;
 #pragma unroll 1
-          for (int ch = 0; ch < 4; ++ch) {
+          for (int ch = 0; ch < 2; ++ch) {
             uint32_t o[32];
             ptx::tmem_ld_32x32(to + ch * 32, o);
             ptx::tmem_ld_wait();
@@ -290,13 +312,13 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           ptx::tmem_st_wait();
         }
         // the P buffer of this tile was last read by the P V MMA two tiles ago
-        if (!warp_wait(&bars->pv_done[t & 1], ((t >> 1) & 1) ^ 1)) { ok = false; break; }
-        // P = exp2(S c - m c) as fp16 into the swizzled K-major operand tile
+        if (!warp_wait(&bars->pv_done[t & 1], ((t >> 1) & 1) ^ 1)) { dead = true; continue; }
+        // P = exp2(S c - m c) as fp16 into this thread's 64-key block of the swizzled operand tile
         const float mc = m * c;
         float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        uint8_t* prow = gen_p + (t & 1) * kTileBytes + row * 128;
+        uint8_t* prow = gen_p + (t & 1) * kTileBytes + half * kBlockBytes + row * 128;
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
+        for (int ch = 0; ch < 2; ++ch) {
           uint32_t packed[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
@@ -306,11 +328,10 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const __half2 hp = __floats2half2_rn(p0, p1);
             packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
           }
-          uint8_t* blk = prow + (ch >> 1) * kBlockBytes;
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            const uint32_t chunk = (uint32_t)((ch & 1) * 4 + v) ^ (row & 7);
-            *reinterpret_cast<uint4*>(blk + chunk * 16) =
+            const uint32_t chunk = (uint32_t)(ch * 4 + v) ^ (row & 7);
+            *reinterpret_cast<uint4*>(prow + chunk * 16) =
                 make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
           }
         }
@@ -320,20 +341,20 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[t & 1]));
       }
-      if (!ok) break;
-      // all key tiles accumulated: normalise and store into the packed output image
+      // all key tiles accumulated: normalise and store this thread's stick of the packed output
       const uint32_t tl = g + n - 1;
-      if (!warp_wait(&bars->pv_done[tl & 1], (tl >> 1) & 1)) break;
+      if (!dead && !warp_wait(&bars->pv_done[tl & 1], (tl >> 1) & 1)) dead = true;
+      const float inv = 1.f / (l + swap_with_partner(l));
+      g += n;
+      if (dead) continue;
       ptx::tc_fence_after_sync();
-      const float inv = 1.f / l;
       const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
+      __half* dst = P.out + (int64_t)(2 * h + half) * P.stick_stride + grow * kStickHalfs;
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
         uint32_t o[32];
         ptx::tmem_ld_32x32(to + ch * 32, o);
         ptx::tmem_ld_wait();
-        __half* dst = P.out + (int64_t)(2 * h + (ch >> 1)) * P.stick_stride + grow * kStickHalfs +
-                      (ch & 1) * 32;
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
           Vec8h ov;
@@ -342,11 +363,10 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const int i = v * 8 + 2 * e;
             ov.h2[e] = __floats2half2_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
           }
-          st_global_v4(dst + v * 8, ov.u);
+          st_global_v4(dst + ch * 32 + v * 8, ov.u);
         }
       }
       ptx::tc_fence_before_sync();
-      g += n;
     }
   }
 
