@@ -138,8 +138,8 @@ def make_workload(name: str, dev, scale_rows=None):
 
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=alg,
                     h2d=rows * cols * 2 + 2 * cols * 2, d2h=rows * 2, launches=1,
-                    # ncu, one launch at this size: 134,266,112 B read + 4,761,600 B written
-                    traffic=139027712 if (rows, cols) == (8192, 8192) else None,
+                    # ncu, one launch at this size: 134,263,296 B read + 3,333,632 B written
+                    traffic=137596928 if (rows, cols) == (8192, 8192) else None,
                     graph_period=ring,
                     desc=f"exp(x*a+b).sum(-1), x fp16 [{rows},{cols}] (BASELINE configs[1])",
                     l2=f"ring of {ring} x buffers ({ring * rows * cols * 2 >> 20} MiB) > L2",
@@ -334,8 +334,8 @@ def make_workload(name: str, dev, scale_rows=None):
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0,
                     flops=2.0 * batch * m * k * n, cpu_scale=float(batch),
                     h2d=(ah.numel() + bh.numel()) * 2, d2h=ch.numel() * 2, launches=1,
-                    # ncu at batch 4: 281,354,752 B read + 50,876,416 B written, scaled by batch
-                    traffic=int(332231168 * batch / 4) if (m, k, n) == (2048, 4096, 4096) else None,
+                    # ncu at batch 4: 248,113,408 B read + 52,386,048 B written, scaled by batch
+                    traffic=int(300499456 * batch / 4) if (m, k, n) == (2048, 4096, 4096) else None,
                     desc=f"bmm fp16 [{batch},{m},{k}] x [{batch},{k},{n}], fp32 accumulate "
                          "(BASELINE configs[3])",
                     l2="operands 1.5 GiB, far larger than L2", cpu_step=cpu_step,
