@@ -509,6 +509,17 @@ def time_device(step, steps, warmup, graph_period=0):
     return start.elapsed_time(end) / 1e3
 
 
+def use_all_host_threads() -> int:
+    """torchrun exports OMP_NUM_THREADS=1 to its workers; the CPU legs are meant to use every host
+    core this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(n, 1))
+    return torch.get_num_threads()
+
+
 def time_cpu(fn, budget_s=12.0, min_runs=3):
     fn()
     times = []
@@ -529,6 +540,7 @@ def run_reference(args, rank, world):
     if rank != 0:
         return
     from oracle import math_ref  # noqa: F401
+    use_all_host_threads()
     wl = make_workload_cpu(args.workload)
     wl["cpu_step"]()
     for _ in range(max(args.warmup - 1, 0)):
@@ -797,6 +809,7 @@ def main():
                            "h2d_bytes_per_step": wl["h2d"], "d2h_bytes_per_step": wl["d2h"],
                            "ms_per_step": e2e_dt * 1e3}
         if not args.no_cpu_baseline and world == 1:
+            use_all_host_threads()
             med, n = time_cpu(wl["cpu_step"])
             scale = wl.get("cpu_scale", 1.0)
             cpu_work = wl["cpu_flops"] / 1e3 if "cpu_flops" in wl else work / scale
