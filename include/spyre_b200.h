@@ -285,9 +285,9 @@ int ts_rotary_f16(const void* x, const void* cos_table, const void* sin_table, v
 
 /* Causal scaled-dot-product attention in one kernel: out = softmax(q k^T * scale + causal mask) v
  * per head.  q, k, v, out are the packed stick images of [batch*seq, heads*head_dim] that the
- * projection GEMMs produce / consume (head h = stick columns 2h, 2h+1); head_dim must be 128 and
- * seq a multiple of 128 (TS_ERR_UNSUPPORTED otherwise: use ts_gemm_f16_ex +
- * ts_softmax_rows_causal).  The score matrix stays on the SM.  The reference has no attention
+ * projection GEMMs produce / consume (head h = stick columns 2h, 2h+1); head_dim must be 128
+ * (TS_ERR_UNSUPPORTED otherwise: use ts_gemm_f16_ex + ts_softmax_rows_causal); seq is free.
+ * The score matrix stays on the SM.  The reference has no attention
  * kernel; this stands in for the bmm / where / _softmax / bmm programs its compiled path would
  * emit for torch.nn.functional.scaled_dot_product_attention (tests/test_modules.py:178-211 is
  * the skipped test that would exercise them).

@@ -348,6 +348,7 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       g += n;
       if (dead) continue;
       ptx::tc_fence_after_sync();
+      const bool row_ok = qt * kTile + row < P.seq;   // the last tile may run past the sequence
       const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
       __half* dst = P.out + (int64_t)(2 * h + half) * P.stick_stride + grow * kStickHalfs;
 #pragma unroll
@@ -363,7 +364,7 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             const int i = v * 8 + 2 * e;
             ov.h2[e] = __floats2half2_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
           }
-          st_global_v4(dst + ch * 32 + v * 8, ov.u);
+          if (row_ok) st_global_v4(dst + ch * 32 + v * 8, ov.u);
         }
       }
       ptx::tc_fence_before_sync();
@@ -392,10 +393,12 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
   if (batch < 0 || seq < 0 || heads < 0) return TS_ERR_INVALID;
   if (batch == 0 || seq == 0 || heads == 0) return TS_OK;
   if (!q || !k || !v || !out) return TS_ERR_INVALID;
-  if (head_dim != kTile || seq % kTile != 0) return TS_ERR_UNSUPPORTED;
+  if (head_dim != kTile) return TS_ERR_UNSUPPORTED;
   if (((uintptr_t)q | (uintptr_t)k | (uintptr_t)v | (uintptr_t)out) % 128) return TS_ERR_ALIGNMENT;
   if (!(scale > 0.f)) return TS_ERR_INVALID;
-  const int64_t rows = batch * seq, q_tiles = seq / kTile;
+  // A last tile that runs past seq reads zeros there (the tensor map has seq as its own dim);
+  // the causal mask already hides those keys from every real query, and their rows are not stored.
+  const int64_t rows = batch * seq, q_tiles = ceil_div(seq, (int64_t)kTile);
   const int64_t items = q_tiles * batch * heads;
   if (rows >= (1ll << 31) || items >= (1ll << 31) || heads * 2 >= (1ll << 31)) return TS_ERR_TOO_LARGE;
   AttnParams P{};

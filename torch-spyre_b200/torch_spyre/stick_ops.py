@@ -406,7 +406,7 @@ def causal_attention(q: StickTensor, k: StickTensor, v: StickTensor, batch: int,
                      scores: Optional[torch.Tensor] = None) -> StickTensor:
     """Causal scaled-dot-product attention over packed [batch, seq, heads*128] q / k / v images.
 
-    seq a multiple of 128: one fused kernel (scores stay on the SM).  Otherwise three launches
+    One fused kernel (scores stay on the SM).  With ``fused_attention`` off, three launches
     for all heads together: scores = q k^T (tcgen05 GEMM reading the heads out of the packed
     images), masked softmax in place, out = probs v written straight into the packed output
     image; `scores` is scratch of heads*batch*seq*seq fp16 elements for that path."""
@@ -414,7 +414,7 @@ def causal_attention(q: StickTensor, k: StickTensor, v: StickTensor, batch: int,
     dev = q.image.device
     rows = batch * seq
     out = out or empty((batch, seq, heads * hd), torch.float16, dev)
-    if seq % 128 == 0 and fused_attention:
+    if fused_attention:
         rc = _abi.lib().ts_attention_causal_f16(q.ptr(), k.ptr(), v.ptr(), out.ptr(), batch, seq,
                                                 heads, hd, float(scale), _stream())
         _abi.check(rc, "ts_attention_causal_f16")
