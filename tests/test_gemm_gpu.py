@@ -26,7 +26,9 @@ def no_kernel_timeout():
 
 
 MM_SHAPES = [(128, 64, 256), (128, 128, 256), (3, 5, 7), (67, 256, 128), (256, 128, 512),
-             (130, 70, 300), (1, 64, 64), (512, 1024, 768), (1000, 4096, 520)]
+             (130, 70, 300), (1, 64, 64), (512, 1024, 768), (1000, 4096, 520),
+             # more 256x256 tiles than CTA pairs, and a last band of tile columns narrower than 8
+             (2304, 192, 2304 + 64)]
 
 
 @pytest.mark.parametrize("m,k,n", MM_SHAPES)
