@@ -47,6 +47,7 @@ struct AttnParams {
   uint32_t batch, seq, heads, q_tiles, num_items;
   int64_t stick_stride;   // elements between stick columns of the packed images
   float scale_log2;       // softmax scale * log2(e)
+  uint32_t heads_per_round;   // two-tile kernel: (batch, head) slices in flight together; 0 = linear order
 };
 
 struct AttnBars {
@@ -402,14 +403,58 @@ struct PairAttnBars {
   int abort_flag;
 };
 
-// Heaviest pairs first.
-__device__ __forceinline__ void decode_pair_item(const AttnParams& P, uint32_t item, uint32_t& pr,
+// Work order of the two-tile kernel.  The grid is heads_per_round x (pairs per head) CTAs; in
+// round r CTA c works on (batch, head) slice r * heads_per_round + c / pairs and on tile pair
+// number (c % pairs + r) % pairs of the sequence light, heavy, light, heavy, ... of it.  So the CTAs running together read the K / V of only
+// heads_per_round slices (they stay in L2 for all the pairs of a slice), and over the rounds
+// every CTA gets each pair index, light and heavy, equally often.  heads_per_round == 0 (more
+// pairs per head than SMs): plain order, heaviest pairs first.
+// When the slices left over after the last full round are no more than the SMs left over
+// after heads_per_round * pairs, those spare CTAs take one left-over slice each, all its pairs,
+// instead of a short last round that would land on CTAs already carrying a full share.
+__device__ __forceinline__ void pair_layout(const AttnParams& P, uint32_t& main_ctas, uint32_t& main_rounds,
+                                            bool& spares_take_rest) {
+  const uint32_t pairs = P.q_tiles / 2, bh_count = P.batch * P.heads;
+  main_ctas = P.heads_per_round * pairs;
+  const uint32_t full = bh_count / P.heads_per_round, rest = bh_count % P.heads_per_round;
+  spares_take_rest = rest != 0 && rest <= gridDim.x - main_ctas;
+  main_rounds = full + ((rest != 0 && !spares_take_rest) ? 1 : 0);
+}
+__device__ __forceinline__ uint32_t pair_item_count(const AttnParams& P) {
+  const uint32_t pairs = P.q_tiles / 2, bh_count = P.batch * P.heads;
+  if (P.heads_per_round == 0) return pairs * bh_count;
+  uint32_t main_ctas, main_rounds;
+  bool spares;
+  pair_layout(P, main_ctas, main_rounds, spares);
+  return (main_rounds > pairs ? main_rounds : pairs) * gridDim.x;
+}
+__device__ __forceinline__ bool decode_pair_item(const AttnParams& P, uint32_t item, uint32_t& pr,
                                                  uint32_t& b, uint32_t& h) {
-  const uint32_t bh_count = P.batch * P.heads;
-  pr = P.q_tiles / 2 - 1 - item / bh_count;
-  const uint32_t bh = item % bh_count;
+  const uint32_t pairs = P.q_tiles / 2, bh_count = P.batch * P.heads;
+  uint32_t bh;
+  if (P.heads_per_round == 0) {
+    pr = pairs - 1 - item / bh_count;
+    bh = item % bh_count;
+  } else {
+    uint32_t main_ctas, main_rounds;
+    bool spares;
+    pair_layout(P, main_ctas, main_rounds, spares);
+    const uint32_t r = item / gridDim.x, c = item - r * gridDim.x;
+    if (c < main_ctas) {
+      if (r >= main_rounds) return false;
+      bh = r * P.heads_per_round + c / pairs;
+      const uint32_t k = (c % pairs + r) % pairs;
+      pr = (k & 1) ? pairs - 1 - (k >> 1) : (k >> 1);   // 0, last, 1, last-1, ...: neighbours sum to a constant
+    } else {
+      if (!spares || r >= pairs) return false;
+      bh = (bh_count / P.heads_per_round) * P.heads_per_round + (c - main_ctas);
+      pr = pairs - 1 - r;                                // a whole slice, heaviest pair first
+    }
+    if (bh >= bh_count) return false;
+  }
   b = bh % P.batch;
   h = bh / P.batch;
+  return true;
 }
 
 __global__ void __launch_bounds__(kPairAttnThreads, 1)
@@ -424,7 +469,7 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
   PairAttnBars* bars = reinterpret_cast<PairAttnBars*>(gen_base + kPairSmemTiles * kTileBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
-  const uint32_t num_items = (P.q_tiles / 2) * P.batch * P.heads;
+  const uint32_t num_items = pair_item_count(P);
 
   if (threadIdx.x == 0) {
     ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
@@ -461,7 +506,7 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
       bool ok = true;
       for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
         uint32_t pr, b, h;
-        decode_pair_item(P, item, pr, b, h);
+        if (!decode_pair_item(P, item, pr, b, h)) continue;
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_empty), (item_n & 1) ^ 1, abort_flag,
                                     kAttnWaitLimit)) break;
         const uint32_t qf = ptx::smem_u32(&bars->q_full);
@@ -536,7 +581,7 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
       bool ok = true;
       for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
         uint32_t pr, b, h;
-        decode_pair_item(P, item, pr, b, h);
+        if (!decode_pair_item(P, item, pr, b, h)) continue;
         const uint32_t n = 2 * pr + 2;          // key tiles loaded for the item
         const uint32_t nx = n - 1 + x;          // key tiles this group uses (A stops one short)
         if (!wait(&bars->q_full, item_n & 1)) break;
@@ -585,7 +630,7 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
     bool ok = true;
     for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
       uint32_t pr, b, h;
-      decode_pair_item(P, item, pr, b, h);
+      if (!decode_pair_item(P, item, pr, b, h)) continue;
       const uint32_t qt = 2 * pr + x, n = qt + 1;
       float m = -1e30f, l = 0.f;
       for (uint32_t j = 0; j < n; ++j, ++g) {
@@ -745,8 +790,11 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
     const cudaError_t e2 = cudaFuncSetAttribute(attention_causal_pair_kernel,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kPairAttnSmem);
     if (e2 != cudaSuccess) { note_cuda_error(e2); return TS_ERR_CUDA; }
-    const int64_t pair_items = items / 2;
-    const uint32_t grid2 = (uint32_t)std::min<int64_t>(pair_items, g_attn_sm_count > 0 ? g_attn_sm_count : 148);
+    const int64_t pair_items = items / 2, pairs = q_tiles / 2;
+    const int64_t sms = g_attn_sm_count > 0 ? g_attn_sm_count : 148;
+    P.heads_per_round = (uint32_t)std::min<int64_t>(sms / pairs, batch * heads);
+    // every SM gets a CTA: those beyond heads_per_round * pairs are the spares of pair_layout()
+    const uint32_t grid2 = (uint32_t)std::min<int64_t>(pair_items, sms);
     attention_causal_pair_kernel<<<grid2, kPairAttnThreads, kPairAttnSmem, (cudaStream_t)stream>>>(mq, mk, mv, P);
     TSB_CHECK_LAUNCH();
     return TS_OK;
