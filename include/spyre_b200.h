@@ -262,6 +262,16 @@ int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t
                 int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream);
 int ts_gemm_error_state(void);
 
+/* ts_gemm_f16 with a residual: c = fp16(a x b [+ bias]) + residual, the sum taken in fp16 exactly
+ * as a separate add of the rounded product would (residual: stick image shaped like c, may be c
+ * itself's input of a skip connection, must not alias c).  Stands in for the mm + add pair of a
+ * residual block (codegen/inputs/spyre_torch_ops.cpp:214-452 followed by the add wrapper of
+ * codegen/templates/base.jinja2) and for addmm with a matrix-shaped bias
+ * (spyre_torch_ops.cpp:380-452). */
+int ts_gemm_f16_residual(const void* a, const void* b, const void* bias, const void* residual,
+                         void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int b_kmajor,
+                         int b_batched, void* stream);
+
 /* ts_gemm_f16 with explicit image strides and an extra "heads" dim, so that the per-head
  * matmuls of attention read Q / K / V straight out of the packed [batch, seq, heads*128]
  * images and write O straight into one: for every head h and batch entry b,

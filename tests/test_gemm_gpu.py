@@ -108,3 +108,15 @@ def test_linearity_property_full_width(cuda):
     rhs = down(K.matmul(up(a1, cuda), sb)).float() + down(K.matmul(up(a2, cuda), sb)).float()
     torch.testing.assert_close(lhs, rhs, rtol=2e-2, atol=2e-2)
     no_kernel_timeout()
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 64, 256), (130, 70, 300), (512, 1024, 768), (67, 256, 128)])
+def test_residual_in_epilogue(m, k, n, cuda):
+    """c = fp16(a @ w.T + bias) + residual, bit for bit what a separate fp16 add would give."""
+    a, w, bias, res = rnd(m, k, seed=1), rnd(n, k, seed=2, scale=0.05), rnd(n, seed=3), rnd(m, n, seed=4)
+    fused = K.matmul(up(a, cuda), up(w, cuda), bias=up(bias, cuda), b_kmajor=True, residual=up(res, cuda))
+    plain = K.matmul(up(a, cuda), up(w, cuda), bias=up(bias, cuda), b_kmajor=True)
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    assert torch.equal(down(fused), down(plain) + res)
+    assert_close(down(fused), (a.float() @ w.float().t() + bias.float()).half() + res)

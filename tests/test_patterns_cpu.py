@@ -55,11 +55,12 @@ def test_rewrites_on_decoder_layer_graphs():
         want = f(xh, ch, sh)
         got = torch.compile(f, backend=backend)(xh, ch, sh)
     assert seen["sdpa"] == 1
-    assert seen["count"] == 4                       # two RMS norms, rotary on q and on k
+    assert seen["count"] == 6        # two RMS norms, rotary on q and on k, two residual matmuls
     after = seen["after"]
     assert sum("spyre.rms_norm" in t for t in after) == 2
     assert sum("spyre.rotary" in t for t in after) == 2
     assert sum("spyre.sdpa_causal" in t for t in after) == 1
+    assert sum("aten.addmm" in t for t in after) == 2     # o_proj and down_proj take their residuals
     assert not any("aten.cat" in t or "aten.pow" in t or "aten.rsqrt" in t for t in after)
     torch.testing.assert_close(got, want, rtol=1e-2, atol=2e-3)
 

@@ -224,3 +224,11 @@ def test_vector_norm(ord, shape, dim):
     want = torch.linalg.vector_norm(x.float(), ord, dim)
     # a fully reduced result is a 1-element 1-D tensor on the device (as 0-dim tensors are)
     assert_close(got.reshape(want.shape), want.half())
+
+
+def test_addmm_with_matrix_bias_matches_mm_plus_add():
+    a, b, r = _rnd(130, 70, seed=1), _rnd(70, 200, seed=2) * 0.1, _rnd(130, 200, seed=3)
+    d = [t.to(DEV) for t in (a, b, r)]
+    got = torch.addmm(d[2], d[0], d[1]).cpu()
+    assert torch.equal(got, (torch.mm(d[0], d[1]) + d[2]).cpu())
+    assert_close(got, torch.addmm(r, a, b))

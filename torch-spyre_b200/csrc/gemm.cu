@@ -47,6 +47,7 @@ __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
 struct GemmParams {
   __half* c;
   const __half* bias;   // [N] stick image or null
+  const __half* residual;   // image shaped and strided like c, added to the rounded product, or null
   uint32_t M, N, K, batch, heads;
   int64_t c_stick_stride, c_head_stride;   // elements
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
@@ -121,8 +122,17 @@ __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int rr = i * 4 + srow;
-      const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
-      if (row0 + rr < P.M) st_global_v4(dst + (int64_t)rr * kStickHalfs, v);
+      Vec8h v;
+      v.u = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
+      if (row0 + rr < P.M) {
+        if (P.residual) {   // fp16 sum of the rounded product and the residual: what add(r, mm(a, b)) gives
+          Vec8h r;
+          r.u = ld_global_v4(P.residual + (dst - P.c) + (int64_t)rr * kStickHalfs);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) v.h2[e] = __hadd2(v.h2[e], r.h2[e]);
+        }
+        st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
+      }
     }
     __syncwarp();
   }
@@ -450,11 +460,12 @@ int g_sm_count = 0;
 
 using namespace tsb;
 
-extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_head_stride,
-                              const void* b, int64_t b_stick_stride, int64_t b_head_stride,
-                              const void* bias, void* c, int64_t c_stick_stride,
-                              int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
-                              int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream) {
+static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_stride,
+                       const void* b, int64_t b_stick_stride, int64_t b_head_stride,
+                       const void* bias, const void* residual, void* c, int64_t c_stick_stride,
+                       int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
+                       int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream) {
+  if ((uintptr_t)residual % 16) return TS_ERR_ALIGNMENT;
   if (heads < 0 || batch < 0 || M < 0 || N < 0 || K < 0) return TS_ERR_INVALID;
   if (heads == 0 || batch == 0 || M == 0 || N == 0) return TS_OK;
   if (!a || !b || !c) return TS_ERR_INVALID;
@@ -474,6 +485,7 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
   GemmParams P{};
   P.c = (__half*)c;
   P.bias = (const __half*)bias;
+  P.residual = (const __half*)residual;
   P.M = (uint32_t)M; P.N = (uint32_t)N; P.K = (uint32_t)K;
   P.batch = (uint32_t)batch; P.heads = (uint32_t)heads;
   P.c_stick_stride = c_stick_stride;
@@ -531,11 +543,28 @@ extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_h
   return TS_OK;
 }
 
+extern "C" int ts_gemm_f16_ex(const void* a, int64_t a_stick_stride, int64_t a_head_stride,
+                              const void* b, int64_t b_stick_stride, int64_t b_head_stride,
+                              const void* bias, void* c, int64_t c_stick_stride,
+                              int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
+                              int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream) {
+  return gemm_launch(a, a_stick_stride, a_head_stride, b, b_stick_stride, b_head_stride, bias, nullptr,
+                     c, c_stick_stride, c_head_stride, heads, batch, M, N, K, b_kmajor, b_batched,
+                     stream);
+}
+
 extern "C" int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch,
                            int64_t M, int64_t N, int64_t K, int b_kmajor, int b_batched,
                            void* stream) {
-  return ts_gemm_f16_ex(a, 0, 0, b, 0, 0, bias, c, 0, 0, 1, batch, M, N, K, b_kmajor, b_batched,
-                        stream);
+  return gemm_launch(a, 0, 0, b, 0, 0, bias, nullptr, c, 0, 0, 1, batch, M, N, K, b_kmajor, b_batched,
+                     stream);
+}
+
+extern "C" int ts_gemm_f16_residual(const void* a, const void* b, const void* bias,
+                                    const void* residual, void* c, int64_t batch, int64_t M,
+                                    int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream) {
+  return gemm_launch(a, 0, 0, b, 0, 0, bias, residual, c, 0, 0, 1, batch, M, N, K, b_kmajor,
+                     b_batched, stream);
 }
 
 // Synchronises the device and reports (and clears) the sticky error word the GEMM

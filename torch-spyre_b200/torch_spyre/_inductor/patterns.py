@@ -10,7 +10,8 @@ tests/test_modules.py:178-211) runs on the fused kernels.
   ``F.scaled_dot_product_attention(..., is_causal=True)`` -> ``spyre.sdpa_causal``.
 * ``rewrite_aten_graph`` runs on the aten graph AOT autograd produces:
   the fp32 RMS-norm idiom -> ``spyre.rms_norm``; rotary position embedding on
-  ``[batch, heads, seq, 128]`` views of a projection -> ``spyre.rotary``.
+  ``[batch, heads, seq, 128]`` views of a projection -> ``spyre.rotary``; a residual added to a
+  matmul -> ``addmm`` with a matrix-shaped bias, which the GEMM adds in its epilogue.
 """
 from __future__ import annotations
 
@@ -171,11 +172,57 @@ def _match_rotary(add: Node):
     return None
 
 
+def _match_residual_mm(add: Node):
+    """res + mm(a, b).view(shape)  (either operand order; the view is optional)."""
+    if not _is(add, aten.add.Tensor) or len(add.args) != 2 or add.kwargs.get("alpha", 1) != 1:
+        return None
+    for i in (0, 1):
+        res, prod = add.args[i], add.args[1 - i]
+        if not isinstance(res, Node) or not isinstance(prod, Node):
+            continue
+        view = prod if (_is(prod, aten.view.default) or _is(prod, aten._unsafe_view.default)) else None
+        mm = view.args[0] if view is not None else prod
+        if not _is(mm, aten.mm.default):
+            continue
+        ms, rs, outs = _shape(mm), _shape(res), _shape(add)
+        if ms is None or rs is None or rs != outs or len(ms) != 2:
+            continue
+        if ms[0] * ms[1] != math.prod(rs) or rs[-1] != ms[1]:
+            continue
+        if view is not None and not (_only_users(view, add) and _only_users(mm, view)):
+            continue
+        if view is None and not _only_users(mm, add):
+            continue
+        if res is mm or res is view:
+            continue
+        return res, mm, view
+    return None
+
+
 def rewrite_aten_graph(gm: GraphModule) -> int:
     g = gm.graph
     count = 0
     for n in list(g.nodes):
         if n.op != "call_function" or not n.users and n.op != "output":
+            continue
+        hit = _match_residual_mm(n)
+        if hit is not None:
+            res, mm, view = hit
+            m_rows, n_cols = _shape(mm)
+            out_shape = list(_shape(n))
+            with g.inserting_before(n):
+                res2 = g.call_function(aten.reshape.default, (res, [m_rows, n_cols]))
+                am = g.call_function(aten.addmm.default, (res2, mm.args[0], mm.args[1]))
+                new = g.call_function(aten.reshape.default, (am, out_shape))
+            for node, shp in ((res2, (m_rows, n_cols)), (am, (m_rows, n_cols))):
+                node.meta = {"val": torch.empty(shp, dtype=torch.float16, device="meta")}
+            new.meta = dict(n.meta)
+            n.replace_all_uses_with(new)
+            g.erase_node(n)
+            if view is not None:
+                g.erase_node(view)
+            g.erase_node(mm)
+            count += 1
             continue
         hit = _match_rms_norm(n)
         if hit is not None:

@@ -501,7 +501,8 @@ def _weight_operand(b: torch.Tensor) -> Tuple[StickTensor, bool]:
     return _st(b), False
 
 
-def _matmul(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+def _matmul(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     _check_fp16(a, b)
     if a.shape[-1] != b.shape[-2]:
         raise RuntimeError(f"mat1 and mat2 shapes cannot be multiplied ({tuple(a.shape)} and {tuple(b.shape)})")
@@ -513,7 +514,7 @@ def _matmul(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = Non
     with _with_device(a):
         sb, kmajor = _weight_operand(b)
         K.matmul(_st(a), sb, bias=_st(bias) if bias is not None else None, b_kmajor=kmajor,
-                 out=_st(out))
+                 out=_st(out), residual=_st(residual) if residual is not None else None)
     return out
 
 
@@ -531,6 +532,9 @@ def _bmm(a, b):
 def _addmm(bias, a, b, *, beta=1, alpha=1):
     if float(beta) == 1.0 and float(alpha) == 1.0 and bias.dim() == 1 and bias.shape[0] == b.shape[-1]:
         return _matmul(a, b, bias)
+    if float(beta) == 1.0 and float(alpha) == 1.0 and a.dim() == 2 and a.shape[-1] > 0 and \
+            tuple(bias.shape) == (a.shape[0], b.shape[-1]) and bias.dtype == torch.float16:
+        return _matmul(a, b, residual=bias)     # matrix-shaped bias: added in the GEMM epilogue
     prod = _matmul(a, b)
     if float(alpha) != 1.0:
         prod = _binary("MUL", prod, float(alpha))

@@ -351,9 +351,11 @@ def run_chain(chain: Chain, out_shape: Sequence[int], n_outputs: int = 1,
 # ---- matmul ---------------------------------------------------------------------
 
 def matmul(a: StickTensor, b: StickTensor, bias: Optional[StickTensor] = None,
-           b_kmajor: bool = False, out: Optional[StickTensor] = None) -> StickTensor:
+           b_kmajor: bool = False, out: Optional[StickTensor] = None,
+           residual: Optional[StickTensor] = None) -> StickTensor:
     """a: [..., M, K].  b: [K, N] or [batch..., K, N] (b_kmajor=False), or [N, K] /
-    [batch..., N, K] (b_kmajor=True, i.e. a @ b^T).  fp32 accumulation, fp16 result."""
+    [batch..., N, K] (b_kmajor=True, i.e. a @ b^T).  fp32 accumulation, fp16 result; `residual`
+    (shaped like the result) is added to the rounded product in the epilogue."""
     if len(a.shape) < 2 or len(b.shape) < 2:
         raise _abi.SpyreKernelError("matmul operands need at least 2 dims")
     M, K = a.shape[-2], a.shape[-1]
@@ -378,6 +380,14 @@ def matmul(a: StickTensor, b: StickTensor, bias: Optional[StickTensor] = None,
         M, batch = M * batch, 1
     if out is None:
         out = empty(tuple(a.shape[:-1]) + (N,), torch.float16, a.image.device)
+    if residual is not None:
+        if tuple(residual.shape) != tuple(out.shape):
+            raise _abi.SpyreKernelError(f"residual shape {residual.shape} != result shape {out.shape}")
+        rc = _abi.lib().ts_gemm_f16_residual(a.ptr(), b.ptr(), bias.ptr() if bias is not None else None,
+                                             residual.ptr(), out.ptr(), batch, M, N, K, int(b_kmajor),
+                                             int(b_batched), _stream())
+        _abi.check(rc, "ts_gemm_f16_residual")
+        return out
     rc = _abi.lib().ts_gemm_f16(a.ptr(), b.ptr(), bias.ptr() if bias is not None else None,
                                 out.ptr(), batch, M, N, K, int(b_kmajor), int(b_batched),
                                 _stream())
