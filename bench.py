@@ -414,7 +414,7 @@ def make_workload(name: str, dev, scale_rows=None):
         return dict(step_dev=step_dev, step_e2e=step_e2e, alg_bytes=0,
                     flops=LR.layer_flops(batch, seq, cfg, causal=True),
                     cpu_flops=LR.layer_flops(1, 512, cfg, causal=True), scaling="strong",
-                    h2d=xh.numel() * 2, d2h=xh.numel() * 2, launches=13,
+                    h2d=xh.numel() * 2, d2h=xh.numel() * 2, launches=11,
                     desc=("transformers LlamaDecoderLayer (unmodified)" if name == "hf_llama_layer"
                           else "Llama-style decoder layer") +
                          " through torch.compile on spyre: d_model 4096, 32 heads x 128, "

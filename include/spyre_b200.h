@@ -268,6 +268,16 @@ int ts_gemm_error_state(void);
  * residual block (codegen/inputs/spyre_torch_ops.cpp:214-452 followed by the add wrapper of
  * codegen/templates/base.jinja2) and for addmm with a matrix-shaped bias
  * (spyre_torch_ops.cpp:380-452). */
+/* A SwiGLU gate/up pair as one GEMM: c[batch, M, N_out] = silu(a x Wg^T) * (a x Wu^T), where
+ * w_gate_up is the stick image of the [2*N_out, K] weight whose rows alternate in blocks of 64
+ * between Wg and Wu (rows 128j..128j+63 = Wg rows 64j.., rows 128j+64..128j+127 = Wu rows 64j..).
+ * N_out must be a multiple of 64.  Roundings are those of the unfused sequence (each product,
+ * the silu and the multiply rounded to fp16).  Stands in for the two matmul programs, the silu
+ * and the mul the reference would run for an MLP block (torch_spyre/_inductor/lowering.py:25-47,
+ * codegen/compute_ops.py:60-393). */
+int ts_gemm_f16_swiglu(const void* a, const void* w_gate_up, void* c, int64_t batch, int64_t M,
+                       int64_t N_out, int64_t K, void* stream);
+
 int ts_gemm_f16_residual(const void* a, const void* b, const void* bias, const void* residual,
                          void* c, int64_t batch, int64_t M, int64_t N, int64_t K, int b_kmajor,
                          int b_batched, void* stream);

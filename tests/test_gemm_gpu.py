@@ -120,3 +120,20 @@ def test_residual_in_epilogue(m, k, n, cuda):
     no_kernel_timeout()
     assert torch.equal(down(fused), down(plain) + res)
     assert_close(down(fused), (a.float() @ w.float().t() + bias.float()).half() + res)
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 64, 128), (130, 70, 320), (512, 256, 704), (67, 128, 64)])
+def test_swiglu_gemm(m, k, n, cuda):
+    """silu(a @ wg.T) * (a @ wu.T) as one GEMM over the interleaved weight, against the unfused
+    device sequence and the CPU formula."""
+    import torch.nn.functional as F
+    from torch_spyre._inductor.customops import interleave_gate_up
+
+    a, wg, wu = rnd(m, k, seed=1), rnd(n, k, seed=2, scale=0.1), rnd(n, k, seed=3, scale=0.1)
+    fused = down(K.swiglu_matmul(up(a, cuda), up(interleave_gate_up(wg, wu), cuda)))
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    gate = down(K.matmul(up(a, cuda), up(wg, cuda), b_kmajor=True))
+    upp = down(K.matmul(up(a, cuda), up(wu, cuda), b_kmajor=True))
+    assert_close(fused, F.silu(gate) * upp)
+    assert_close(fused, F.silu(F.linear(a, wg)) * F.linear(a, wu))

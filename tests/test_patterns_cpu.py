@@ -55,12 +55,13 @@ def test_rewrites_on_decoder_layer_graphs():
         want = f(xh, ch, sh)
         got = torch.compile(f, backend=backend)(xh, ch, sh)
     assert seen["sdpa"] == 1
-    assert seen["count"] == 6        # two RMS norms, rotary on q and on k, two residual matmuls
+    assert seen["count"] == 7        # two RMS norms, rotary on q and on k, two residual matmuls, SwiGLU
     after = seen["after"]
     assert sum("spyre.rms_norm" in t for t in after) == 2
     assert sum("spyre.rotary" in t for t in after) == 2
     assert sum("spyre.sdpa_causal" in t for t in after) == 1
     assert sum("aten.addmm" in t for t in after) == 2     # o_proj and down_proj take their residuals
+    assert sum("spyre.swiglu_linear" in t for t in after) == 1 and not any("aten.silu" in t for t in after)
     assert not any("aten.cat" in t or "aten.pow" in t or "aten.rsqrt" in t for t in after)
     torch.testing.assert_close(got, want, rtol=1e-2, atol=2e-3)
 

@@ -48,6 +48,7 @@ struct GemmParams {
   __half* c;
   const __half* bias;   // [N] stick image or null
   const __half* residual;   // image shaped and strided like c, added to the rounded product, or null
+  int swiglu;               // 1: stick columns of the product alternate gate / up; c = silu(gate) * up
   uint32_t M, N, K, batch, heads;
   int64_t c_stick_stride, c_head_stride;   // elements
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
@@ -133,6 +134,58 @@ __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, 
         }
         st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
       }
+    }
+    __syncwarp();
+  }
+}
+
+// The drain for a gate/up projection pair computed as one product whose stick columns alternate
+// gate, up, gate, up: every pair of accumulator sticks becomes one output stick
+// silu(gate) * up, with the roundings of the unfused sequence (product -> fp16, silu -> fp16,
+// multiply -> fp16).
+__device__ __forceinline__ float silu_of(float x) {
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
+  return x * __fdividef(1.f, 1.f + e);
+}
+__device__ __forceinline__ void drain_rows_swiglu(const GemmParams& P, uint32_t taddr, uint8_t* stage,
+                                                  uint32_t row0, uint32_t col0, uint32_t b, uint32_t h,
+                                                  int lane) {
+  const uint32_t c_sticks = (P.N / 2 + 63) / 64;
+  const int srow = lane >> 3, piece = lane & 7;
+#pragma unroll 1
+  for (int pair = 0; pair < BN / 128; ++pair) {
+    const uint32_t stick = (col0 >> 7) + pair;
+    if (stick >= c_sticks) break;   // warp-uniform
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+      uint32_t g[32], u[32];
+      ptx::tmem_ld_32x32(taddr + pair * 128 + sub * 32, g);
+      ptx::tmem_ld_32x32(taddr + pair * 128 + 64 + sub * 32, u);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        Vec8h o;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = v * 8 + 2 * e;
+          const __half2 g16 = __floats2half2_rn(__uint_as_float(g[i]), __uint_as_float(g[i + 1]));
+          const __half2 u16 = __floats2half2_rn(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
+          const float2 gf = __half22float2(g16);
+          const __half2 s16 = __floats2half2_rn(silu_of(gf.x), silu_of(gf.y));
+          o.h2[e] = __hmul2(s16, u16);
+        }
+        *reinterpret_cast<uint4*>(stage + lane * 128 + (((sub * 4 + v) ^ (lane & 7)) * 16)) = o.u;
+      }
+    }
+    __syncwarp();
+    __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
+                  ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int rr = i * 4 + srow;
+      const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
+      if (row0 + rr < P.M) st_global_v4(dst + (int64_t)rr * kStickHalfs, v);
     }
     __syncwarp();
   }
@@ -265,8 +318,12 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
       ptx::tc_fence_after_sync();
-      drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
-                 tm * BM + q * 32, tn * BN, b, h, lane);
+      if (P.swiglu)
+        drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
+                          tm * BM + q * 32, tn * BN, b, h, lane);
+      else
+        drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
+                   tm * BM + q * 32, tn * BN, b, h, lane);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
@@ -432,8 +489,12 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
       ptx::tc_fence_after_sync();
-      drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
-                 tm * 2 * BM + rank * BM + q * 32, tn * BN, b, h, lane);
+      if (P.swiglu)
+        drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
+                          tm * 2 * BM + rank * BM + q * 32, tn * BN, b, h, lane);
+      else
+        drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
+                   tm * 2 * BM + rank * BM + q * 32, tn * BN, b, h, lane);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0)
@@ -464,8 +525,10 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
                        const void* b, int64_t b_stick_stride, int64_t b_head_stride,
                        const void* bias, const void* residual, void* c, int64_t c_stick_stride,
                        int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
-                       int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream) {
+                       int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream,
+                       int swiglu = 0) {
   if ((uintptr_t)residual % 16) return TS_ERR_ALIGNMENT;
+  if (swiglu && (N % 128 != 0 || bias || residual)) return TS_ERR_UNSUPPORTED;
   if (heads < 0 || batch < 0 || M < 0 || N < 0 || K < 0) return TS_ERR_INVALID;
   if (heads == 0 || batch == 0 || M == 0 || N == 0) return TS_OK;
   if (!a || !b || !c) return TS_ERR_INVALID;
@@ -486,6 +549,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   P.c = (__half*)c;
   P.bias = (const __half*)bias;
   P.residual = (const __half*)residual;
+  P.swiglu = swiglu ? 1 : 0;
   P.M = (uint32_t)M; P.N = (uint32_t)N; P.K = (uint32_t)K;
   P.batch = (uint32_t)batch; P.heads = (uint32_t)heads;
   P.c_stick_stride = c_stick_stride;
@@ -577,4 +641,14 @@ extern "C" int ts_gemm_error_state(void) {
     cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
   }
   return v;
+}
+
+extern "C" int ts_gemm_f16_swiglu(const void* a, const void* w_gate_up, void* c, int64_t batch,
+                                  int64_t M, int64_t N_out, int64_t K, void* stream) {
+  if (N_out < 0) return TS_ERR_INVALID;
+  if (N_out % 64 != 0) return TS_ERR_UNSUPPORTED;
+  // the product has 2 * N_out columns; the result image has N_out: its default stick stride is
+  // that of a dense [batch, M, N_out] image, which is also what the product's would be
+  return gemm_launch(a, 0, 0, w_gate_up, 0, 0, nullptr, nullptr, c, 0, 0, 1, batch, M, 2 * N_out, K, 1, 0,
+                     stream, 1);
 }

@@ -75,6 +75,8 @@ SIGNATURES = {
     "ts_gemm_f16": (ctypes.c_int, [vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                    ctypes.c_int64, ctypes.c_int, ctypes.c_int, vp]),
     "ts_gemm_error_state": (ctypes.c_int, []),
+    "ts_gemm_f16_swiglu": (ctypes.c_int, [vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                          ctypes.c_int64, vp]),
     "ts_gemm_f16_residual": (ctypes.c_int, [vp, vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64,
                                             ctypes.c_int64, ctypes.c_int64, ctypes.c_int, ctypes.c_int,
                                             vp]),

@@ -147,6 +147,40 @@ def _(x, cos, sin, heads):
     return x.new_empty(x.size())
 
 
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[2N, K] weight whose rows alternate between w_gate and w_up in blocks of 64: the operand of
+    the fused SwiGLU GEMM, whose 256-column tiles then hold matching gate / up stick pairs."""
+    n, k = w_gate.shape
+    return torch.stack((w_gate.reshape(n // 64, 64, k), w_up.reshape(n // 64, 64, k)), dim=1).reshape(2 * n, k)
+
+
+_gate_up_cache: dict = {}
+
+
+@torch.library.custom_op("spyre::swiglu_linear", mutates_args=())
+def swiglu_linear(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """silu(x @ w_gate^T) * (x @ w_up^T); x: [..., K], weights [N, K]."""
+    if _on_spyre(x) and w_gate.shape[0] % 64 == 0:
+        from .. import ops, stick_ops as K
+
+        key = (w_gate.data_ptr(), w_up.data_ptr(), w_gate._version, w_up._version, tuple(w_gate.shape))
+        w = _gate_up_cache.get(key)
+        if w is None:
+            if len(_gate_up_cache) >= 8:
+                _gate_up_cache.clear()
+            w = _gate_up_cache[key] = interleave_gate_up(w_gate, w_up)
+        out = torch.empty(tuple(x.shape[:-1]) + (w_gate.shape[0],), dtype=x.dtype, device=x.device)
+        with torch.cuda.device(x.device.index or 0):
+            K.swiglu_matmul(ops._st(x), ops._st(w), out=ops._st(out))
+        return out
+    return torch.nn.functional.silu(torch.nn.functional.linear(x, w_gate)) * torch.nn.functional.linear(x, w_up)
+
+
+@swiglu_linear.register_fake
+def _(x, w_gate, w_up):
+    return x.new_empty(tuple(x.shape[:-1]) + (w_gate.shape[0],))
+
+
 @torch.library.custom_op("spyre::sdpa_causal", mutates_args=())
 def sdpa_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
     """F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale) on [batch, heads, seq,

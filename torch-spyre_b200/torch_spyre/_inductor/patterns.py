@@ -11,7 +11,8 @@ tests/test_modules.py:178-211) runs on the fused kernels.
 * ``rewrite_aten_graph`` runs on the aten graph AOT autograd produces:
   the fp32 RMS-norm idiom -> ``spyre.rms_norm``; rotary position embedding on
   ``[batch, heads, seq, 128]`` views of a projection -> ``spyre.rotary``; a residual added to a
-  matmul -> ``addmm`` with a matrix-shaped bias, which the GEMM adds in its epilogue.
+  matmul -> ``addmm`` with a matrix-shaped bias, which the GEMM adds in its epilogue;
+  ``silu(x @ Wg^T) * (x @ Wu^T)`` -> ``spyre.swiglu_linear`` (one GEMM over interleaved weights).
 """
 from __future__ import annotations
 
@@ -199,11 +200,75 @@ def _match_residual_mm(add: Node):
     return None
 
 
+def _linear_parts(v):
+    """(view, mm, x2d, weight) of ``mm(x2d, weight^T)`` seen through an optional view."""
+    view = v if (_is(v, aten.view.default) or _is(v, aten._unsafe_view.default)) else None
+    mm = view.args[0] if view is not None else v
+    if not _is(mm, aten.mm.default):
+        return None
+    wt = mm.args[1]
+    if _is(wt, aten.permute.default) and list(wt.args[1]) == [1, 0]:
+        w = wt.args[0]
+    elif _is(wt, aten.t.default):
+        w = wt.args[0]
+    else:
+        return None
+    if view is not None and not _only_users(mm, view):
+        return None
+    return view, mm, mm.args[0], w
+
+
+def _same_matrix(a, b) -> bool:
+    """The same node, or two views of one source with the same shape."""
+    if a is b:
+        return True
+    views = (aten.view.default, aten._unsafe_view.default, aten.reshape.default)
+    return (isinstance(a, Node) and isinstance(b, Node) and a.target in views and b.target in views and
+            a.args[0] is b.args[0] and _shape(a) == _shape(b) and _shape(a) is not None)
+
+
+def _match_swiglu(mul: Node):
+    """silu(x @ Wg^T) * (x @ Wu^T)"""
+    if not _is(mul, aten.mul.Tensor) or len(mul.args) != 2:
+        return None
+    for i in (0, 1):
+        act, up = mul.args[i], mul.args[1 - i]
+        if not (_is(act, aten.silu.default) and _only_users(act, mul) and isinstance(up, Node)):
+            continue
+        gp, upp = _linear_parts(act.args[0]), _linear_parts(up)
+        if gp is None or upp is None:
+            continue
+        (gv, gmm, gx, wg), (uv, umm, ux, wu) = gp, upp
+        ws = _shape(wg)
+        if ws is None or ws != _shape(wu) or len(ws) != 2 or ws[0] % 64 or not _same_matrix(gx, ux):
+            continue
+        g_out = gv if gv is not None else gmm
+        u_out = uv if uv is not None else umm
+        if not (_only_users(g_out, act) and _only_users(u_out, mul)):
+            continue
+        return gx, wg, wu, [mul, act] + [n for n in (gv, gmm, uv, umm) if n is not None]
+    return None
+
+
 def rewrite_aten_graph(gm: GraphModule) -> int:
     g = gm.graph
     count = 0
     for n in list(g.nodes):
         if n.op != "call_function" or not n.users and n.op != "output":
+            continue
+        hit = _match_swiglu(n)
+        if hit is not None:
+            x2d, wg, wu, dead = hit
+            rows, n_out = _shape(x2d)[0], _shape(wg)[0]
+            with g.inserting_before(n):
+                fused = g.call_function(torch.ops.spyre.swiglu_linear.default, (x2d, wg, wu))
+                new = g.call_function(aten.reshape.default, (fused, list(_shape(n))))
+            fused.meta = {"val": torch.empty((rows, n_out), dtype=torch.float16, device="meta")}
+            new.meta = dict(n.meta)
+            n.replace_all_uses_with(new)
+            for d in dead:
+                g.erase_node(d)
+            count += 1
             continue
         hit = _match_residual_mm(n)
         if hit is not None:

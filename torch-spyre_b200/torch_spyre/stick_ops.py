@@ -395,6 +395,23 @@ def matmul(a: StickTensor, b: StickTensor, bias: Optional[StickTensor] = None,
     return out
 
 
+def swiglu_matmul(a: StickTensor, w_gate_up: StickTensor, out: Optional[StickTensor] = None) -> StickTensor:
+    """silu(a @ Wg^T) * (a @ Wu^T) in one GEMM.  a: [..., M, K]; w_gate_up: [2*N, K], rows alternating
+    between Wg and Wu in blocks of 64 (see ``interleave_gate_up``)."""
+    K = a.shape[-1]
+    n_out = w_gate_up.shape[0] // 2
+    if w_gate_up.shape[1] != K or n_out % 64:
+        raise _abi.SpyreKernelError(f"swiglu_matmul: weight {w_gate_up.shape} does not fit input {a.shape}")
+    m = 1
+    for s in a.shape[:-1]:
+        m *= s
+    if out is None:
+        out = empty(tuple(a.shape[:-1]) + (n_out,), torch.float16, a.image.device)
+    rc = _abi.lib().ts_gemm_f16_swiglu(a.ptr(), w_gate_up.ptr(), out.ptr(), 1, m, n_out, K, _stream())
+    _abi.check(rc, "ts_gemm_f16_swiglu")
+    return out
+
+
 # ---- attention pieces -------------------------------------------------------------
 
 def rotary(x: StickTensor, cos: StickTensor, sin: StickTensor, batch: int, seq: int, heads: int,
