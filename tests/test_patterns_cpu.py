@@ -77,3 +77,22 @@ def test_rms_norm_pattern_needs_exclusive_intermediates():
 
     gm = make_fx(f)(torch.randn(4, 64).half(), torch.ones(64).half())
     assert patterns.rewrite_aten_graph(gm) == 0
+
+
+def test_gate_up_interleave_and_its_cache():
+    from torch_spyre._inductor import customops as C
+
+    wg, wu = torch.randn(128, 64).half(), torch.randn(128, 64).half()
+    w = C.interleave_gate_up(wg, wu)
+    assert w.shape == (256, 64)
+    assert torch.equal(w[0:64], wg[0:64]) and torch.equal(w[64:128], wu[0:64])
+    assert torch.equal(w[128:192], wg[64:128]) and torch.equal(w[192:256], wu[64:128])
+    first = C._cached_gate_up(wg, wu)
+    assert C._cached_gate_up(wg, wu) is first
+    wg.add_(1)                                   # written to: the cached copy is stale
+    assert C._cached_gate_up(wg, wu) is not first
+    other = torch.randn(128, 64).half()          # a different tensor, wherever it lives
+    assert torch.equal(C._cached_gate_up(other, wu)[0:64], other[0:64])
+    x = torch.randn(5, 64).half()
+    want = torch.nn.functional.silu(x @ wg.t()) * (x @ wu.t())
+    torch.testing.assert_close(torch.ops.spyre.swiglu_linear(x, wg, wu), want)

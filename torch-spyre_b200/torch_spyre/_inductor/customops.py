@@ -157,18 +157,31 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
 _gate_up_cache: dict = {}
 
 
+def _cached_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """The interleaved weight for this pair of weight tensors, rebuilt whenever either tensor is a
+    different object, lives elsewhere or has been written to (an address alone could be a new
+    tensor in recycled memory)."""
+    import weakref
+
+    key = (id(w_gate), id(w_up))
+    stamp = (w_gate.data_ptr(), w_up.data_ptr(), w_gate._version, w_up._version, tuple(w_gate.shape))
+    hit = _gate_up_cache.get(key)
+    if hit is not None and hit[0]() is w_gate and hit[1]() is w_up and hit[2] == stamp:
+        return hit[3]
+    if len(_gate_up_cache) >= 16:
+        _gate_up_cache.clear()
+    w = interleave_gate_up(w_gate, w_up)
+    _gate_up_cache[key] = (weakref.ref(w_gate), weakref.ref(w_up), stamp, w)
+    return w
+
+
 @torch.library.custom_op("spyre::swiglu_linear", mutates_args=())
 def swiglu_linear(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     """silu(x @ w_gate^T) * (x @ w_up^T); x: [..., K], weights [N, K]."""
     if _on_spyre(x) and w_gate.shape[0] % 64 == 0:
         from .. import ops, stick_ops as K
 
-        key = (w_gate.data_ptr(), w_up.data_ptr(), w_gate._version, w_up._version, tuple(w_gate.shape))
-        w = _gate_up_cache.get(key)
-        if w is None:
-            if len(_gate_up_cache) >= 8:
-                _gate_up_cache.clear()
-            w = _gate_up_cache[key] = interleave_gate_up(w_gate, w_up)
+        w = _cached_gate_up(w_gate, w_up)
         out = torch.empty(tuple(x.shape[:-1]) + (w_gate.shape[0],), dtype=x.dtype, device=x.device)
         with torch.cuda.device(x.device.index or 0):
             K.swiglu_matmul(ops._st(x), ops._st(w), out=ops._st(out))
