@@ -232,3 +232,28 @@ def test_addmm_with_matrix_bias_matches_mm_plus_add():
     got = torch.addmm(d[2], d[0], d[1]).cpu()
     assert torch.equal(got, (torch.mm(d[0], d[1]) + d[2]).cpu())
     assert_close(got, torch.addmm(r, a, b))
+
+
+def test_cat_edge_cases():
+    a, b = _rnd(3, 70, seed=1), _rnd(0, 70, seed=2)
+    assert torch.equal(torch.cat([a.to(DEV), b.to(DEV)], 0).cpu(), torch.cat([a, b], 0))
+    legacy_empty = torch.empty(0, dtype=torch.float16)            # 1-D empties are skipped
+    assert torch.equal(torch.cat([legacy_empty.to(DEV), a.to(DEV)], 0).cpu(), a)
+    t = _rnd(6, 130, seed=3).to(DEV)
+    assert torch.equal(torch.cat([t[:, :64], t[:, 64:]], 1).cpu(), t.cpu())      # views as inputs
+    assert torch.equal(torch.cat([t.t(), t.t()], 0).cpu(), torch.cat([t.cpu().t(), t.cpu().t()], 0))
+    with pytest.raises(RuntimeError):
+        torch.cat([a.to(DEV), _rnd(3, 71).to(DEV)], 0)
+
+
+def test_vector_norm_keepdim_and_zero_rows():
+    x = _rnd(4, 300)
+    x[1] = 0
+    got = torch.linalg.vector_norm(x.to(DEV), 2, -1, keepdim=True).cpu()
+    assert got.shape == (4, 1) and got[1, 0] == 0
+    assert_close(got, torch.linalg.vector_norm(x.float(), 2, -1, keepdim=True).half())
+
+
+def test_tril_rejects_vectors():
+    with pytest.raises(RuntimeError):
+        torch.tril(_rnd(5).to(DEV))
