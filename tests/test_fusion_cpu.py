@@ -112,3 +112,87 @@ def test_slot_pressure_is_reported():
     with pytest.raises(fusion.CannotFuse):
         for g in groups:
             fusion.linearise(g, compiler._outside_users(owner, g))
+
+
+class _EmulatingCompile:
+    """Stand-in for SpyreAsyncCompile on a machine without the device: runs a fused program
+    with the host emulator of the instruction set."""
+
+    def sdsc(self, name, spec):
+        info = spec.op_info
+
+        class Runner:
+            def run(self, *tensors):
+                nodes = [object() for _ in tensors]
+                outs = [object() for _ in range(info["n_outputs"])]
+                red = object() if info["reduce"] else None
+                prog = fusion.Program(info["insns"], nodes, outs, tuple(spec.dimensions), info["reduce"],
+                                      info["reduce_scale"], info["keepdim"], red)
+                got = fusion.emulate(prog, dict(zip(nodes, tensors)))
+                return [got[o] for o in outs] + ([got[red]] if red is not None else [])
+
+        return Runner()
+
+    def wait(self, scope):
+        pass
+
+
+def run_compiled(monkeypatch, fn, *inputs):
+    monkeypatch.setattr(compiler, "SpyreAsyncCompile", _EmulatingCompile)
+    gm = trace(fn, *inputs)
+    cg = compiler.CompiledGraph(gm)
+    got = cg(list(inputs))
+    want = fn(*inputs)
+    got = got if isinstance(got, (tuple, list)) else (got,)
+    want = want if isinstance(want, (tuple, list)) else (want,)
+    for g, w in zip(got, want):
+        torch.testing.assert_close(g.float(), w.float(), rtol=1e-2, atol=2e-3)
+    return cg
+
+
+def test_outside_reader_between_members_of_a_group(monkeypatch):
+    """exp feeds a matmul and a later add: [exp, add] fuse, and the fused launch has to be
+    scheduled before the matmul that reads exp's stored result."""
+    def fn(t, w):
+        p1 = torch.exp(t)
+        q = p1 @ w
+        p2 = p1 + 1.0
+        return q, p2
+
+    cg = run_compiled(monkeypatch, fn, x(32, 64) * 0.1, x(64, 64, seed=1) * 0.1)
+    assert cg.fused_nodes == 2 and len(cg.kernel_specs) == 1
+
+
+def test_outside_reader_between_group_and_its_reduction(monkeypatch):
+    def fn(t, w):
+        e = torch.exp(t * 0.5)
+        q = e @ w
+        return q, e.sum(-1)
+
+    cg = run_compiled(monkeypatch, fn, x(32, 64) * 0.1, x(64, 64, seed=1) * 0.1)
+    assert len(cg.kernel_specs) == 1 and cg.kernel_specs[0].is_reduction
+
+
+def test_group_waits_for_a_late_input(monkeypatch):
+    """The second member's other operand is produced by a matmul that comes after the first
+    member: the fused launch has to wait for it."""
+    def fn(t, w):
+        a = torch.tanh(t)
+        m = t @ w
+        return (a + m) * 2.0
+
+    run_compiled(monkeypatch, fn, x(32, 64) * 0.1, x(64, 64, seed=1) * 0.1)
+
+
+def test_intermediates_are_released_after_their_last_reader(monkeypatch):
+    def fn(t, w):
+        h = torch.relu(t + 1.0)
+        y = h @ w
+        return torch.sigmoid(y) * 2.0
+
+    cg = run_compiled(monkeypatch, fn, x(32, 64), x(64, 64, seed=1))
+    freed = {i for f in cg.frees for i in f}
+    out_nodes = set()
+    torch.fx.node.map_arg(cg.output_node.args[0], lambda a: out_nodes.add(a) or a)
+    assert all(cg.slot[n] not in freed for n in out_nodes)
+    assert len(freed) >= 3      # inputs and both intermediates

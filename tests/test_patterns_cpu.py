@@ -96,3 +96,49 @@ def test_gate_up_interleave_and_its_cache():
     x = torch.randn(5, 64).half()
     want = torch.nn.functional.silu(x @ wg.t()) * (x @ wu.t())
     torch.testing.assert_close(torch.ops.spyre.swiglu_linear(x, wg, wu), want)
+
+
+def _sdpa_rewrites(q, k, v):
+    seen = {}
+
+    def backend(gm, example_inputs):
+        seen["count"] = patterns.rewrite_dynamo_graph(gm)
+        return gm.forward
+
+    f = lambda q, k, v: torch.nn.functional.scaled_dot_product_attention(q, k, v, is_causal=True)  # noqa: E731
+    torch._dynamo.reset()
+    torch.compile(f, backend=backend)(q, k, v)
+    return seen["count"]
+
+
+def test_sdpa_rewrite_only_for_what_the_fused_kernel_takes():
+    """head_dim 128, fp16, q / k / v of one shape: anything else keeps the stock SDPA."""
+    h = lambda *s: torch.randn(*s).half()  # noqa: E731
+    assert _sdpa_rewrites(h(1, 2, 16, 128), h(1, 2, 16, 128), h(1, 2, 16, 128)) == 1
+    assert _sdpa_rewrites(h(1, 2, 16, 64), h(1, 2, 16, 64), h(1, 2, 16, 64)) == 0        # head_dim 64
+    assert _sdpa_rewrites(torch.randn(1, 2, 16, 128), torch.randn(1, 2, 16, 128),
+                          torch.randn(1, 2, 16, 128)) == 0                                # fp32
+    assert _sdpa_rewrites(h(1, 2, 16, 128), h(1, 2, 24, 128), h(1, 2, 24, 128)) == 0     # longer keys
+
+
+def test_attention_wrapper_refuses_before_any_launch():
+    """The host wrapper validates shapes and head size itself; these calls must raise without
+    reaching the kernel library (the stand-in images are CPU tensors and are never read)."""
+    from torch_spyre import _abi, stick_ops as K
+
+    def st(*shape, dtype=torch.float16):
+        return K.StickTensor(torch.empty(0, dtype=dtype), tuple(shape), dtype)
+
+    with pytest.raises(_abi.SpyreKernelError, match="head_dim"):
+        K.causal_attention(st(1, 128, 128), st(1, 128, 128), st(1, 128, 128), 1, 128, 2, 0.1)   # head_dim 64
+    with pytest.raises(_abi.SpyreKernelError, match="one shape"):
+        K.causal_attention(st(1, 128, 256), st(1, 256, 256), st(1, 256, 256), 1, 128, 2, 0.1)
+    with pytest.raises(_abi.SpyreKernelError, match="out shape"):
+        K.causal_attention(st(1, 128, 256), st(1, 128, 256), st(1, 128, 256), 1, 128, 2, 0.1,
+                           out=st(1, 128, 128))
+    with pytest.raises(_abi.SpyreKernelError, match="float16"):
+        K.causal_attention(st(1, 128, 256, dtype=torch.bfloat16), st(1, 128, 256), st(1, 128, 256),
+                           1, 128, 2, 0.1)
+    with pytest.raises(_abi.SpyreKernelError, match="does not match"):
+        K.causal_attention(st(1, 128, 256), st(1, 128, 256), st(1, 128, 256), 2, 128, 2, 0.1)
+    K.check_attention_args((2, 128, 256), (2, 128, 256), (2, 128, 256), 2, (torch.float16,) * 3)

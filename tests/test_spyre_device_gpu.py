@@ -257,3 +257,36 @@ def test_vector_norm_keepdim_and_zero_rows():
 def test_tril_rejects_vectors():
     with pytest.raises(RuntimeError):
         torch.tril(_rnd(5).to(DEV))
+
+
+def test_mean_over_several_dims_keeps_partial_results_in_range():
+    """Constant inputs whose plain partial sums pass the fp16 maximum (65504): torch CPU eager
+    accumulates in fp32 and returns the constant; so must the staged device reduction."""
+    x = torch.full((8, 512, 4096), 10.0, dtype=torch.float16)
+    xs = x.to(DEV)
+    assert_close(xs.mean().cpu().reshape(()), x.mean())
+    assert_close(xs.mean((0, 1)).cpu(), x.mean((0, 1)))
+    assert_close(xs.mean((1, 2)).cpu(), x.mean((1, 2)))
+    assert_close(xs.mean((0, 2), keepdim=True).cpu(), x.mean((0, 2), keepdim=True))
+    ones = torch.ones(4, 2048, 1024, dtype=torch.float16)
+    assert ones.to(DEV).mean().cpu().item() == 1.0
+
+
+def test_scalar_first_operands_with_alpha():
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(67, 256, generator=g).half()
+    xs = x.to(DEV)
+    assert_close(torch.sub(3.0, xs, alpha=2).cpu(), torch.sub(3.0, x, alpha=2))
+    assert_close(torch.add(3.0, xs, alpha=0.5).cpu(), torch.add(3.0, x, alpha=0.5))
+    assert_close(torch.rsub(xs, 3.0, alpha=2).cpu(), torch.rsub(x, 3.0, alpha=2))
+    assert_close(torch.rsub(xs, 3.0).cpu(), torch.rsub(x, 3.0))
+    assert_close(torch.sub(xs, 3.0, alpha=2).cpu(), torch.sub(x, 3.0, alpha=2))
+
+
+def test_manual_seed_with_a_device_seeds_that_device():
+    torch.spyre.manual_seed(123, device=0)
+    assert torch.cuda.default_generators[0].initial_seed() == 123
+    torch.spyre.manual_seed(77, device=torch.device("spyre", 0))
+    assert torch.cuda.default_generators[0].initial_seed() == 77
+    with pytest.raises(RuntimeError):
+        torch.spyre.manual_seed(1, device=4096)

@@ -54,10 +54,17 @@ class _SpyreImpl:
         # a CUDA context does not survive fork(): the child must not touch the device
         self._in_bad_fork = True
 
-    def manual_seed(self, seed: int, device: int | None = None) -> None:
+    def manual_seed(self, seed: int, device=None) -> None:
         import torch
 
-        torch.cuda.manual_seed(int(seed)) if device is None else None
+        if device is None:
+            torch.cuda.manual_seed(int(seed))
+            return
+        index = device.index if isinstance(device, torch.device) else int(device)
+        if not 0 <= index < torch.cuda.device_count():
+            raise RuntimeError(f"manual_seed: no spyre device {index}")
+        with torch.cuda.device(index):
+            torch.cuda.manual_seed(int(seed))
 
     def manual_seed_all(self, seed: int) -> None:
         import torch

@@ -56,91 +56,207 @@ def spec_from_program(name: str, prog: fusion.Program) -> KernelSpec:
                       scales=scales, op_info=op_info)
 
 
+class _Unit:
+    """One schedulable piece of the plan: a fused group or a single FX node."""
+
+    __slots__ = ("produces", "needs", "make_step", "first")
+
+    def __init__(self, produces, needs, make_step, first):
+        self.produces, self.needs, self.make_step, self.first = produces, needs, make_step, first
+
+
+def _arg_reader(a, slot: Dict[Node, int]):
+    """Compiles one FX argument into (is_constant, value-or-reader): nodes become slot reads,
+    lists / tuples of nodes become readers that rebuild the container, the rest is constant."""
+    if isinstance(a, Node):
+        i = slot[a]
+        return False, (lambda env: env[i])
+    if isinstance(a, (list, tuple)):
+        parts = [_arg_reader(x, slot) for x in a]
+        if all(c for c, _ in parts):
+            return True, a
+        kind = type(a)
+        return False, (lambda env: kind(v if c else v(env) for c, v in parts))
+    if isinstance(a, dict):
+        parts = {k: _arg_reader(v, slot) for k, v in a.items()}
+        if all(c for c, _ in parts.values()):
+            return True, a
+        return False, (lambda env: {k: (v if c else v(env)) for k, (c, v) in parts.items()})
+    if isinstance(a, slice):
+        parts = [_arg_reader(x, slot) for x in (a.start, a.stop, a.step)]
+        if all(c for c, _ in parts):
+            return True, a
+        return False, (lambda env: slice(*[(v if c else v(env)) for c, v in parts]))
+    return True, a
+
+
 class CompiledGraph:
-    """Executable plan: fused launches and eager aten calls in graph order."""
+    """Executable plan: fused launches and eager aten calls, in an order that respects every
+    data dependency.  Values live in a flat slot list; each step's arguments are compiled once
+    into slot reads, and a value's slot is cleared after its last reader so that its memory goes
+    back to the allocator while the graph is still running."""
 
     def __init__(self, gm: GraphModule):
         self.gm = gm
-        self.steps: List[Callable[[Dict[Node, Any]], None]] = []
+        self.steps: List[Callable[[list], None]] = []
         self.kernel_specs: List[KernelSpec] = []
         self.fused_nodes = 0
         self.placeholders: List[Node] = [n for n in gm.graph.nodes if n.op == "placeholder"]
         self.output_node: Node = next(n for n in gm.graph.nodes if n.op == "output")
+        self.slot: Dict[Node, int] = {n: i for i, n in enumerate(gm.graph.nodes)}
         self._build()
 
-    def _build(self) -> None:
+    # -- planning ------------------------------------------------------------------------
+    def _units(self) -> List[_Unit]:
         graph = self.gm.graph
+        order = {n: i for i, n in enumerate(graph.nodes)}
         groups, owner = fusion.build_groups(graph)
         programs: Dict[int, fusion.Program] = {}
-        async_compile = SpyreAsyncCompile()
-        emitted: Dict[int, bool] = {}
-        for gi, g in enumerate(groups):
+        for g in groups:
             if len(g.nodes) == 1 and g.reduction is None:
                 continue  # a lone op gains nothing over its eager kernel
             try:
                 programs[id(g)] = fusion.linearise(g, _outside_users(owner, g))
             except (fusion.CannotFuse, Exception):
                 continue
+        units: List[_Unit] = []
+        seen: Dict[int, bool] = {}
         for n in graph.nodes:
             if n.op in ("placeholder", "output"):
                 continue
             g = owner.get(n)
             prog = programs.get(id(g)) if g is not None else None
             if prog is not None:
-                last = g.reduction if g.reduction is not None else g.nodes[-1]
-                if n is last and not emitted.get(id(g)):
-                    emitted[id(g)] = True
-                    name = f"spyre_fused_{len(self.kernel_specs)}"
-                    spec = spec_from_program(name, prog)
-                    self.kernel_specs.append(spec)
-                    runner = async_compile.sdsc(name, spec)
-                    self.fused_nodes += len(g.nodes) + (1 if g.reduction is not None else 0)
-                    self.steps.append(self._fused_step(prog, runner))
+                if not seen.get(id(g)):
+                    seen[id(g)] = True
+                    members = list(g.nodes) + ([g.reduction] if g.reduction is not None else [])
+                    units.append(_Unit(members, list(prog.inputs),
+                                       (lambda prog=prog, members=members: self._fused_step(prog, len(members))),
+                                       order[members[0]]))
                 continue
             if n.op == "get_attr":
-                self.steps.append(self._attr_step(n))
+                units.append(_Unit([n], [], (lambda n=n: self._attr_step(n)), order[n]))
             elif n.op == "call_function":
-                self.steps.append(self._call_step(n))
+                units.append(_Unit([n], list(n.all_input_nodes), (lambda n=n: self._call_step(n)), order[n]))
             else:
                 raise RuntimeError(f"unsupported FX node {n.op}")
+        return units
 
+    @staticmethod
+    def _schedule(units: List[_Unit], ready: Sequence[Node]) -> List[_Unit]:
+        """Stable topological order: at every point the unit that comes first in the graph among
+        those whose inputs exist.  A fused group needs the inputs of all its members at once, so
+        it may have to run later than its first member and earlier than an outside reader of
+        one of its stored values."""
+        have = set(ready)
+        pending = sorted(units, key=lambda u: u.first)
+        out: List[_Unit] = []
+        while pending:
+            for i, u in enumerate(pending):
+                if all(d in have for d in u.needs):
+                    out.append(pending.pop(i))
+                    have.update(u.produces)
+                    break
+            else:
+                raise fusion.CannotFuse("fused groups depend on each other")
+        return out
+
+    def _build(self) -> None:
+        try:
+            plan = self._schedule(self._units(), self.placeholders)
+        except fusion.CannotFuse:
+            # cannot happen while build_groups keeps groups acyclic; run unfused if it ever does
+            saved = fusion.is_pointwise
+            fusion.is_pointwise = lambda n: False
+            try:
+                plan = self._schedule(self._units(), self.placeholders)
+            finally:
+                fusion.is_pointwise = saved
+        for u in plan:
+            self.steps.append(u.make_step())
+        self._plan_frees(plan)
+
+    def _plan_frees(self, plan: List[_Unit]) -> None:
+        """After each step, clear the slots whose last reader that step was."""
+        keep = set()
+        torch.fx.node.map_arg(self.output_node.args[0], lambda a: keep.add(a) or a)
+        last_reader: Dict[Node, int] = {}
+        for i, u in enumerate(plan):
+            for d in u.needs:
+                last_reader[d] = i
+            for p in u.produces:
+                last_reader.setdefault(p, i)
+        frees: List[List[int]] = [[] for _ in plan]
+        for node, i in last_reader.items():
+            if node not in keep:
+                frees[i].append(self.slot[node])
+        self.frees = [tuple(f) for f in frees]
+
+    # -- steps ---------------------------------------------------------------------------
     def _attr_step(self, n: Node):
         value = getattr(self.gm, n.target)
+        i = self.slot[n]
 
         def step(env):
-            env[n] = value
+            env[i] = value
 
         return step
 
-    @staticmethod
-    def _call_step(n: Node):
+    def _call_step(self, n: Node):
+        target, i = n.target, self.slot[n]
+        args = [_arg_reader(a, self.slot) for a in n.args]
+        kwargs = {k: _arg_reader(v, self.slot) for k, v in n.kwargs.items()}
+        if not kwargs and all(not c for c, _ in args) and len(args) <= 3:
+            readers = [v for _, v in args]
+            if len(readers) == 1:
+                r0 = readers[0]
+
+                def step(env):
+                    env[i] = target(r0(env))
+            elif len(readers) == 2:
+                r0, r1 = readers
+
+                def step(env):
+                    env[i] = target(r0(env), r1(env))
+            else:
+                def step(env):
+                    env[i] = target(*[r(env) for r in readers])
+            return step
+
         def step(env):
-            args = torch.fx.node.map_arg(n.args, lambda a: env[a])
-            kwargs = torch.fx.node.map_arg(n.kwargs, lambda a: env[a])
-            env[n] = n.target(*args, **kwargs)
+            env[i] = target(*[(v if c else v(env)) for c, v in args],
+                            **{k: (v if c else v(env)) for k, (c, v) in kwargs.items()})
 
         return step
 
-    @staticmethod
-    def _fused_step(prog: fusion.Program, runner):
-        out_nodes = list(prog.outputs) + ([prog.reduce_node] if prog.reduce else [])
+    def _fused_step(self, prog: fusion.Program, n_members: int):
+        name = f"spyre_fused_{len(self.kernel_specs)}"
+        spec = spec_from_program(name, prog)
+        self.kernel_specs.append(spec)
+        runner = SpyreAsyncCompile().sdsc(name, spec)
+        self.fused_nodes += n_members
+        out_slots = [self.slot[n] for n in list(prog.outputs) + ([prog.reduce_node] if prog.reduce else [])]
+        in_slots = [self.slot[n] for n in prog.inputs]
 
         def step(env):
-            results = runner.run(*[env[i] for i in prog.inputs])
-            for node, value in zip(out_nodes, results):
-                env[node] = value
+            results = runner.run(*[env[i] for i in in_slots])
+            for i, value in zip(out_slots, results):
+                env[i] = value
 
         return step
 
     def __call__(self, args: Sequence[Any]):
-        env: Dict[Node, Any] = {}
+        env: list = [None] * len(self.slot)
         for p, a in zip(self.placeholders, args):
-            env[p] = a
+            env[self.slot[p]] = a
         if isinstance(args, list):
             args.clear()
-        for step in self.steps:
+        for step, free in zip(self.steps, self.frees):
             step(env)
-        return torch.fx.node.map_arg(self.output_node.args[0], lambda a: env[a])
+            for i in free:
+                env[i] = None
+        slot = self.slot
+        return torch.fx.node.map_arg(self.output_node.args[0], lambda a: env[slot[a]])
 
 
 def compile_graph(gm: GraphModule, example_inputs) -> Callable:

@@ -194,6 +194,13 @@ def _(x, w_gate, w_up):
     return x.new_empty(tuple(x.shape[:-1]) + (w_gate.shape[0],))
 
 
+def _fused_attention_fits(q, k, v, head_dim: int) -> bool:
+    """The fused kernel takes head_dim 128, fp16 and q / k / v of one shape; any other causal
+    attention keeps torch's own formula (which decomposes into ops the device does have)."""
+    return (head_dim == 128 and tuple(k.shape) == tuple(q.shape) and tuple(v.shape) == tuple(q.shape)
+            and q.dtype == k.dtype == v.dtype == torch.float16)
+
+
 @torch.library.custom_op("spyre::sdpa_causal", mutates_args=())
 def sdpa_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
     """F.scaled_dot_product_attention(q, k, v, is_causal=True, scale=scale) on [batch, heads, seq,
@@ -201,7 +208,7 @@ def sdpa_causal(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float)
     form: when q / k / v are the usual transposed views of projection outputs, that form is the
     projection output itself and nothing is copied."""
     b, h, s, d = q.shape
-    if _on_spyre(q):
+    if _on_spyre(q) and _fused_attention_fits(q, k, v, d):
         packed = [t.transpose(1, 2).reshape(b, s, h * d) for t in (q, k, v)]
         out = torch.ops.spyre.causal_attention(packed[0], packed[1], packed[2], h, scale)
         return out.view(b, s, h, d).transpose(1, 2)
@@ -223,6 +230,8 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: i
     if _on_spyre(q):
         from .. import ops, stick_ops as K
 
+        # raises for any head size other than 128, unequal shapes or another dtype
+        K.check_attention_args(q.shape, k.shape, v.shape, heads, (q.dtype, k.dtype, v.dtype))
         out = torch.empty_like(q)
         with torch.cuda.device(q.device.index or 0):
             K.causal_attention(ops._st(q), ops._st(k), ops._st(v), b, s, heads, scale, out=ops._st(out))

@@ -38,6 +38,11 @@ def _shape(n: Node):
     return tuple(v.shape) if isinstance(v, torch.Tensor) else None
 
 
+def _dtype(n: Node):
+    v = n.meta.get("val", n.meta.get("example_value"))
+    return v.dtype if isinstance(v, torch.Tensor) else None
+
+
 # ---- dynamo level -----------------------------------------------------------------------
 
 def rewrite_dynamo_graph(gm: GraphModule) -> int:
@@ -53,9 +58,11 @@ def rewrite_dynamo_graph(gm: GraphModule) -> int:
         if not bound.get("is_causal") or bound.get("attn_mask") is not None or bound.get("dropout_p", 0.0):
             continue
         q, k, v = bound["query"], bound["key"], bound["value"]
-        qs, ks = _shape(q), _shape(k)
-        if qs is None or len(qs) != 4 or ks is None or ks[1] != qs[1]:
-            continue   # grouped-query attention would need the heads repeated first
+        qs, ks, vs = _shape(q), _shape(k), _shape(v)
+        if qs is None or len(qs) != 4 or ks != qs or vs != qs:
+            continue   # grouped-query attention or a cached key length: not the fused kernel's case
+        if qs[-1] != 128 or any(_dtype(t) != torch.float16 for t in (q, k, v)):
+            continue   # the fused kernel is built for head_dim 128 in fp16; leave stock SDPA alone
         scale = bound.get("scale")
         if scale is None:
             scale = 1.0 / math.sqrt(qs[-1])

@@ -107,6 +107,17 @@ def _binary(op: str, a, b, rop: Optional[str] = None, alpha=1) -> torch.Tensor:
     if _is_number(a):
         if rop is None:
             raise NotImplementedError(f"scalar {op} tensor")
+        if alpha != 1:
+            # scalar <op> (alpha * tensor): scale the tensor, then apply the reversed opcode
+            _check_fp16(b)
+            out = _new(b.shape, b)
+            if out.numel() == 0:
+                return out
+            with _with_device(b):
+                c = Chain()
+                c.emit("LOAD", c.tensor(_st(b))).emit("MUL", c.imm(alpha)).emit(rop, c.imm(_number(a))).store(0)
+                K.run_chain(c, b.shape, outputs=[_st(out)])
+            return out
         a, b, op = b, a, rop
     _check_fp16(a)
     shape_b = () if _is_number(b) else tuple(b.shape)
@@ -192,7 +203,8 @@ _impl("maximum")(lambda a, b: _binary("MAX", a, b, "MAX"))
 _impl("minimum")(lambda a, b: _binary("MIN", a, b, "MIN"))
 _impl("pow.Tensor_Scalar")(lambda a, b: _binary("POW", a, b))
 _impl("pow.Tensor_Tensor")(lambda a, b: _binary("POW", a, b))
-_impl("rsub.Scalar")(lambda a, b, alpha=1: _binary("RSUB", a, _number(b)))
+# rsub(a, b, alpha) = b - alpha * a
+_impl("rsub.Scalar")(lambda a, b, alpha=1: _binary("SUB", _number(b), a, "RSUB", alpha))
 
 
 @_impl("where.self")
@@ -280,9 +292,11 @@ def _reduce(x: torch.Tensor, dims, op: str, keepdim: bool, mean: bool = False) -
     for d in dims:
         count *= x.shape[d] if x.dim() else 1
     out = x
-    for i, d in enumerate(dims):  # innermost first, so earlier results keep their positions
-        last = i == len(dims) - 1
-        out = _reduce_one(out, d, op, keepdim, (1.0 / count) if (mean and last) else 1.0)
+    for d in dims:  # innermost first, so earlier results keep their positions
+        # a mean divides stage by stage: every fp16 intermediate is then a mean itself and stays
+        # within the range of its inputs (partial sums would pass 65504 long before the end)
+        extent = x.shape[d] if x.dim() else 1
+        out = _reduce_one(out, d, op, keepdim, (1.0 / max(extent, 1)) if mean else 1.0)
     return out
 
 

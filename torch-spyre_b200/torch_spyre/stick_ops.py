@@ -427,6 +427,33 @@ def rotary(x: StickTensor, cos: StickTensor, sin: StickTensor, batch: int, seq: 
 # False routes every shape through the three-launch path (kept for comparison in tests / bench)
 fused_attention = True
 
+# the only head size the attention kernels are built for (their tensor maps span 2 sticks a head)
+ATTENTION_HEAD_DIM = 128
+
+
+def check_attention_args(q_shape, k_shape, v_shape, heads: int, dtypes, out_shape=None,
+                         batch: Optional[int] = None, seq: Optional[int] = None) -> None:
+    """Host-side validation done before any attention launch: the kernels index q / k / v / out
+    as [batch, seq, heads*128] fp16 images of one common shape, so anything else would make them
+    read and write outside the buffers."""
+    q_shape, k_shape, v_shape = tuple(q_shape), tuple(k_shape), tuple(v_shape)
+    if len(q_shape) != 3:
+        raise _abi.SpyreKernelError(f"causal_attention: q must be [batch, seq, heads*head_dim], got {q_shape}")
+    if k_shape != q_shape or v_shape != q_shape:
+        raise _abi.SpyreKernelError(
+            f"causal_attention: q, k and v must have one shape, got {q_shape}, {k_shape}, {v_shape}")
+    if out_shape is not None and tuple(out_shape) != q_shape:
+        raise _abi.SpyreKernelError(f"causal_attention: out shape {tuple(out_shape)} != q shape {q_shape}")
+    if heads < 1 or q_shape[2] != heads * ATTENTION_HEAD_DIM:
+        raise _abi.SpyreKernelError(
+            f"causal_attention: width {q_shape[2]} with {heads} heads is head_dim "
+            f"{q_shape[2] / max(heads, 1):g}; the kernel is built for head_dim {ATTENTION_HEAD_DIM} only")
+    if any(d != torch.float16 for d in dtypes):
+        raise _abi.SpyreKernelError(f"causal_attention: float16 only, got {tuple(dtypes)}")
+    if (batch is not None and batch != q_shape[0]) or (seq is not None and seq != q_shape[1]):
+        raise _abi.SpyreKernelError(
+            f"causal_attention: batch {batch} x seq {seq} does not match q shape {q_shape}")
+
 
 def causal_attention(q: StickTensor, k: StickTensor, v: StickTensor, batch: int, seq: int,
                      heads: int, scale: float, out: Optional[StickTensor] = None,
@@ -437,7 +464,9 @@ def causal_attention(q: StickTensor, k: StickTensor, v: StickTensor, batch: int,
     for all heads together: scores = q k^T (tcgen05 GEMM reading the heads out of the packed
     images), masked softmax in place, out = probs v written straight into the packed output
     image; `scores` is scratch of heads*batch*seq*seq fp16 elements for that path."""
-    hd = 128
+    hd = ATTENTION_HEAD_DIM
+    check_attention_args(q.shape, k.shape, v.shape, heads, (q.dtype, k.dtype, v.dtype),
+                         out.shape if out is not None else None, batch, seq)
     dev = q.image.device
     rows = batch * seq
     out = out or empty((batch, seq, heads * hd), torch.float16, dev)
