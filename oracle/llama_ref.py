@@ -62,9 +62,11 @@ def rotate_half(x):
 
 
 def layer_forward(x: torch.Tensor, w: dict, cfg: LayerConfig) -> torch.Tensor:
+    """Every op in x.dtype, rounding after each one (what eager does)."""
     b, s, d = x.shape
     hd, nh = cfg.head_dim, cfg.heads
-    cos, sin = rope_tables(s, hd, cfg.rope_theta, x.dtype)
+    # the tables are fp16 values whatever the compute dtype: they are inputs of the layer
+    cos, sin = (t.to(x.dtype) for t in rope_tables(s, hd, cfg.rope_theta, torch.float16))
     h = rms_norm(x, w["norm1"], cfg.eps)
     q = F.linear(h, w["q"]).view(b, s, nh, hd).transpose(1, 2)
     k = F.linear(h, w["k"]).view(b, s, nh, hd).transpose(1, 2)
@@ -79,6 +81,23 @@ def layer_forward(x: torch.Tensor, w: dict, cfg: LayerConfig) -> torch.Tensor:
     x = x + F.linear(attn, w["o"])
     h = rms_norm(x, w["norm2"], cfg.eps)
     return x + F.linear(F.silu(F.linear(h, w["gate"])) * F.linear(h, w["up"]), w["down"])
+
+
+def layer_forward_fp32(x: torch.Tensor, w: dict, cfg: LayerConfig) -> torch.Tensor:
+    """The same layer on the same fp16 inputs, evaluated in fp32 throughout: the yardstick two
+    fp16 evaluations are measured against when they round in different places."""
+    return layer_forward(x.float(), {k: v.float() for k, v in w.items()}, cfg)
+
+
+def attention_forward(q, k, v, heads: int, scale: float):
+    """Causal attention on packed [batch, seq, heads*head_dim] tensors, every op in q.dtype."""
+    b, s, width = q.shape
+    hd = width // heads
+    qh, kh, vh = (t.view(b, s, heads, hd).transpose(1, 2) for t in (q, k, v))
+    scores = torch.matmul(qh, kh.transpose(2, 3)) * scale
+    mask = torch.full((s, s), float("-inf"), dtype=torch.float32).triu(1)
+    probs = torch.softmax(scores.float() + mask, dim=-1).to(q.dtype)
+    return torch.matmul(probs, vh).transpose(1, 2).reshape(b, s, width)
 
 
 def layer_flops(batch: int, seq: int, cfg: LayerConfig, causal: bool = True) -> float:

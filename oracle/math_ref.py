@@ -55,3 +55,32 @@ def bmm_inputs(batch=32, m=2048, k=4096, n=4096, seed=0):
 
 def assert_close(actual: torch.Tensor, expected: torch.Tensor, rtol=RTOL, atol=ATOL):
     torch.testing.assert_close(actual.float().cpu(), expected.float().cpu(), rtol=rtol, atol=atol)
+
+
+def errors_against_fp32(got: torch.Tensor, cpu_fp16: torch.Tensor, truth_fp32: torch.Tensor,
+                        rtol=RTOL, atol=ATOL) -> dict:
+    """How far a device result and the CPU fp16 eager result each are from an fp32 evaluation of
+    the same inputs: maximum and RMS error of both, and the share of device elements that meet
+    rtol / atol against the CPU fp16 result.  Used where a chain of fp16 ops is deep enough that
+    two correct evaluations differ by more than atol element by element."""
+    t = truth_fp32.float().cpu()
+    eg = (got.float().cpu() - t).abs()
+    ec = (cpu_fp16.float().cpu() - t).abs()
+    d = (got.float().cpu() - cpu_fp16.float().cpu()).abs()
+    inside = d <= atol + rtol * cpu_fp16.float().cpu().abs()
+    return {"gpu_max": float(eg.max()), "cpu_max": float(ec.max()),
+            "gpu_rms": float(eg.pow(2).mean().sqrt()), "cpu_rms": float(ec.pow(2).mean().sqrt()),
+            "frac_within_tol": float(inside.float().mean())}
+
+
+def assert_no_worse_than_cpu_fp16(got, cpu_fp16, truth_fp32, factor=1.5, what="result") -> dict:
+    """The device result may be at most `factor` times as far from the fp32 evaluation as torch
+    CPU fp16 eager is, in maximum and in RMS error."""
+    e = errors_against_fp32(got, cpu_fp16, truth_fp32)
+    if not torch.isfinite(got.float()).all():
+        raise AssertionError(f"{what}: non-finite values in the device result")
+    if e["gpu_max"] > factor * e["cpu_max"] + 1e-6 or e["gpu_rms"] > factor * e["cpu_rms"] + 1e-7:
+        raise AssertionError(f"{what}: device error against fp32 (max {e['gpu_max']:.3e}, rms "
+                             f"{e['gpu_rms']:.3e}) exceeds {factor} x CPU fp16 eager's (max "
+                             f"{e['cpu_max']:.3e}, rms {e['cpu_rms']:.3e})")
+    return e
