@@ -39,6 +39,7 @@ constexpr int kAttnSmem = kSmemTiles * kTileBytes + 1024 /*align*/ + 1280 /*barr
 constexpr uint32_t kAttnTmemCols = 512;         // S0 | S1 | O | (unused)
 constexpr float kRescaleThreshold = 8.f;        // in units of the exponent (log2)
 constexpr long long kAttnWaitLimit = 4000000000ll;  // ~2 s of SM clocks
+constexpr long long kAttnDrainLimit = 200000ll;   // ~0.1 ms: far longer than a TMA copy is in flight
 
 __device__ int g_attn_error;  // sticky: set when a bounded wait gave up
 
@@ -156,12 +157,11 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
         const uint32_t issued = g < (uint32_t)kKvStages ? g : (uint32_t)kKvStages;
         for (uint32_t k = 0; k < issued; ++k) {
           const uint32_t t = g - 1 - k, s = t % kKvStages, ph = (t / kKvStages) & 1;
-          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_full[s]), ph, abort_flag, kAttnWaitLimit / 16);
-          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_full[s]), ph, abort_flag, kAttnWaitLimit / 16);
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[s]), ph, kAttnDrainLimit);
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full[s]), ph, kAttnDrainLimit);
         }
         if (item_n > 0)
-          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, abort_flag,
-                                 kAttnWaitLimit / 16);
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
       }
     }
     __syncwarp();
@@ -538,11 +538,11 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
       if (*abort_flag) {   // after an abort only: let copies in flight land before the CTA exits
         for (uint32_t k = 0; k < (kt < 2u ? kt : 2u); ++k) {
           const uint32_t t = kt - 1 - k;
-          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_full[t & 1]), (t >> 1) & 1, abort_flag, kAttnWaitLimit / 16);
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[t & 1]), (t >> 1) & 1, kAttnDrainLimit);
         }
-        if (kt > 0) ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_full), (kt - 1) & 1, abort_flag, kAttnWaitLimit / 16);
+        if (kt > 0) ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full), (kt - 1) & 1, kAttnDrainLimit);
         if (item_n > 0)
-          ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, abort_flag, kAttnWaitLimit / 16);
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
       }
     }
     __syncwarp();

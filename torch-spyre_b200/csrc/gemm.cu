@@ -41,6 +41,7 @@ constexpr int kStagingBytes = 4 * 32 * 128;   // epilogue: 32 rows x 128 bytes p
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
+constexpr long long kDrainLimit = 200000ll;     // ~0.1 ms: far longer than a TMA copy is in flight
 
 __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
 
@@ -427,6 +428,21 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
                                     (int)(tn * (BN / 64) + rank * (BN / 128) + j), (int)h);
           }
         }
+      }
+      // Let copies still in flight land before either CTA can exit.  On the normal path every
+      // issued stage has been consumed by then and these waits return at once.  The "full"
+      // barriers live in the leader and count both CTAs' bytes, so the leader waits on them
+      // (ignoring the abort flag, which is what brought it here on the unwinding path); the
+      // other CTA cannot observe them, so when it unwinds it simply lets a bounded time pass
+      // that is far longer than a copy takes.  Both CTAs then meet in cluster_sync_all below.
+      if (rank == 0) {
+        const uint32_t issued = it < (uint32_t)kPairStages ? it : (uint32_t)kPairStages;
+        for (uint32_t k = 0; k < issued; ++k) {
+          const uint32_t j = it - 1 - k, s = j % kPairStages, ph = (j / kPairStages) & 1;
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->full[s]), ph, kDrainLimit);
+        }
+      } else if (!ok) {
+        ptx::spin_cycles(kDrainLimit);
       }
     }
     __syncwarp();

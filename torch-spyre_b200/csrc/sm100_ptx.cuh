@@ -57,6 +57,24 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
   }
 }
 
+// Wait used while unwinding: ignores the abort flag (it is usually already set) and gives up
+// after `limit_cycles`.  Lets copies that are still in flight land before shared memory is
+// given back.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, long long limit_cycles) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (clock64() - t0 < limit_cycles)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+// Plain bounded delay (cycles), for the unwinding path of a CTA that cannot observe the barrier
+// its copies complete on.
+__device__ __forceinline__ void spin_cycles(long long cycles) {
+  const long long t0 = clock64();
+  while (clock64() - t0 < cycles) {
+  }
+}
+
 // ---- TMA ------------------------------------------------------------------------
 __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
                                             int c0, int c1, int c2, int c3) {
