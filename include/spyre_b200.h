@@ -87,6 +87,37 @@ int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int el
                            const int64_t* device_size, const int64_t* device_strides,
                            const int32_t* dim_map, int ndev, void* stream);
 
+/* Stick image -> stick image for a strided view on either side, in one pass:
+ * the device-side restickify behind transposed / permuted / sliced / narrowed
+ * / expanded tensors.  Stands in for the reference's data-op programs
+ * (2-D and 3-D transposes in 64x64 pieces and slices,
+ * torch_spyre/_inductor/codegen/data_ops.py:16-189, 193-487, 490-630) and for
+ * the CPU bounce of its view ops (codegen/templates/view.jinja2:40-46).
+ *
+ * Each side is the generic stick image of a row-major base tensor
+ * (`*_base`, `*_base_rank` dims) together with a view of that base: `size`
+ * (shared by both sides, `rank` dims), element strides and an element offset
+ * in the base's row-major numbering, exactly a torch tensor's sizes / strides
+ * / storage_offset.  dst[view index] = src[view index] for every index.
+ * Transposes between the stick dim and another dim go through 64x64 tiles in
+ * shared memory; everything else is moved in 16-byte units.
+ * Pad lanes of the destination are zeroed where the destination view reaches
+ * the end of its base's innermost dim; elements of the destination base that
+ * the view does not address are left as they are.
+ * Returns TS_ERR_UNSUPPORTED (and launches nothing) for a view that is not a
+ * walk along single base dims, for a walk along the stick dim that neither
+ * starts at a stick boundary with step 1 nor stays inside one stick, for a
+ * destination with a zero stride, and for negative strides: callers then take
+ * the two-pass route through ts_relayout_from_sticks / ts_relayout_to_sticks.
+ * elem_bytes is 1, 2 or 4 (tiled transposes: 2 only; other sizes are moved
+ * element by element).  The two images must not overlap.
+ */
+int ts_transpose_tiles(const void* src_sticks, const int64_t* src_base, int src_base_rank,
+                       const int64_t* src_strides, int64_t src_offset, void* dst_sticks,
+                       const int64_t* dst_base, int dst_base_rank, const int64_t* dst_strides,
+                       int64_t dst_offset, const int64_t* size, int rank, int elem_bytes,
+                       void* stream);
+
 /* SpyreTensorLayout::init (torch_spyre/csrc/spyre_tensor_impl.cpp:29-74) as a
  * plain function: fills device_size / device_strides / dim_map (rank + 1
  * entries each) for the generic stick layout of host_size; dim_order may be

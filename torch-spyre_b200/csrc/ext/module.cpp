@@ -116,6 +116,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   });
   // helpers for the Python op layer
   m.def("is_canonical", &spyre::is_canonical);
+  // test hook: False sends device-to-device copies of views through the two-pass route
+  m.def("set_restickify_enabled", &spyre::set_restickify_enabled);
   m.def("base_shape", [](const at::Tensor& t) { return spyre::storage_ctx(t)->base_shape; });
   m.def("storage_ptr", [](const at::Tensor& t) { return (uintptr_t)spyre::storage_ctx(t)->ptr; });
   m.def("storage_as_cuda_bytes", &spyre::storage_as_cuda_bytes);

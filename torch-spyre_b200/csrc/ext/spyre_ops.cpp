@@ -252,6 +252,27 @@ void device_to_host(const at::Tensor& src, const at::Tensor& dst_cpu) {
   dst_cpu.copy_(view_in(raw, src));
 }
 
+// One pass, image to image, when both tensors are views the restickify kernel can walk.
+bool restickify(const at::Tensor& src, const at::Tensor& dst) {
+  StorageCtx* sctx = storage_ctx(src);
+  StorageCtx* dctx = storage_ctx(dst);
+  if (sctx->device != dctx->device || sctx->elem_bytes != dctx->elem_bytes) return false;
+  if (sctx->ptr == dctx->ptr) return false;            // overlapping images: take the two-pass route
+  auto size = dst.sizes().vec();
+  at::Tensor s = src.sizes() == dst.sizes() ? src : src.expand(dst.sizes());
+  auto sstr = s.strides().vec(), dstr = dst.strides().vec();
+  if (size.empty()) { size = {1}; sstr = {1}; dstr = {1}; }
+  if ((int)size.size() > TS_MAX_DIMS) return false;
+  const int rc = ts_transpose_tiles(sctx->ptr, sctx->base_shape.data(), (int)sctx->base_shape.size(),
+                                    sstr.data(), s.storage_offset(), dctx->ptr, dctx->base_shape.data(),
+                                    (int)dctx->base_shape.size(), dstr.data(), dst.storage_offset(),
+                                    size.data(), (int)size.size(), dctx->elem_bytes,
+                                    current_stream(dctx->device));
+  if (rc == TS_ERR_UNSUPPORTED) return false;
+  check_status(rc, "restickify");
+  return true;
+}
+
 void device_to_device(const at::Tensor& src, const at::Tensor& dst) {
   StorageCtx* sctx = storage_ctx(src);
   StorageCtx* dctx = storage_ctx(dst);
@@ -261,6 +282,16 @@ void device_to_device(const at::Tensor& src, const at::Tensor& dst) {
     C10_CUDA_CHECK(cudaMemcpyAsync(dctx->ptr, sctx->ptr, stick_nbytes(dctx->base_shape, dctx->elem_bytes),
                                    cudaMemcpyDefault, current_stream(dctx->device)));
     return;
+  }
+  if (restickify_enabled()) {
+    if (restickify(src, dst)) return;
+    if (!is_canonical(dst) && !is_canonical(src)) {
+      // the source is a view the one-pass kernel cannot walk: give it its own image first (two
+      // passes over the source only), then write that image into the destination view
+      at::Tensor tmp = at::empty(dst.sizes(), src.options());
+      device_to_device(src, tmp);
+      if (restickify(tmp, dst)) return;
+    }
   }
   at::Tensor sraw = base_to_rowmajor(src);
   at::Tensor sview = view_in(sraw, src);
@@ -281,6 +312,15 @@ void device_to_device(const at::Tensor& src, const at::Tensor& dst) {
   view_in(draw, dst).copy_(sview);
   rowmajor_to_base(draw, dst);
 }
+
+}  // namespace
+
+// Test hook: route device-to-device copies of views through the two-pass path instead.
+static bool g_restickify = true;
+bool restickify_enabled() { return g_restickify; }
+void set_restickify_enabled(bool on) { g_restickify = on; }
+
+namespace {
 
 at::Tensor spyre_copy_from(const at::Tensor& self, const at::Tensor& dst, bool non_blocking) {
   TORCH_CHECK(self.scalar_type() == dst.scalar_type(),

@@ -45,6 +45,11 @@ bool is_canonical(const at::Tensor& t);
 // CUDA uint8 tensor aliasing the storage bytes (keeps the storage alive).
 at::Tensor storage_as_cuda_bytes(const at::Tensor& t);
 
+// Device-to-device copies of views go image to image in one pass (ts_transpose_tiles) when this
+// is on (the default); off sends them through a row-major temporary, which tests compare against.
+bool restickify_enabled();
+void set_restickify_enabled(bool on);
+
 void register_debug_flag();
 bool debug_enabled();
 

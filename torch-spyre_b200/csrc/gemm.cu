@@ -41,6 +41,7 @@ constexpr int kStagingBytes = 4 * 32 * 128;   // epilogue: 32 rows x 128 bytes p
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
+constexpr double kWideCost = 0.93;              // time of a 256 x 512 pair tile relative to two 256 x 256 ones
 constexpr long long kDrainLimit = 200000ll;     // ~0.1 ms: far longer than a TMA copy is in flight
 
 __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
@@ -53,6 +54,7 @@ struct GemmParams {
   uint32_t M, N, K, batch, heads;
   int64_t c_stick_stride, c_head_stride;   // elements
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
+  uint32_t band_tiles;   // tile columns per band of the tile order (see decode_tile)
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
 };
@@ -66,17 +68,16 @@ struct Barriers {
 // Tile order within one (batch, head): bands of kBandTiles tile columns, rows fastest across
 // a band, so that the tiles in flight at any time (one per CTA or CTA pair) form a roughly
 // square block and share both their A row panels and their B column panels in L2.
-constexpr uint32_t kBandTiles = 8;
 __device__ __forceinline__ void decode_tile(const GemmParams& P, uint32_t tile, uint32_t tiles_m,
                                             uint32_t& tm, uint32_t& tn, uint32_t& b, uint32_t& h) {
   const uint32_t per_bh = P.tiles_n * tiles_m;
   const uint32_t bh = tile / per_bh, t = tile - bh * per_bh;
   b = bh % P.batch;
   h = bh / P.batch;
-  const uint32_t band = t / (kBandTiles * tiles_m), r = t - band * (kBandTiles * tiles_m);
-  const uint32_t width = min(kBandTiles, P.tiles_n - band * kBandTiles);
+  const uint32_t band = t / (P.band_tiles * tiles_m), r = t - band * (P.band_tiles * tiles_m);
+  const uint32_t width = min(P.band_tiles, P.tiles_n - band * P.band_tiles);
   tm = r / width;
-  tn = band * kBandTiles + (r - tm * width);
+  tn = band * P.band_tiles + (r - tm * width);
 }
 
 // Drains one warp's 32 accumulator rows x BN columns: tensor memory -> registers -> fp16 ->
@@ -341,27 +342,53 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }
 
 // ---- the same GEMM on CTA pairs ------------------------------------------------------
-// A cluster of two CTAs computes one 256 x 256 tile: tcgen05.mma cta_group::2 multiplies the
-// 256 rows of A held by the two CTAs (128 each) by a 256-column B tile of which each CTA
-// loads only its half (128 columns), so an SM pulls 32 KiB of operands per 64-k step out of L2
-// instead of 48 KiB, and the ring is 6 stages deep in the same shared memory.  The leader CTA
-// (rank 0) owns the "full" barriers (both CTAs' TMA loads count on them) and issues the MMAs;
-// it signals "stage free" and "accumulator ready" to both CTAs; each CTA drains its own 128
-// accumulator rows.  No multicast anywhere.
-constexpr int kPairStages = 6;
-constexpr int kPairBBytes = (BN / 2) * BK * 2;                 // 16 KiB
-constexpr int kPairStageBytes = kABytes + kPairBBytes;        // 32 KiB per CTA
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kStagingBytes + 1024 + 256;
+// A cluster of two CTAs computes one 256-row tile: tcgen05.mma cta_group::2 multiplies the
+// 256 rows of A held by the two CTAs (128 each) by a 256-column B block of which each CTA
+// loads only its half (128 columns).  The leader CTA (rank 0) owns the "full" barriers (both
+// CTAs' TMA loads count on them) and issues the MMAs; it signals "stage free" and "accumulator
+// ready" to both CTAs; each CTA drains its own 128 accumulator rows.  No multicast anywhere.
+//
+// NH = 1: 256 x 256 tiles.  An SM pulls 32 KiB of operands per 64-k step (instead of the 48 KiB
+// of the single-CTA kernel), the ring is 6 stages deep and the two 256-column accumulators in
+// tensor memory alternate between consecutive tiles, so a tile's drain overlaps the next
+// tile's main loop.
+// NH = 2: 256 x 512 tiles, the two accumulators being the two 256-column halves of one tile.
+// An SM then pulls 48 KiB per 64-k step for twice the flops: a quarter less L2 -> SM operand
+// traffic per flop, which is what the tensor pipe waits for (and what the power cap bills).
+// The drain still overlaps: half 0 of a tile is drained while the MMAs of half 1 of its last k
+// step run, and the next tile's first MMAs into a half wait only for that half to be drained.
+// 4 stages of 48 KiB.
+constexpr int kPairStagesMax = 6;
+constexpr int kPairBBytes = (BN / 2) * BK * 2;                 // 16 KiB: one CTA's share of a 256-column block
+
+template <int NH>
+struct PairCfg {
+  static constexpr int kStages = NH == 1 ? 6 : 4;
+  static constexpr int kStageBytes = kABytes + NH * kPairBBytes;   // 32 / 48 KiB per CTA
+  static constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 + 256;
+};
 
 struct PairBarriers {
-  uint64_t full[kPairStages], empty[kPairStages], acc_full[2], acc_empty[2];
+  uint64_t full[kPairStagesMax], empty[kPairStagesMax], acc_full[2], acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
+// Accumulator slot and how many times it has been used before, for block `half` of the CTA
+// pair's `local_tile`-th tile.
+template <int NH>
+__device__ __forceinline__ void acc_slot(uint32_t local_tile, uint32_t half, uint32_t& slot, uint32_t& use) {
+  if (NH == 1) { slot = local_tile & 1; use = local_tile >> 1; }
+  else { slot = half; use = local_tile; }
+}
+
+template <int NH>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                      const __grid_constant__ GemmParams P) {
+  using Cfg = PairCfg<NH>;
+  constexpr int kPairStages = Cfg::kStages, kPairStageBytes = Cfg::kStageBytes;
+  constexpr int BNT = BN * NH;     // tile width
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t tiles = (raw + 1023u) & ~1023u;
@@ -418,14 +445,19 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t sa = tiles + s * kPairStageBytes, sb = sa + kABytes;
           ptx::tma_load_5d_pair(sa, &map_a, full_leader, 0, (int)(tm * 2 * BM + rank * BM), (int)b,
                                 (int)kb, (int)h);
-          if (P.b_kmajor) {
-            ptx::tma_load_5d_pair(sb, &map_b, full_leader, 0, (int)(tn * BN + rank * (BN / 2)), bb,
-                                  (int)kb, (int)h);
-          } else {
 #pragma unroll
-            for (int j = 0; j < BN / 128; ++j)
-              ptx::tma_load_5d_pair(sb + j * (BK * 128), &map_b, full_leader, 0, (int)(kb * BK), bb,
-                                    (int)(tn * (BN / 64) + rank * (BN / 128) + j), (int)h);
+          for (int half = 0; half < NH; ++half) {
+            const uint32_t sbh = sb + half * kPairBBytes;
+            if (P.b_kmajor) {
+              ptx::tma_load_5d_pair(sbh, &map_b, full_leader, 0,
+                                    (int)(tn * BNT + half * BN + rank * (BN / 2)), bb, (int)kb, (int)h);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 128; ++j)
+                ptx::tma_load_5d_pair(sbh + j * (BK * 128), &map_b, full_leader, 0, (int)(kb * BK), bb,
+                                      (int)(tn * (BNT / 64) + half * (BN / 64) + rank * (BN / 128) + j),
+                                      (int)h);
+            }
           }
         }
       }
@@ -462,34 +494,40 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t s = 0, ph = 0, local_tile = 0;
       bool ok = true;
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
-        const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_empty[acc]), acc_ph ^ 1, abort_flag,
-                                    kWaitLimit)) break;
-        ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        for (uint32_t kb = 0; kb < P.k_blocks; ++kb) {
+        for (uint32_t kb = 0; ok && kb < P.k_blocks; ++kb) {
           if (!ptx::mbar_wait_bounded(full0 + s * 8, ph, abort_flag, kWaitLimit)) {
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
           const uint32_t so = s * (kPairStageBytes >> 4);
-          uint32_t a_lo = (uint32_t)da0 + so, b_lo = (uint32_t)db0 + so;
 #pragma unroll
-          for (int k16 = 0; k16 < BK / 16; ++k16) {
-            ptx::umma_f16_pair(d_tmem, ((uint64_t)a_hi << 32) | a_lo, ((uint64_t)b_hi << 32) | b_lo,
-                               idesc, k16 ? 1u : kb);
-            a_lo += 32u >> 4;
-            b_lo += b_step;
+          for (int half = 0; half < NH; ++half) {
+            uint32_t slot, use;
+            acc_slot<NH>(local_tile, half, slot, use);
+            if (kb == 0) {   // the block's accumulator must have been drained by both CTAs
+              if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_empty[slot]), (use & 1) ^ 1, abort_flag,
+                                          kWaitLimit)) { ok = false; break; }
+              ptx::tc_fence_after_sync();
+            }
+            const uint32_t d_tmem = tmem_base + slot * BN;
+            uint32_t a_lo = (uint32_t)da0 + so, b_lo = (uint32_t)db0 + so + half * (kPairBBytes >> 4);
+#pragma unroll
+            for (int k16 = 0; k16 < BK / 16; ++k16) {
+              ptx::umma_f16_pair(d_tmem, ((uint64_t)a_hi << 32) | a_lo, ((uint64_t)b_hi << 32) | b_lo,
+                                 idesc, k16 ? 1u : kb);
+              a_lo += 32u >> 4;
+              b_lo += b_step;
+            }
+            if (kb + 1 == P.k_blocks) {   // this block is complete once the MMAs issued so far are
+              const uint32_t f = ptx::smem_u32(&bars->acc_full[slot]);
+              ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
+              ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
+            }
           }
           ptx::umma_commit_pair(empty_c0 + s * 8);
           ptx::umma_commit_pair(empty_c1 + s * 8);
           if (++s == kPairStages) { s = 0; ph ^= 1; }
-        }
-        if (ok) {
-          const uint32_t f = ptx::smem_u32(&bars->acc_full[acc]);
-          ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
-          ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
         }
       }
     }
@@ -498,23 +536,28 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const uint32_t q = warp & 3;
     uint32_t local_tile = 0;
-    for (uint32_t tile = pair; tile < num_tiles; tile += num_pairs, ++local_tile) {
+    bool ok = true;
+    for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
       uint32_t tm, tn, b, h;
       decode_tile(P, tile, tiles_m, tm, tn, b, h);
-      const uint32_t acc = local_tile & 1, acc_ph = (local_tile >> 1) & 1;
-      if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
-                                  kWaitLimit)) break;
-      ptx::tc_fence_after_sync();
-      if (P.swiglu)
-        drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
-                          tm * 2 * BM + rank * BM + q * 32, tn * BN, b, h, lane);
-      else
-        drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
-                   tm * 2 * BM + rank * BM + q * 32, tn * BN, b, h, lane);
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0)
-        ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[acc]), 0));
+#pragma unroll 1
+      for (int half = 0; half < NH; ++half) {
+        uint32_t slot, use;
+        acc_slot<NH>(local_tile, half, slot, use);
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[slot]), use & 1, abort_flag,
+                                    kWaitLimit)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        if (P.swiglu)
+          drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + slot * BN, staging + q * (32 * 128),
+                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN, b, h, lane);
+        else
+          drain_rows(P, tmem_base + ((q * 32u) << 16) + slot * BN, staging + q * (32 * 128),
+                     tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN, b, h, lane);
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0)
+          ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[slot]), 0));
+      }
     }
   }
 
@@ -579,10 +622,33 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   P.b_kmajor = b_kmajor ? 1 : 0;
   P.b_batched = b_batched ? 1 : 0;
 
-  // CTA pairs whenever a 256-row tile has work for both halves (TS_GEMM_PAIR=0 / 1 in the
-  // environment forces one kernel or the other, for comparisons)
-  static const int pair_env = getenv("TS_GEMM_PAIR") ? atoi(getenv("TS_GEMM_PAIR")) : -1;
-  const bool use_pair = pair_env >= 0 ? pair_env != 0 : M > BM;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  });
+  // CTA pairs whenever a 256-row tile has work for both halves; 512-wide pair tiles when that
+  // does not cost more in the last, partly filled wave than it saves in operand traffic.
+  const int sms = g_sm_count > 0 ? g_sm_count : 148;
+  bool use_pair = M > BM;
+  int nh = 1;
+  if (use_pair) {
+    const int64_t pairs = sms / 2, tm2 = ceil_div(M, 2 * BM);
+    const int64_t t1 = tm2 * ceil_div(N, BN) * batch * heads, t2 = tm2 * ceil_div(N, 2 * BN) * batch * heads;
+    // time in units of one 256 x 256 tile: whole waves, a 512-wide tile costing kWideCost of two
+    const double cost1 = (double)ceil_div(t1, pairs), cost2 = 2.0 * kWideCost * (double)ceil_div(t2, pairs);
+    if (N > BN && cost2 < cost1) nh = 2;
+  }
+  uint32_t band = 8;
+#ifdef TSB_TUNING
+  // experiment hooks of the tuning build only (never compiled into the product library)
+  if (const char* e = getenv("TS_GEMM_PAIR")) use_pair = atoi(e) != 0 && M > BM;
+  if (const char* e = getenv("TS_GEMM_NH")) nh = atoi(e) == 2 && use_pair ? 2 : 1;
+  if (const char* e = getenv("TS_GEMM_BAND")) band = (uint32_t)std::max(1, atoi(e));
+#endif
+  P.band_tiles = band;
+  if (use_pair) P.tiles_n = (uint32_t)ceil_div(N, BN * nh);
   CUtensorMap map_a, map_b;
   if (!make_stick_map(&map_a, a, (uint64_t)M, (uint64_t)batch, (uint64_t)ks, (uint64_t)heads, a_stick_stride,
                 a_head_stride, BM))
@@ -596,21 +662,23 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   if (!okb) return TS_ERR_CUDA;
   if (b_heads == 1 && heads > 1) return TS_ERR_UNSUPPORTED;  // kernel indexes B by head
 
-  static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
-  std::call_once(once, [] {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
-  });
   if (use_pair) {
-    attr_err = cudaFuncSetAttribute(gemm_f16_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    kPairSmemBytes);
-    if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }
     const int64_t tiles2 = (int64_t)ceil_div(M, 2 * BM) * P.tiles_n * batch * heads;
-    const int64_t pairs = std::min<int64_t>(tiles2, (g_sm_count > 0 ? g_sm_count : 148) / 2);
-    gemm_f16_pair_kernel<<<(uint32_t)(2 * pairs), kThreads, kPairSmemBytes, (cudaStream_t)stream>>>(
-        map_a, map_b, P);
+    const int64_t pairs = std::min<int64_t>(tiles2, sms / 2);
+    if (nh == 2) {
+      attr_err = cudaFuncSetAttribute(gemm_f16_pair_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PairCfg<2>::kSmemBytes);
+      if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }
+      gemm_f16_pair_kernel<2><<<(uint32_t)(2 * pairs), kThreads, PairCfg<2>::kSmemBytes, (cudaStream_t)stream>>>(
+          map_a, map_b, P);
+    } else {
+      attr_err = cudaFuncSetAttribute(gemm_f16_pair_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      PairCfg<1>::kSmemBytes);
+      if (attr_err != cudaSuccess) { note_cuda_error(attr_err); return TS_ERR_CUDA; }
+      gemm_f16_pair_kernel<1><<<(uint32_t)(2 * pairs), kThreads, PairCfg<1>::kSmemBytes, (cudaStream_t)stream>>>(
+          map_a, map_b, P);
+    }
     TSB_CHECK_LAUNCH();
     return TS_OK;
   }

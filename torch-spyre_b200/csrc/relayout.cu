@@ -38,13 +38,21 @@ struct CopyPlan {
   int nchecks;
   int64_t vmul[kMaxChecks][kMaxDims];
   int64_t vlimit[kMaxChecks];
+  // kPerCheck mode: an index that fails check c is written as zero when vfill[c] (it is a pad
+  // lane of the destination image) and skipped otherwise (it does not exist in the destination)
+  int vfill[kMaxChecks];
   // copy_tiles: 256 threads cover T0 x T1 x T2 indices of dims 0,1,2; each thread then
   // walks kUnitsPerThread steps of `kstep` indices along dim `kd`.
   int log_t0, log_t1, kd;
   uint32_t kstep;
-  // transpose_tiles: which of dims 0 / 1 the CTA walks its kSubTiles tiles along
+  // transpose_tiles: the plan dim the CTA walks its kSubTiles tiles along: dim 0 or 1 (64 indices
+  // per step) or an outer dim (one index per step)
   int sub_dim;
 };
+
+// What happens to an index that fails a padding check.
+enum FillMode { kSkip = 0 /* image -> strided memory */, kFill = 1 /* strided memory -> image */,
+                kPerCheck = 2 /* image -> image: CopyPlan::vfill decides */ };
 
 template <int UNIT>
 struct UnitType;
@@ -65,6 +73,7 @@ template <> __device__ __forceinline__ uint4 load_unit<uint4>(const char* p) { r
 
 struct TileBase {
   uint32_t o0, o1, o2;       // tile origin along dims 0, 1, 2
+  uint32_t osub;             // tile origin along CopyPlan::sub_dim (transpose_tiles)
   int64_t soff, doff;        // byte offsets of the tile origin
   int64_t v[kMaxChecks];     // check sums at the tile origin
 };
@@ -72,7 +81,7 @@ struct TileBase {
 template <bool CHECKS>
 __device__ __forceinline__ TileBase decode_tile(const CopyPlan& p, uint32_t tile_id) {
   TileBase b;
-  b.o0 = b.o1 = b.o2 = 0;
+  b.o0 = b.o1 = b.o2 = b.osub = 0;
   b.soff = b.doff = 0;
   b.v[0] = b.v[1] = 0;
   uint32_t rem = tile_id;
@@ -86,6 +95,7 @@ __device__ __forceinline__ TileBase decode_tile(const CopyPlan& p, uint32_t tile
     if (d == 0) b.o0 = o;
     if (d == 1) b.o1 = o;
     if (d == 2) b.o2 = o;
+    if (d == p.sub_dim) b.osub = o;
     b.soff += (int64_t)o * p.sbytes[d];
     b.doff += (int64_t)o * p.dbytes[d];
     if (CHECKS) {
@@ -97,7 +107,7 @@ __device__ __forceinline__ TileBase decode_tile(const CopyPlan& p, uint32_t tile
 }
 
 // ---------------------------------------------------------------------------
-template <int UNIT, bool TO_DEVICE, bool CHECKS>
+template <int UNIT, int MODE, bool CHECKS>
 __global__ void __launch_bounds__(kThreads)
 copy_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src, char* __restrict__ dst) {
   using T = typename UnitType<UNIT>::T;
@@ -135,15 +145,19 @@ copy_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src, cha
 #pragma unroll
   for (int k = 0; k < kUnitsPerThread; ++k) {
     const bool inb = fixed_ok && (xk + k * p.kstep < nk);
-    bool valid = true;
+    bool valid = true, exists = true;
     if (CHECKS) {
 #pragma unroll
       for (int c = 0; c < kMaxChecks; ++c)
-        if (c < p.nchecks) valid = valid && (vv[c] + k * dv[c] < p.vlimit[c]);
+        if (c < p.nchecks) {
+          const bool ok = vv[c] + k * dv[c] < p.vlimit[c];
+          valid = valid && ok;
+          if (MODE == kSkip || (MODE == kPerCheck && !p.vfill[c])) exists = exists && ok;
+        }
     }
     val[k] = zero_of<T>();
     if (inb && valid) val[k] = load_unit<T>(sp + k * ds);
-    live[k] = inb && (TO_DEVICE || valid);
+    live[k] = inb && exists;
   }
 #pragma unroll
   for (int k = 0; k < kUnitsPerThread; ++k)
@@ -160,11 +174,12 @@ constexpr int kPitchWords = 33;
 
 // Number of leading elements (0..8), along dim `dim`, that satisfy every check, given
 // the check sums at the first element.
+template <bool ONLY_SKIPPING = false>
 __device__ __forceinline__ int valid_run(const CopyPlan& p, const int64_t* vsum, int dim) {
   int n = 8;
 #pragma unroll
   for (int c = 0; c < kMaxChecks; ++c) {
-    if (c < p.nchecks) {
+    if (c < p.nchecks && !(ONLY_SKIPPING && p.vfill[c])) {
       const int64_t room = p.vlimit[c] - vsum[c];
       const int64_t mul = p.vmul[c][dim];
       int64_t k;
@@ -177,7 +192,7 @@ __device__ __forceinline__ int valid_run(const CopyPlan& p, const int64_t* vsum,
   return n;
 }
 
-template <bool TO_DEVICE, bool VEC_IN, bool VEC_OUT, bool CHECKS>
+template <int MODE, bool VEC_IN, bool VEC_OUT, bool CHECKS>
 __global__ void __launch_bounds__(kThreads, 4)
 transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src,
                 char* __restrict__ dst) {
@@ -194,10 +209,13 @@ transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src
   const int64_t srow32 = 32 * p.sbytes[1];
   char* dp0 = dst + b.doff + (int64_t)(2 * pcol) * p.dbytes[0] + grp * 16;
   // byte and index steps from one sub-tile to the next
-  const int64_t sub_s = (int64_t)kTT * p.sbytes[sd], sub_d = (int64_t)kTT * p.dbytes[sd];
+  const int sub_idx = sd < 2 ? kTT : 1;
+  const int64_t sub_s = (int64_t)sub_idx * p.sbytes[sd], sub_d = (int64_t)sub_idx * p.dbytes[sd];
   const int step_a = sd == 0 ? kTT : 0, step_b = sd == 1 ? kTT : 0;
   // extent left in this CTA's first sub-tile (may exceed one tile)
   const int left_a = (int)(p.size[0] - b.o0), left_b = (int)(p.size[1] - b.o1);
+  // sub-tiles that exist when they are walked along an outer dim
+  const int left_sub = sd < 2 ? kSubTiles : (int)(p.size[sd] - b.osub);
 
   // Phase 1: every load of the CTA's sub-tiles is issued before the first use, so the
   // sub-tiles' rows (adjacent in memory when they lie along dim 0) reach DRAM together.
@@ -210,13 +228,14 @@ transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src
       const int row = row1 + k * 32;
       int na = rem_a - vec1 * 8;
       na = na < 0 ? 0 : (na > 8 ? 8 : na);
-      if (row >= rem_b) na = 0;
-      if (CHECKS && TO_DEVICE && na > 0) {
+      if (row >= rem_b || sub >= left_sub) na = 0;
+      if (CHECKS && MODE != kSkip && na > 0) {
         int64_t vs[kMaxChecks];
 #pragma unroll
         for (int c = 0; c < kMaxChecks; ++c)
           vs[c] = b.v[c] + (int64_t)(sub * step_b + row) * p.vmul[c][1] +
-                  (int64_t)(sub * step_a + vec1 * 8) * p.vmul[c][0];
+                  (int64_t)(sub * step_a + vec1 * 8) * p.vmul[c][0] +
+                  (sd < 2 ? 0 : (int64_t)sub * p.vmul[c][sd]);
         na = min(na, valid_run(p, vs, 0));
       }
       const char* sp = sp0 + k * srow32 + sub * sub_s;
@@ -255,18 +274,20 @@ transpose_tiles(const __grid_constant__ CopyPlan p, const char* __restrict__ src
     for (int j = 0; j < 8; ++j) t[j] = tile[sub][(8 * grp + j) * kPitchWords + pcol];
     int nb = rem_b - grp * 8;
     nb = nb < 0 ? 0 : (nb > 8 ? 8 : nb);
+    if (sub >= left_sub) nb = 0;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
       const int a = 2 * pcol + half;
       if (a >= rem_a) continue;
       int n = nb;
-      if (CHECKS && !TO_DEVICE && n > 0) {
+      if (CHECKS && MODE != kFill && n > 0) {
         int64_t vs[kMaxChecks];
 #pragma unroll
         for (int c = 0; c < kMaxChecks; ++c)
           vs[c] = b.v[c] + (int64_t)(sub * step_a + a) * p.vmul[c][0] +
-                  (int64_t)(sub * step_b + grp * 8) * p.vmul[c][1];
-        n = min(n, valid_run(p, vs, 1));
+                  (int64_t)(sub * step_b + grp * 8) * p.vmul[c][1] +
+                  (sd < 2 ? 0 : (int64_t)sub * p.vmul[c][sd]);
+        n = min(n, valid_run<MODE == kPerCheck>(p, vs, 1));
       }
       const uint32_t sel = half ? 0x7632u : 0x5410u;
       uint4 q;
@@ -318,42 +339,48 @@ struct Request {
   int ndev;
 };
 
-template <bool TO_DEVICE, bool CHECKS>
+template <int MODE, bool CHECKS>
 int launch_copy2(const CopyPlan& plan, int unit, uint32_t blocks, const char* src, char* dst,
                  cudaStream_t st) {
   switch (unit) {
-    case 16: copy_tiles<16, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    case 8: copy_tiles<8, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    case 4: copy_tiles<4, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    case 2: copy_tiles<2, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
-    default: copy_tiles<1, TO_DEVICE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 16: copy_tiles<16, MODE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 8: copy_tiles<8, MODE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 4: copy_tiles<4, MODE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    case 2: copy_tiles<2, MODE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
+    default: copy_tiles<1, MODE, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst); break;
   }
   TSB_CHECK_LAUNCH();
   return TS_OK;
 }
-template <bool TO_DEVICE>
-int launch_copy(const CopyPlan& plan, int unit, bool checks, uint32_t blocks, const char* src,
+int launch_copy(const CopyPlan& plan, int mode, int unit, bool checks, uint32_t blocks, const char* src,
                 char* dst, cudaStream_t st) {
-  return checks ? launch_copy2<TO_DEVICE, true>(plan, unit, blocks, src, dst, st)
-                : launch_copy2<TO_DEVICE, false>(plan, unit, blocks, src, dst, st);
+  if (!checks)   // without checks the mode makes no difference
+    return launch_copy2<kFill, false>(plan, unit, blocks, src, dst, st);
+  if (mode == kFill) return launch_copy2<kFill, true>(plan, unit, blocks, src, dst, st);
+  if (mode == kSkip) return launch_copy2<kSkip, true>(plan, unit, blocks, src, dst, st);
+  return launch_copy2<kPerCheck, true>(plan, unit, blocks, src, dst, st);
 }
 
-template <bool TO_DEVICE, bool CHECKS>
+template <int MODE, bool CHECKS>
 int launch_transpose2(const CopyPlan& plan, bool vin, bool vout, uint32_t blocks, const char* src,
                       char* dst, cudaStream_t st) {
-  if (vin && vout) transpose_tiles<TO_DEVICE, true, true, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
-  else if (vin) transpose_tiles<TO_DEVICE, true, false, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
-  else if (vout) transpose_tiles<TO_DEVICE, false, true, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
-  else transpose_tiles<TO_DEVICE, false, false, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  if (vin && vout) transpose_tiles<MODE, true, true, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  else if (vin) transpose_tiles<MODE, true, false, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  else if (vout) transpose_tiles<MODE, false, true, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
+  else transpose_tiles<MODE, false, false, CHECKS><<<blocks, kThreads, 0, st>>>(plan, src, dst);
   TSB_CHECK_LAUNCH();
   return TS_OK;
 }
-template <bool TO_DEVICE>
-int launch_transpose(const CopyPlan& plan, bool vin, bool vout, bool checks, uint32_t blocks,
+int launch_transpose(const CopyPlan& plan, int mode, bool vin, bool vout, bool checks, uint32_t blocks,
                      const char* src, char* dst, cudaStream_t st) {
-  return checks ? launch_transpose2<TO_DEVICE, true>(plan, vin, vout, blocks, src, dst, st)
-                : launch_transpose2<TO_DEVICE, false>(plan, vin, vout, blocks, src, dst, st);
+  if (!checks) return launch_transpose2<kFill, false>(plan, vin, vout, blocks, src, dst, st);
+  if (mode == kFill) return launch_transpose2<kFill, true>(plan, vin, vout, blocks, src, dst, st);
+  if (mode == kSkip) return launch_transpose2<kSkip, true>(plan, vin, vout, blocks, src, dst, st);
+  return launch_transpose2<kPerCheck, true>(plan, vin, vout, blocks, src, dst, st);
 }
+
+int plan_and_launch(IterDim* it, int nd, int nchecks, const int64_t* vlimit, const int* vfill, int mode,
+                    int eb, const char* src, char* dst, cudaStream_t st);
 
 int run(const Request& rq, cudaStream_t st) {
   if (!rq.host_size || !rq.host_strides || !rq.dev_size || !rq.dev_strides || !rq.dim_map)
@@ -407,9 +434,18 @@ int run(const Request& rq, cudaStream_t st) {
     it[d].d = rq.to_device ? rq.dev_strides[d] : host_step;
     for (int c = 0; c < kMaxChecks; ++c) it[d].vm[c] = (check_of_host[h] == c) ? mult : 0;
   }
+  const int fill[kMaxChecks] = {rq.to_device ? 1 : 0, rq.to_device ? 1 : 0};
+  return plan_and_launch(it, rq.ndev, nchecks, vlimit, fill, rq.to_device ? kFill : kSkip, eb, rq.src,
+                         rq.dst, st);
+}
+
+// Turns an iteration space into a CopyPlan and launches the kernel that suits it.  `it` has room
+// for kMaxDims entries and is modified.
+int plan_and_launch(IterDim* it, int nd_in, int nchecks, const int64_t* vlimit, const int* vfill, int mode,
+                    int eb, const char* src, char* dst, cudaStream_t st) {
   // Drop size-1 dims, then merge neighbours that are contiguous on both sides.
   int nd = 0;
-  for (int d = 0; d < rq.ndev; ++d)
+  for (int d = 0; d < nd_in; ++d)
     if (it[d].size != 1) it[nd++] = it[d];
   if (nd == 0) { it[0] = IterDim{1, 1, 1, {0, 0}}; nd = 1; }
   for (int d = nd - 2; d >= 0; --d) {
@@ -427,7 +463,10 @@ int run(const Request& rq, cudaStream_t st) {
 
   CopyPlan plan{};
   plan.nchecks = nchecks;
-  for (int c = 0; c < kMaxChecks; ++c) plan.vlimit[c] = vlimit[c];
+  for (int c = 0; c < kMaxChecks; ++c) {
+    plan.vlimit[c] = vlimit[c];
+    plan.vfill[c] = vfill[c];
+  }
   const bool checks = nchecks > 0;
 
   int ua = -1, ub = -1;  // unit-stride dims of source / destination
@@ -435,7 +474,7 @@ int run(const Request& rq, cudaStream_t st) {
     if (it[d].s == 1 && ua < 0) ua = d;
     if (it[d].d == 1 && ub < 0) ub = d;
   }
-  const uintptr_t sbase = (uintptr_t)rq.src, dbase = (uintptr_t)rq.dst;
+  const uintptr_t sbase = (uintptr_t)src, dbase = (uintptr_t)dst;
 
   // Fills plan dims from `order` (plan position -> index into it[]); unit = bytes per
   // index step of plan dim 0 on the copy path (elements there are grouped into units).
@@ -474,14 +513,23 @@ int run(const Request& rq, cudaStream_t st) {
       if (k != 0 && plan.sbytes[k] % 16) vin = false;
       if (k != 1 && plan.dbytes[k] % 16) vout = false;
     }
-    plan.sub_dim = plan.size[0] >= plan.size[1] ? 0 : 1;   // walk along the longer tiled dim
+    // The CTA's kSubTiles tiles lie along the longer tiled dim, or, when neither has room for
+    // them (a transpose between two stick images: both are one stick wide), along the outer dim
+    // whose steps are closest together in the source, so that the tiles' rows are neighbours in
+    // memory and reach DRAM together.
+    plan.sub_dim = plan.size[0] >= plan.size[1] ? 0 : 1;
+    if (plan.size[plan.sub_dim] < (uint32_t)(2 * kTT)) {
+      int best = -1;
+      for (int k = 2; k < n; ++k)
+        if (plan.size[k] > 1 && plan.sbytes[k] > 0 && (best < 0 || plan.sbytes[k] < plan.sbytes[best])) best = k;
+      if (best >= 0) plan.sub_dim = best;
+    }
     plan.tile[0] = kTT * (plan.sub_dim == 0 ? kSubTiles : 1);
     plan.tile[1] = kTT * (plan.sub_dim == 1 ? kSubTiles : 1);
+    if (plan.sub_dim >= 2) plan.tile[plan.sub_dim] = kSubTiles;
     uint64_t ntiles;
     if (!count_tiles(ntiles)) return TS_ERR_TOO_LARGE;
-    return rq.to_device
-               ? launch_transpose<true>(plan, vin, vout, checks, (uint32_t)ntiles, rq.src, rq.dst, st)
-               : launch_transpose<false>(plan, vin, vout, checks, (uint32_t)ntiles, rq.src, rq.dst, st);
+    return launch_transpose(plan, mode, vin, vout, checks, (uint32_t)ntiles, src, dst, st);
   }
 
   // ---- copy path.  Plan dim 0 must have unit stride on both sides; an extent-1 dummy
@@ -554,8 +602,157 @@ int run(const Request& rq, cudaStream_t st) {
   plan.tile[kd] *= kUnitsPerThread;
   uint64_t ntiles;
   if (!count_tiles(ntiles)) return TS_ERR_TOO_LARGE;
-  return rq.to_device ? launch_copy<true>(plan, unit, checks, (uint32_t)ntiles, rq.src, rq.dst, st)
-                      : launch_copy<false>(plan, unit, checks, (uint32_t)ntiles, rq.src, rq.dst, st);
+  return launch_copy(plan, mode, unit, checks, (uint32_t)ntiles, src, dst, st);
+}
+
+// ---------------------------------------------------------------------------
+// Stick image -> stick image for a strided view on either side.
+//
+// A side is the generic stick image of a row-major base tensor plus a view of that base (sizes
+// shared by both sides, element strides and an element offset in the base's row-major numbering):
+// what a transposed, permuted, sliced, narrowed or expanded `spyre` tensor is.  The view is
+// expressible when every view dim walks along a single base dim, and the dim walking the base's
+// innermost (stick) dim does so with step 1 from a stick boundary (or stays inside one stick).
+struct ViewSide {
+  const int64_t* base;     // row-major base shape
+  int nb;
+  const int64_t* strides;  // view strides, elements of the base
+  int64_t offset;
+};
+
+struct SideDim {            // how one view dim moves through a side's stick image
+  bool split;              // walks the stick dim across sticks: index = 64 * hi + lo
+  int64_t step;            // elements of the image per index (per lo index when split)
+  int64_t hi_step;         // elements of the image per stick (split only)
+};
+
+// Fills dims[] for every view dim and returns the constant element offset into the image, or a
+// negative status.
+int64_t decompose_side(const ViewSide& v, const int64_t* size, int rank, int lanes, bool is_dst,
+                       SideDim* dims, bool* walks_stick_to_end) {
+  if (v.nb < 1 || v.nb + 1 > kMaxDims) return TS_ERR_INVALID;
+  int64_t rm[kMaxDims], img[kMaxDims];   // row-major strides of the base; image strides of its dims
+  int64_t numel = 1;
+  for (int b = v.nb - 1; b >= 0; --b) {
+    if (v.base[b] <= 0) return TS_ERR_INVALID;
+    rm[b] = numel;
+    numel *= v.base[b];
+  }
+  const int last = v.nb - 1;
+  int64_t rows = 1;
+  for (int b = last - 1; b >= 0; --b) {
+    img[b] = rows * lanes;
+    rows *= v.base[b];
+  }
+  const int64_t stick_stride = rows * lanes;   // between stick columns
+  if (v.offset < 0 || v.offset >= numel) return TS_ERR_INVALID;
+  int64_t o[kMaxDims];
+  for (int b = 0; b < v.nb; ++b) o[b] = (v.offset / rm[b]) % v.base[b];
+  bool used[kMaxDims] = {false};
+  int64_t constant = 0;
+  for (int b = 0; b < last; ++b) constant += o[b] * img[b];
+  constant += (o[last] / lanes) * stick_stride + o[last] % lanes;
+  *walks_stick_to_end = false;
+  for (int i = 0; i < rank; ++i) {
+    dims[i] = SideDim{false, 0, 0};
+    if (size[i] <= 1) continue;
+    const int64_t st = v.strides[i];
+    if (st == 0) {
+      if (is_dst) return TS_ERR_UNSUPPORTED;   // several indices would write one element
+      continue;
+    }
+    if (st < 0) return TS_ERR_UNSUPPORTED;
+    int found = -1;
+    for (int b = 0; b < v.nb && found < 0; ++b) {
+      if (used[b] || v.base[b] <= 1 || st % rm[b]) continue;
+      if (o[b] + (size[i] - 1) * (st / rm[b]) < v.base[b]) found = b;
+    }
+    if (found < 0) return TS_ERR_UNSUPPORTED;
+    used[found] = true;
+    const int64_t k = st / rm[found];
+    if (found != last) {
+      dims[i].step = k * img[found];
+      continue;
+    }
+    const bool to_end = k == 1 && o[last] + size[i] == v.base[last];
+    const bool inside = o[last] % lanes + (size[i] - 1) * k < lanes;
+    // a destination whose last stick has pad lanes gets them zeroed, which the split form does
+    const bool must_pad = is_dst && to_end && v.base[last] % lanes != 0;
+    if (inside && !must_pad) {
+      dims[i].step = k;                       // stays inside one stick
+    } else if (k == 1 && o[last] % lanes == 0) {
+      dims[i] = SideDim{true, 1, stick_stride};
+      *walks_stick_to_end = to_end;
+    } else {
+      return TS_ERR_UNSUPPORTED;
+    }
+  }
+  return constant;
+}
+
+int run_view(const char* src, char* dst, int eb, const int64_t* size, int rank, const ViewSide& sv,
+             const ViewSide& dv, cudaStream_t st) {
+  if (rank < 1 || rank > kMaxDims || !size || !sv.base || !dv.base || !sv.strides || !dv.strides)
+    return TS_ERR_INVALID;
+  if (eb != 1 && eb != 2 && eb != 4) return TS_ERR_INVALID;
+  for (int i = 0; i < rank; ++i) {
+    if (size[i] < 0) return TS_ERR_INVALID;
+    if (size[i] == 0) return TS_OK;
+  }
+  if (!src || !dst) return TS_ERR_INVALID;
+  const int lanes = kStickBytes / eb;
+  SideDim sd[kMaxDims], dd[kMaxDims];
+  bool s_end, d_end;
+  const int64_t soff = decompose_side(sv, size, rank, lanes, false, sd, &s_end);
+  if (soff < 0) return (int)soff;
+  const int64_t doff = decompose_side(dv, size, rank, lanes, true, dd, &d_end);
+  if (doff < 0) return (int)doff;
+  // Iteration dims: a view dim split on either side becomes (stick, lane); the side that is
+  // not split walks it with strides (lanes * step, step).
+  IterDim it[kMaxDims];
+  int nd = 0, nchecks = 0;
+  int64_t vlimit[kMaxChecks] = {0, 0};
+  int vfill[kMaxChecks] = {0, 0};
+  for (int i = 0; i < rank; ++i) {
+    if (size[i] <= 1) continue;
+    const bool split = sd[i].split || dd[i].split;
+    if (!split) {
+      if (nd == kMaxDims) return TS_ERR_UNSUPPORTED;
+      it[nd++] = IterDim{size[i], sd[i].step, dd[i].step, {0, 0}};
+      continue;
+    }
+    if (nd + 2 > kMaxDims) return TS_ERR_UNSUPPORTED;
+    const int64_t sticks = ceil_div(size[i], lanes);
+    IterDim hi{sticks, sd[i].split ? sd[i].hi_step : sd[i].step * lanes,
+               dd[i].split ? dd[i].hi_step : dd[i].step * lanes, {0, 0}};
+    IterDim lo{lanes, sd[i].step, dd[i].step, {0, 0}};
+    if (size[i] % lanes) {
+      if (nchecks == kMaxChecks) return TS_ERR_UNSUPPORTED;
+      hi.vm[nchecks] = lanes;
+      lo.vm[nchecks] = 1;
+      vlimit[nchecks] = size[i];
+      // lanes past the end are pad lanes of the destination image (to be zeroed) only when the
+      // destination walks its stick dim here and reaches the end of it; anywhere else they are
+      // other elements, or do not exist
+      vfill[nchecks] = (dd[i].split && d_end) ? 1 : 0;
+      ++nchecks;
+    }
+    it[nd++] = hi;
+    it[nd++] = lo;
+  }
+  if (dv.base[dv.nb - 1] == 1) {
+    // one value per stick in the destination: a lane dim that repeats the value, of which only
+    // lane 0 exists, zeroes the other lanes
+    if (nd == kMaxDims || nchecks == kMaxChecks) return TS_ERR_UNSUPPORTED;
+    IterDim lo{lanes, 0, 1, {0, 0}};
+    lo.vm[nchecks] = 1;
+    vlimit[nchecks] = 1;
+    vfill[nchecks] = 1;
+    ++nchecks;
+    it[nd++] = lo;
+  }
+  if (nd == 0) it[nd++] = IterDim{1, 1, 1, {0, 0}};
+  return plan_and_launch(it, nd, nchecks, vlimit, vfill, kPerCheck, eb, src + soff * eb, dst + doff * eb, st);
 }
 
 // Lowest and one-past-highest element offsets a non-negatively strided host tensor touches.
@@ -662,4 +859,15 @@ extern "C" int ts_layout_init(const int64_t* host_size, int rank, int elem_bytes
     cur *= device_size[i];
   }
   return ndev;
+}
+
+extern "C" int ts_transpose_tiles(const void* src_sticks, const int64_t* src_base, int src_base_rank,
+                                  const int64_t* src_strides, int64_t src_offset, void* dst_sticks,
+                                  const int64_t* dst_base, int dst_base_rank, const int64_t* dst_strides,
+                                  int64_t dst_offset, const int64_t* size, int rank, int elem_bytes,
+                                  void* stream) {
+  const ViewSide sv{src_base, src_base_rank, src_strides, src_offset};
+  const ViewSide dv{dst_base, dst_base_rank, dst_strides, dst_offset};
+  return run_view((const char*)src_sticks, (char*)dst_sticks, elem_bytes, size, rank, sv, dv,
+                  (cudaStream_t)stream);
 }

@@ -378,9 +378,10 @@ def _cuda_device(t: torch.Tensor) -> torch.device:
 
 @_impl("cat")
 def _cat(tensors, dim=0):
-    """Inputs are unpacked side by side into one row-major scratch tensor (the relayout kernel
-    writes through any strides) which is then laid out as the result: two passes over the data,
-    whatever the number of inputs or the dim."""
+    """One image-to-image pass per input when the inputs land on stick boundaries of the result
+    (any dim but the last, or widths that are multiples of a stick).  Otherwise the inputs are
+    unpacked side by side into one row-major scratch tensor (the relayout kernel writes through
+    any strides) which is then laid out as the result: two passes over the data."""
     tensors = [t for t in tensors if not (t.dim() == 1 and t.numel() == 0)]   # legacy empties
     if not tensors:
         raise RuntimeError("torch.cat(): expected a non-empty list of Tensors")
@@ -399,6 +400,17 @@ def _cat(tensors, dim=0):
         out_shape[dim] += t.shape[dim]
     out = _new(out_shape, like)
     if out.numel() == 0:
+        return out
+    lanes = 128 // like.element_size()
+    if dim != nd - 1 or all(t.shape[dim] % lanes == 0 for t in tensors[:-1]):
+        # every input lands on stick boundaries of the result: one image-to-image pass each,
+        # straight into its slice (pad lanes are zeroed by the slice that reaches the end)
+        off = 0
+        for t in tensors:
+            n = t.shape[dim]
+            if n:
+                out.narrow(dim, off, n).copy_(t)
+            off += n
         return out
     with _with_device(like):
         raw = torch.empty(out_shape, dtype=like.dtype, device=_cuda_device(like))
