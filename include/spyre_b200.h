@@ -57,7 +57,7 @@ const char* ts_last_cuda_error(void);
  * times in dim_map is split over those device dims, outermost most
  * significant.  to_sticks writes every element of the stick image (pad lanes
  * become zero); from_sticks writes exactly the host tensor's elements.
- * elem_bytes is 1, 2 or 4.  Bit-exact: elements are moved, never converted.
+ * elem_bytes is 1, 2, 4 or 8.  Bit-exact: elements are moved, never converted.
  */
 int ts_relayout_to_sticks(const void* strided, void* sticks, int elem_bytes,
                           const int64_t* host_size, const int64_t* host_strides, int rank,
@@ -109,7 +109,7 @@ int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int el
  * starts at a stick boundary with step 1 nor stays inside one stick, for a
  * destination with a zero stride, and for negative strides: callers then take
  * the two-pass route through ts_relayout_from_sticks / ts_relayout_to_sticks.
- * elem_bytes is 1, 2 or 4 (tiled transposes: 2 only; other sizes are moved
+ * elem_bytes is 1, 2, 4 or 8 (tiled transposes: 2 only; other sizes are moved
  * element by element).  The two images must not overlap.
  */
 int ts_transpose_tiles(const void* src_sticks, const int64_t* src_base, int src_base_rank,
@@ -117,6 +117,51 @@ int ts_transpose_tiles(const void* src_sticks, const int64_t* src_base, int src_
                        const int64_t* dst_base, int dst_base_rank, const int64_t* dst_strides,
                        int64_t dst_offset, const int64_t* size, int rank, int elem_bytes,
                        void* stream);
+
+/* Element type conversion between two stick images of one logical
+ * [rows, cols] tensor, on the device: the work behind `_to_copy` with a dtype
+ * change, which the reference's copy path refuses
+ * (torch_spyre/csrc/spyre_mem.cpp:669-671) and its view template sends through
+ * the host (codegen/templates/view.jinja2:40-46).  dtype codes: 0 = float16,
+ * 1 = bfloat16, 2 = float32.  Each image has the stick width of its own type
+ * (64 lanes of 2 bytes, 32 lanes of 4 bytes).  Round to nearest even; pad
+ * lanes of the destination are written as zero.
+ */
+enum { TS_DTYPE_F16 = 0, TS_DTYPE_BF16 = 1, TS_DTYPE_F32 = 2 };
+int ts_convert_sticks(const void* src, int src_dtype, void* dst, int dst_dtype, int64_t rows,
+                      int64_t cols, void* stream);
+
+/* ---- index-driven and scan ops of the eager long tail ------------------------
+ *
+ * embedding (codegen/inputs/Metadata.yaml:105, "Gather"): out[t, :] =
+ * weight[indices[t], :] for the tokens t of an [index_rows, index_cols] index
+ * tensor.  weight is the fp16 stick image of [vocab, dim], out that of
+ * [index_rows * index_cols, dim].  indices are int32 or int64 (index_bytes 4 / 8)
+ * in device memory: the stick image of the index tensor when indices_are_image
+ * != 0 (32 or 16 lanes per stick), else a plain array of index_rows * index_cols
+ * values.  A row whose index lies outside [0, vocab) is written as zeros and
+ * ts_gather_error_state() then reports 1 (it synchronises and clears the flag).
+ */
+int ts_embedding_rows(const void* weight, const void* indices, int index_bytes, int indices_are_image,
+                      int64_t index_rows, int64_t index_cols, void* out, int64_t vocab, int64_t dim,
+                      void* stream);
+int ts_gather_error_state(void);
+
+/* cumsum, which the reference computes on the host
+ * (codegen/inputs/spyre_torch_ops.cpp:501-505).  fp16 in and out, fp32 running
+ * sum.  ts_cumsum_rows: along the innermost (stick) dim of the stick image of
+ * [rows, cols]; ts_cumsum_mid: along the middle dim of a contiguous
+ * [outer][n][inner] array, which is what any other dim of a stick image is.
+ */
+int ts_cumsum_rows(const void* x, void* y, int64_t rows, int64_t cols, void* stream);
+int ts_cumsum_mid(const void* x, void* y, int64_t outer, int64_t n, int64_t inner, void* stream);
+
+/* upsample_nearest2d (codegen/inputs/Metadata.yaml:331,
+ * "ResizeNearestNeighbor") on fp16 stick images of [planes, in_h, in_w] and
+ * [planes, out_h, out_w] (planes = N * C); source index floor(dst * in / out).
+ */
+int ts_upsample_nearest2d(const void* x, void* y, int64_t planes, int64_t in_h, int64_t in_w,
+                          int64_t out_h, int64_t out_w, void* stream);
 
 /* SpyreTensorLayout::init (torch_spyre/csrc/spyre_tensor_impl.cpp:29-74) as a
  * plain function: fills device_size / device_strides / dim_map (rank + 1

@@ -290,3 +290,121 @@ def test_manual_seed_with_a_device_seeds_that_device():
     assert torch.cuda.default_generators[0].initial_seed() == 77
     with pytest.raises(RuntimeError):
         torch.spyre.manual_seed(1, device=4096)
+
+
+def test_dtype_conversion_stays_on_the_device():
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(5, 70, 130, generator=g).half()
+    xs = x.to(DEV)
+    f = xs.float()
+    assert f.device.type == DEV and f.dtype == torch.float32
+    assert torch.equal(f.cpu(), x.float())
+    assert torch.equal(f.half().cpu(), x)
+    assert torch.equal(xs.to(torch.bfloat16).cpu(), x.to(torch.bfloat16))
+    y = torch.randn(67, 100, generator=g) * 100
+    ys = y.to(DEV)
+    assert torch.equal(ys.half().cpu(), y.half())                       # round to nearest even, like the host
+    assert torch.equal(ys.to(torch.bfloat16).cpu(), y.to(torch.bfloat16))
+    assert torch.equal(ys.to(torch.bfloat16).float().cpu(), y.to(torch.bfloat16).float())
+    assert torch.equal(xs.to("cpu", dtype=torch.float32), x.float())
+    one = torch.tensor([3.5], dtype=torch.float16).to(DEV)
+    assert one.float().cpu().item() == 3.5
+    with pytest.raises(RuntimeError, match="type conversion"):
+        xs.to(torch.int32)
+
+
+def test_events_and_streams_of_the_spyre_guard():
+    """c10 events on spyre are CUDA events: record / query / synchronize / wait / elapsed time."""
+    s = torch.Stream(device=DEV)
+    e0, e1 = torch.Event(DEV, enable_timing=True), torch.Event(DEV, enable_timing=True)
+    x = torch.randn(512, 512).half().to(DEV)
+    e0.record()                    # on the device's current stream, where the kernels go
+    y = x @ x
+    e1.record()
+    e1.synchronize()
+    assert e1.query() and e0.query()
+    assert e0.elapsed_time(e1) >= 0.0
+    other = torch.Stream(device=DEV)
+    other.wait_event(e1)
+    other.synchronize()
+    assert_close(y.cpu(), x.cpu() @ x.cpu(), atol=2e-2)
+    e2 = torch.Event(DEV)          # no timing: still records and synchronises
+    e2.record(s)
+    e2.synchronize()
+    assert e2.query()
+
+
+def test_embedding_with_device_and_host_indices():
+    g = torch.Generator().manual_seed(13)
+    w = torch.randn(1000, 200, generator=g).half()
+    ids = torch.randint(0, 1000, (3, 70), generator=g)
+    ws = w.to(DEV)
+    want = F.embedding(ids, w)
+    assert torch.equal(F.embedding(ids.to(DEV), ws).cpu(), want)                 # int64 indices on the device
+    assert torch.equal(F.embedding(ids.int().to(DEV), ws).cpu(), want)           # int32
+    assert torch.equal(F.embedding(ids, ws).cpu(), want)                          # host indices
+    assert torch.equal(F.embedding(ids[0, :5].to(DEV), ws).cpu(), want[0, :5])    # 1-D, short
+    emb = torch.nn.Embedding(1000, 200).half()
+    with torch.no_grad():
+        emb.weight.copy_(w)
+    assert torch.equal(emb.to(DEV)(ids.to(DEV)).cpu(), want)
+    from torch_spyre import _abi
+    assert _abi.lib().ts_gather_error_state() == 0
+    bad = ids.clone()
+    bad[1, 3] = 5000                                                             # outside the table: zeros + flag
+    got = F.embedding(bad.to(DEV), ws).cpu()
+    assert _abi.lib().ts_gather_error_state() == 1 and _abi.lib().ts_gather_error_state() == 0
+    assert torch.equal(got[1, 3], torch.zeros(200, dtype=torch.float16))
+    assert torch.equal(got[0], want[0])
+
+
+def test_int64_tensors_round_trip():
+    x = torch.randint(-2 ** 40, 2 ** 40, (5, 37), generator=torch.Generator().manual_seed(14))
+    xs = x.to(DEV)
+    assert xs.dtype == torch.int64 and torch.equal(xs.cpu(), x)
+    assert torch.equal(xs.t().contiguous().cpu(), x.t().contiguous())
+
+
+@pytest.mark.parametrize("shape,dim", [((67, 256), 1), ((67, 256), 0), ((4, 50, 130), 2), ((4, 50, 130), 1),
+                                       ((4, 50, 130), 0), ((300,), 0), ((5, 7), -1)])
+def test_cumsum(shape, dim):
+    x = (torch.randn(*shape, generator=torch.Generator().manual_seed(15)) * 0.5).half()
+    got = torch.cumsum(x.to(DEV), dim).cpu()
+    assert_close(got, torch.cumsum(x, dim), atol=2e-2)    # sums of up to 256 terms: the tolerance sums take elsewhere
+
+
+def test_repeat_unsafe_view_bitwise_not_and_compare_out():
+    g = torch.Generator().manual_seed(16)
+    x = torch.randn(3, 5, 70, generator=g).half()
+    xs = x.to(DEV)
+    for reps in ((2, 1, 1), (1, 3, 1), (2, 2, 1), (1, 1, 2), (2, 3, 2), (2, 1, 1, 1)):
+        assert torch.equal(xs.repeat(*reps).cpu(), x.repeat(*reps)), reps
+    assert torch.equal(torch.ops.aten._unsafe_view(xs, [15, 70]).cpu(), x.view(15, 70))
+    mask = torch.ge(xs, 0.0)
+    assert torch.equal(torch.bitwise_not(mask).cpu().bool(), ~(x >= 0))
+    out = torch.empty(3, 5, 70, dtype=torch.float16, device=DEV)
+    torch.ne(xs, 0.5, out=out)
+    assert torch.equal(out.cpu().bool(), x != 0.5)
+
+
+@pytest.mark.parametrize("size", [(8, 12), (7, 5), (16, 130), (3, 3)])
+def test_upsample_nearest2d(size):
+    x = torch.randn(2, 3, 4, 6, generator=torch.Generator().manual_seed(17)).half()
+    got = F.interpolate(x.to(DEV), size=size, mode="nearest").cpu()
+    assert torch.equal(got, F.interpolate(x.float(), size=size, mode="nearest").half())
+    if size == (8, 12):
+        assert torch.equal(F.interpolate(x.to(DEV), scale_factor=2, mode="nearest").cpu(), got)
+
+
+def test_dropout_forward_and_backward_ops():
+    x = torch.randn(64, 256, generator=torch.Generator().manual_seed(18)).half()
+    xs = x.to(DEV)
+    y, m = torch.ops.aten.native_dropout(xs, 0.25, True)
+    y, m = y.cpu(), m.cpu()
+    assert set(m.unique().tolist()) <= {0.0, 1.0} and 0.6 < m.float().mean() < 0.9
+    assert_close(y, x * m * (1 / 0.75))
+    y2, m2 = torch.ops.aten.native_dropout(xs, 0.25, False)
+    assert torch.equal(y2.cpu(), x) and torch.equal(m2.cpu(), torch.ones_like(x))
+    gsp = torch.ops.aten.native_dropout_backward(xs, m.to(DEV), 2.0).cpu()
+    assert_close(gsp, x * m * 2.0)
+    assert torch.equal(F.dropout(xs, 0.5, training=False).cpu(), x)

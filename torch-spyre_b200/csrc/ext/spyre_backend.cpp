@@ -163,6 +163,63 @@ struct SpyreGuardImpl final : c10::impl::DeviceGuardImplInterface {
     c10::cuda::device_synchronize();
   }
   void recordDataPtrOnStream(const c10::DataPtr&, const c10::Stream&) const override {}
+  void* getStreamNativeHandle(const c10::Stream s) const override { return unwrap(s).stream(); }
+
+  // ---- events: CUDA events behind c10::Event, as the reference's guard implements them on its
+  // own runtime (torch_spyre/csrc/spyre_hooks.cpp:108-256: record, block, queryEvent,
+  // elapsedTime, destroyEvent).  An event is created lazily by its first record().
+  void destroyEvent(void* event, const c10::DeviceIndex device_index) const noexcept override {
+    if (!event) return;
+    int orig = -1;
+    if (cudaGetDevice(&orig) != cudaSuccess) return;
+    if (device_index >= 0) cudaSetDevice(device_index);
+    cudaEventDestroy(static_cast<cudaEvent_t>(event));
+    cudaSetDevice(orig);
+  }
+  void record(void** event, const c10::Stream& stream, const c10::DeviceIndex device_index,
+              const c10::EventFlag flag) const override {
+    TORCH_CHECK(device_index == -1 || device_index == stream.device_index(), "Event device index ",
+                device_index, " does not match recording stream's device index ", stream.device_index(), ".");
+    const c10::cuda::CUDAGuard guard(stream.device_index());
+    auto ev = static_cast<cudaEvent_t>(*event);
+    if (!ev) {
+      unsigned int cuda_flag = cudaEventDisableTiming;
+      switch (flag) {
+        case c10::EventFlag::PYTORCH_DEFAULT: cuda_flag = cudaEventDisableTiming; break;
+        case c10::EventFlag::BACKEND_DEFAULT: cuda_flag = cudaEventDefault; break;
+        default: TORCH_CHECK(false, "spyre event received unknown flag");
+      }
+      C10_CUDA_CHECK(cudaEventCreateWithFlags(&ev, cuda_flag));
+    }
+    C10_CUDA_CHECK(cudaEventRecord(ev, unwrap(stream).stream()));
+    *event = ev;
+  }
+  void block(void* event, const c10::Stream& stream) const override {
+    if (!event) return;
+    const c10::cuda::CUDAGuard guard(stream.device_index());
+    C10_CUDA_CHECK(cudaStreamWaitEvent(unwrap(stream).stream(), static_cast<cudaEvent_t>(event), 0));
+  }
+  bool queryEvent(void* event) const override {
+    if (!event) return true;
+    const cudaError_t err = cudaEventQuery(static_cast<cudaEvent_t>(event));
+    if (err == cudaErrorNotReady) {
+      (void)cudaGetLastError();   // not ready is an answer, not an error
+      return false;
+    }
+    C10_CUDA_CHECK(err);
+    return true;
+  }
+  void synchronizeEvent(void* event) const override {
+    if (!event) return;
+    C10_CUDA_CHECK(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+  }
+  double elapsedTime(void* event1, void* event2, const c10::DeviceIndex device_index) const override {
+    TORCH_CHECK(event1 && event2, "Both events must be recorded before calculating elapsed time.");
+    const c10::cuda::CUDAGuard guard(device_index >= 0 ? device_index : c10::cuda::current_device());
+    float ms = 0;
+    C10_CUDA_CHECK(cudaEventElapsedTime(&ms, static_cast<cudaEvent_t>(event1), static_cast<cudaEvent_t>(event2)));
+    return static_cast<double>(ms);
+  }
 };
 
 struct SpyreHooks final : at::PrivateUse1HooksInterface {

@@ -29,7 +29,7 @@ void check_status(int rc, const char* what) {
 
 int checked_elem_bytes(c10::ScalarType t) {
   const int eb = (int)c10::elementSize(t);
-  TORCH_CHECK(eb == 1 || eb == 2 || eb == 4, "spyre tensors hold 1-, 2- or 4-byte elements; got ",
+  TORCH_CHECK(eb == 1 || eb == 2 || eb == 4 || eb == 8, "spyre tensors hold 1-, 2-, 4- or 8-byte elements; got ",
               t);
   return eb;
 }

@@ -45,6 +45,19 @@ constexpr double kWideCost = 0.93;              // time of a 256 x 512 pair tile
 constexpr long long kDrainLimit = 200000ll;     // ~0.1 ms: far longer than a TMA copy is in flight
 
 __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
+#ifdef TSB_TUNING
+// experiment counters of the tuning build: cycles the leaders' MMA threads spent waiting for
+// operands [0] and for a drained accumulator [1], their total loop cycles [2], cycles the
+// producers waited for a free stage [3], producer loop cycles [4]
+__device__ unsigned long long g_gemm_prof[8];
+#define TSB_PROF_DECL long long prof_t0 = 0, prof_a = 0, prof_b = 0; const long long prof_start = clock64();
+#define TSB_PROF_BEGIN prof_t0 = clock64();
+#define TSB_PROF_END(acc) acc += clock64() - prof_t0;
+#else
+#define TSB_PROF_DECL
+#define TSB_PROF_BEGIN
+#define TSB_PROF_END(acc)
+#endif
 
 struct GemmParams {
   __half* c;
@@ -55,6 +68,9 @@ struct GemmParams {
   int64_t c_stick_stride, c_head_stride;   // elements
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
   uint32_t band_tiles;   // tile columns per band of the tile order (see decode_tile)
+#ifdef TSB_TUNING
+  int tune_noload;       // experiment: arm the "full" barriers without issuing the TMA loads
+#endif
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
 };
@@ -429,6 +445,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
     if (lane == 0) {
+      TSB_PROF_DECL
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs) {
@@ -437,10 +454,18 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int bb = P.b_batched ? (int)b : 0;
         for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
           const uint32_t s = it % kPairStages, ph = (it / kPairStages) & 1;
+          TSB_PROF_BEGIN
           if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[s]), ph ^ 1, abort_flag,
                                       kWaitLimit)) { ok = false; break; }
+          TSB_PROF_END(prof_a)
           const uint32_t full_local = ptx::smem_u32(&bars->full[s]);
           const uint32_t full_leader = ptx::map_to_cta(full_local, 0);
+#ifdef TSB_TUNING
+          if (P.tune_noload && it >= (uint32_t)kPairStages) {
+            if (rank == 0) ptx::mbar_arrive(full_local);
+            continue;
+          }
+#endif
           if (rank == 0) ptx::mbar_arrive_expect_tx(full_local, 2 * kPairStageBytes);
           const uint32_t sa = tiles + s * kPairStageBytes, sb = sa + kABytes;
           ptx::tma_load_5d_pair(sa, &map_a, full_leader, 0, (int)(tm * 2 * BM + rank * BM), (int)b,
@@ -461,6 +486,12 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           }
         }
       }
+#ifdef TSB_TUNING
+      if (rank == 0) {
+        atomicAdd(&g_gemm_prof[3], (unsigned long long)prof_a);
+        atomicAdd(&g_gemm_prof[4], (unsigned long long)(clock64() - prof_start));
+      }
+#endif
       // Let copies still in flight land before either CTA can exit.  On the normal path every
       // issued stage has been consumed by then and these waits return at once.  The "full"
       // barriers live in the leader and count both CTAs' bytes, so the leader waits on them
@@ -493,12 +524,15 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t empty_c1 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 1);
       uint32_t s = 0, ph = 0, local_tile = 0;
       bool ok = true;
+      TSB_PROF_DECL
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
         for (uint32_t kb = 0; ok && kb < P.k_blocks; ++kb) {
+          TSB_PROF_BEGIN
           if (!ptx::mbar_wait_bounded(full0 + s * 8, ph, abort_flag, kWaitLimit)) {
             ok = false;
             break;
           }
+          TSB_PROF_END(prof_a)
           ptx::tc_fence_after_sync();
           const uint32_t so = s * (kPairStageBytes >> 4);
 #pragma unroll
@@ -506,8 +540,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             uint32_t slot, use;
             acc_slot<NH>(local_tile, half, slot, use);
             if (kb == 0) {   // the block's accumulator must have been drained by both CTAs
+              TSB_PROF_BEGIN
               if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_empty[slot]), (use & 1) ^ 1, abort_flag,
                                           kWaitLimit)) { ok = false; break; }
+              TSB_PROF_END(prof_b)
               ptx::tc_fence_after_sync();
             }
             const uint32_t d_tmem = tmem_base + slot * BN;
@@ -530,6 +566,11 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
       }
+#ifdef TSB_TUNING
+      atomicAdd(&g_gemm_prof[0], (unsigned long long)prof_a);
+      atomicAdd(&g_gemm_prof[1], (unsigned long long)prof_b);
+      atomicAdd(&g_gemm_prof[2], (unsigned long long)(clock64() - prof_start));
+#endif
     }
     __syncwarp();
   } else {
@@ -646,6 +687,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   if (const char* e = getenv("TS_GEMM_PAIR")) use_pair = atoi(e) != 0 && M > BM;
   if (const char* e = getenv("TS_GEMM_NH")) nh = atoi(e) == 2 && use_pair ? 2 : 1;
   if (const char* e = getenv("TS_GEMM_BAND")) band = (uint32_t)std::max(1, atoi(e));
+  P.tune_noload = getenv("TS_GEMM_NOLOAD") ? atoi(getenv("TS_GEMM_NOLOAD")) : 0;
 #endif
   P.band_tiles = band;
   if (use_pair) P.tiles_n = (uint32_t)ceil_div(N, BN * nh);
@@ -736,3 +778,13 @@ extern "C" int ts_gemm_f16_swiglu(const void* a, const void* w_gate_up, void* c,
   return gemm_launch(a, 0, 0, w_gate_up, 0, 0, nullptr, nullptr, c, 0, 0, 1, batch, M, 2 * N_out, K, 1, 0,
                      stream, 1);
 }
+
+#ifdef TSB_TUNING
+// tuning build only: reads and clears the experiment counters
+extern "C" int ts_gemm_prof(unsigned long long* out8) {
+  if (cudaMemcpyFromSymbol(out8, g_gemm_prof, sizeof(unsigned long long) * 8) != cudaSuccess) return TS_ERR_CUDA;
+  unsigned long long zero[8] = {0};
+  cudaMemcpyToSymbol(g_gemm_prof, zero, sizeof(zero));
+  return TS_OK;
+}
+#endif

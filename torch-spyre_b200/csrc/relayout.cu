@@ -386,7 +386,7 @@ int run(const Request& rq, cudaStream_t st) {
   if (!rq.host_size || !rq.host_strides || !rq.dev_size || !rq.dev_strides || !rq.dim_map)
     return TS_ERR_INVALID;
   if (rq.rank < 1 || rq.rank > kMaxDims || rq.ndev < 1 || rq.ndev > kMaxDims) return TS_ERR_INVALID;
-  if (rq.elem_bytes != 1 && rq.elem_bytes != 2 && rq.elem_bytes != 4) return TS_ERR_INVALID;
+  if (rq.elem_bytes != 1 && rq.elem_bytes != 2 && rq.elem_bytes != 4 && rq.elem_bytes != 8) return TS_ERR_INVALID;
   const int eb = rq.elem_bytes;
   int64_t total = 1;
   for (int d = 0; d < rq.ndev; ++d) {
@@ -694,7 +694,7 @@ int run_view(const char* src, char* dst, int eb, const int64_t* size, int rank, 
              const ViewSide& dv, cudaStream_t st) {
   if (rank < 1 || rank > kMaxDims || !size || !sv.base || !dv.base || !sv.strides || !dv.strides)
     return TS_ERR_INVALID;
-  if (eb != 1 && eb != 2 && eb != 4) return TS_ERR_INVALID;
+  if (eb != 1 && eb != 2 && eb != 4 && eb != 8) return TS_ERR_INVALID;
   for (int i = 0; i < rank; ++i) {
     if (size[i] < 0) return TS_ERR_INVALID;
     if (size[i] == 0) return TS_OK;

@@ -54,6 +54,13 @@ SIGNATURES = {
     "ts_transpose_tiles": (ctypes.c_int, [vp, c_i64p, ctypes.c_int, c_i64p, ctypes.c_int64, vp, c_i64p,
                                           ctypes.c_int, c_i64p, ctypes.c_int64, c_i64p, ctypes.c_int,
                                           ctypes.c_int, vp]),
+    "ts_convert_sticks": (ctypes.c_int, [vp, ctypes.c_int, vp, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, vp]),
+    "ts_embedding_rows": (ctypes.c_int, [vp, vp, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, vp,
+                                         ctypes.c_int64, ctypes.c_int64, vp]),
+    "ts_gather_error_state": (ctypes.c_int, []),
+    "ts_cumsum_rows": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, vp]),
+    "ts_cumsum_mid": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp]),
+    "ts_upsample_nearest2d": (ctypes.c_int, [vp, vp] + [ctypes.c_int64] * 5 + [vp]),
     "ts_layout_init": (ctypes.c_int, [c_i64p, ctypes.c_int, ctypes.c_int, c_i32p, c_i64p, c_i64p,
                                       c_i32p]),
     "ts_pointwise_chain": (ctypes.c_int, [ctypes.POINTER(PwInsn), ctypes.c_int,

@@ -569,16 +569,179 @@ def _addmm(bias, a, b, *, beta=1, alpha=1):
     return _binary("ADD", prod, bias, alpha=float(beta))
 
 
+_CONVERTIBLE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+def _convert_on_device(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """fp16 / bf16 / fp32 conversion of a spyre tensor by the device kernel (no host round trip)."""
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    if x.numel() == 0:
+        return out
+    with _with_device(x):
+        sx, so = _st(x), _st(out)
+        rc = K._abi.lib().ts_convert_sticks(sx.ptr(), _CONVERTIBLE[x.dtype], so.ptr(), _CONVERTIBLE[dtype],
+                                            sx.rows, sx.cols, K._stream())
+        K._abi.check(rc, "ts_convert_sticks")
+    return out
+
+
 @_impl("_to_copy")
 def _to_copy(x, *, dtype=None, layout=None, device=None, pin_memory=None, non_blocking=False,
              memory_format=None):
     device = torch.device(device) if device is not None else x.device
     dtype = dtype or x.dtype
     if dtype != x.dtype:
-        # dtype conversion happens on the host: the device copy path moves bits only
-        host = x.to("cpu") if x.device.type != "cpu" else x
-        host = host.to(dtype)
-        return host if device.type == "cpu" else host.to(device)
+        if x.device.type == "cpu":
+            # the data is on the host anyway: convert there, then it is an ordinary copy
+            return x.to(dtype).to(device)
+        if dtype not in _CONVERTIBLE or x.dtype not in _CONVERTIBLE:
+            # as the reference's copy path (torch_spyre/csrc/spyre_mem.cpp:669-671)
+            raise RuntimeError(f"Spyre backend does not support type conversion from {x.dtype} to {dtype} "
+                               "on the device (float16, bfloat16 and float32 convert)")
+        converted = _convert_on_device(x, dtype)
+        return converted if device == x.device else converted.to(device)
     out = torch.empty(x.shape, dtype=dtype, device=device)
     out.copy_(x)
+    return out
+
+
+# ---- the rest of the reference's eager op list ------------------------------------------
+# (codegen/inputs/Metadata.yaml: embedding :105, bitwise_not :31, repeat :245, _unsafe_view :325,
+# upsample_nearest2d :331, native_dropout_backward :93; codegen/inputs/spyre_torch_ops.cpp:494-505:
+# ne.Scalar_out and cumsum, which the reference bounces through the host)
+
+@_impl("embedding")
+def _embedding(weight, indices, padding_idx=-1, scale_grad_by_freq=False, sparse=False):
+    """Row gather.  Indices: an int32 / int64 spyre tensor, or a host tensor (copied over)."""
+    _check_fp16(weight)
+    if weight.dim() != 2:
+        raise RuntimeError("embedding: 'weight' must be 2-D")
+    if indices.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError(f"embedding: indices must be int32 or int64, got {indices.dtype}")
+    vocab, dim = weight.shape
+    out = torch.empty(tuple(indices.shape) + (dim,), dtype=weight.dtype, device=weight.device)
+    if out.numel() == 0:
+        return out
+    with _with_device(weight):
+        if indices.device.type == "cpu":
+            idx = indices.contiguous().to(_cuda_device(weight), non_blocking=False)
+            ptr, is_image, rows, cols = idx.data_ptr(), 0, 1, idx.numel()
+        else:
+            idx = _st(indices if indices.dim() else indices.reshape(1))
+            ptr, is_image, rows, cols = idx.ptr(), 1, idx.rows, idx.cols
+        rc = K._abi.lib().ts_embedding_rows(_st(weight).ptr(), ptr, indices.element_size(), is_image, rows, cols,
+                                            _st(out).ptr(), vocab, dim, K._stream())
+        K._abi.check(rc, "ts_embedding_rows")
+        del idx
+    return out
+
+
+@_impl("bitwise_not")
+def _bitwise_not(x):
+    """The device's masks are fp16 0 / 1 tensors (what its comparisons return), so this is the
+    logical not, as the reference maps it (LogicalNot)."""
+    if x.dtype != torch.float16:
+        raise NotImplementedError(f"bitwise_not on spyre is defined for fp16 0/1 masks, got {x.dtype}")
+    return _unary("LOGICAL_NOT", x)
+
+
+for _name, _opcode in {"eq": "EQ", "ne": "NE", "lt": "LT", "le": "LE", "gt": "GT", "ge": "GE"}.items():
+    _impl(_name + ".Scalar_out")(lambda a, b, *, out, _o=_opcode: _copy_into(out, _binary(_o, a, b)))
+    _impl(_name + ".Tensor_out")(lambda a, b, *, out, _o=_opcode: _copy_into(out, _binary(_o, a, b)))
+
+
+@_impl("_unsafe_view")
+def _unsafe_view(x, size):
+    return x.view(size)
+
+
+@_impl("repeat")
+def _repeat(x, repeats):
+    """out viewed as [r0, s0, r1, s1, ...] takes x expanded over the r dims: one image-to-image
+    pass when the innermost dim is not repeated, the general copy route otherwise."""
+    repeats = [int(r) for r in repeats]
+    if len(repeats) < x.dim():
+        raise RuntimeError("Number of dimensions of repeat dims can not be smaller than number of "
+                           "dimensions of tensor")
+    shape = [1] * (len(repeats) - x.dim()) + list(x.shape)
+    out_shape = [r * s for r, s in zip(repeats, shape)]
+    out = torch.empty(out_shape, dtype=x.dtype, device=x.device)
+    if out.numel() == 0:
+        return out
+    inter, src_shape = [], []
+    for r, s in zip(repeats, shape):
+        inter += [r, s]
+        src_shape += [1, s]
+    out.view(inter).copy_(x.reshape(src_shape).expand(inter))
+    return out
+
+
+@_impl("cumsum")
+def _cumsum(x, dim, *, dtype=None):
+    _check_fp16(x)
+    if dtype not in (None, torch.float16):
+        raise NotImplementedError("cumsum on spyre accumulates in fp32 and returns fp16")
+    out = _new(x.shape, x)
+    if x.numel() == 0:
+        return out
+    nd = max(x.dim(), 1)
+    d = dim % nd
+    with _with_device(x):
+        sx, so = _st(x), _st(out)
+        if d == nd - 1:
+            rc = K._abi.lib().ts_cumsum_rows(sx.ptr(), so.ptr(), sx.rows, sx.cols, K._stream())
+        else:
+            outer, n, inner = K._mid_view(sx.shape, d)
+            rc = K._abi.lib().ts_cumsum_mid(sx.ptr(), so.ptr(), outer, n, inner, K._stream())
+        K._abi.check(rc, "ts_cumsum")
+    return out
+
+
+@_impl("upsample_nearest2d")
+def _upsample_nearest2d(x, output_size, scales_h=None, scales_w=None):
+    _check_fp16(x)
+    if x.dim() != 4:
+        raise RuntimeError("upsample_nearest2d expects a [N, C, H, W] tensor")
+    n, c, ih, iw = x.shape
+    oh, ow = (int(v) for v in output_size)
+    for given, i, o in ((scales_h, ih, oh), (scales_w, iw, ow)):
+        if given is not None and abs(float(given) - o / i) > 1e-6:
+            raise NotImplementedError("upsample_nearest2d with scale factors that differ from the size ratio")
+    out = torch.empty((n, c, oh, ow), dtype=x.dtype, device=x.device)
+    if out.numel() == 0:
+        return out
+    with _with_device(x):
+        rc = K._abi.lib().ts_upsample_nearest2d(_st(x).ptr(), _st(out).ptr(), n * c, ih, iw, oh, ow, K._stream())
+        K._abi.check(rc, "ts_upsample_nearest2d")
+    return out
+
+
+@_impl("native_dropout")
+def _native_dropout(x, p, train):
+    """(x * mask / (1 - p), mask) with an fp16 0 / 1 mask drawn from the CUDA generator of the
+    tensor's device; identity (mask of ones) when not training.  The reference returns its input
+    untouched (codegen/inputs/spyre_torch_ops.cpp:186-194)."""
+    _check_fp16(x)
+    p = float(p)
+    if not train or p == 0.0:
+        return x.clone(), _fill(_new(x.shape, x), 1.0)
+    if p >= 1.0:
+        return _fill(_new(x.shape, x), 0.0), _fill(_new(x.shape, x), 0.0)
+    with _with_device(x):
+        keep = (torch.rand(tuple(x.shape) or (1,), device=_cuda_device(x)) >= p).to(torch.float16)
+        mask = _new(x.shape, x)
+        K.to_sticks(keep, out=_st(mask))
+    return _native_dropout_backward(x, mask, 1.0 / (1.0 - p)), mask
+
+
+@_impl("native_dropout_backward")
+def _native_dropout_backward(grad, mask, scale):
+    _check_fp16(grad, mask)
+    out = _new(grad.shape, grad)
+    if out.numel() == 0:
+        return out
+    with _with_device(grad):
+        c = Chain()
+        c.emit("LOAD", c.tensor(_st(grad))).emit("MUL", c.tensor(_st(mask))).emit("MUL", c.imm(float(scale))).store(0)
+        K.run_chain(c, grad.shape, outputs=[_st(out)])
     return out
