@@ -87,6 +87,34 @@ int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int el
                            const int64_t* device_size, const int64_t* device_strides,
                            const int32_t* dim_map, int ndev, void* stream);
 
+/* Pipelined forms of the two host-buffer calls.  The host span is cut along the
+ * tensor's leading dim into chunks of about 8 MiB that travel through the two
+ * halves of `staging`: the PCIe copy of one chunk runs on an internal copy
+ * stream while the relayout kernel of the previous one runs on `stream`, and
+ * the staging buffer need only hold ts_copy_staging_bytes(...) bytes (at most
+ * 16 MiB) instead of the whole span.  Synchronising `stream` afterwards
+ * covers the copies too.  A tensor that cannot be cut that way (rank 1, a
+ * leading dim that is the stick dim or overlaps in memory, a destination with
+ * gaps between its elements) takes the single-shot path above and then
+ * needs staging_bytes >= ts_host_span_bytes(...) (TS_ERR_TOO_LARGE otherwise).
+ * First use on a device creates that device's copy stream and four events
+ * (no device memory); later calls on the device reuse them and are serialised
+ * while they enqueue.  Same reference interfaces as above
+ * (torch_spyre/csrc/spyre_mem.cpp:408-438).
+ */
+int64_t ts_copy_staging_bytes(int elem_bytes, const int64_t* host_size, const int64_t* host_strides,
+                              int rank);
+int ts_copy_host_to_sticks_pipelined(const void* host, void* staging, int64_t staging_bytes, void* sticks,
+                                     int elem_bytes, const int64_t* host_size,
+                                     const int64_t* host_strides, int rank, const int64_t* device_size,
+                                     const int64_t* device_strides, const int32_t* dim_map, int ndev,
+                                     void* stream);
+int ts_copy_sticks_to_host_pipelined(const void* sticks, void* staging, int64_t staging_bytes, void* host,
+                                     int elem_bytes, const int64_t* host_size,
+                                     const int64_t* host_strides, int rank, const int64_t* device_size,
+                                     const int64_t* device_strides, const int32_t* dim_map, int ndev,
+                                     void* stream);
+
 /* Stick image -> stick image for a strided view on either side, in one pass:
  * the device-side restickify behind transposed / permuted / sliced / narrowed
  * / expanded tensors.  Stands in for the reference's data-op programs

@@ -137,6 +137,41 @@ def test_host_buffer_entry_points(cuda):
         assert torch.equal(back.view(torch.int16), bits)
 
 
+@pytest.mark.parametrize("shape,perm", [((40, 512, 1024), None), ((37, 300, 1000), None), ((24, 1024, 512), (0, 2, 1)),
+                                        ((5, 2048, 4096), None), ((3000, 4100), None)])
+def test_pipelined_host_copies_in_chunks(shape, perm, cuda):
+    """Tensors large enough to be cut into several chunks (8 MiB, or one leading slice if that
+    is larger): image against the oracle, round trip bit for bit, with the small staging block the
+    library asks for, from pinned and from pageable host memory, and through the spyre device."""
+    g = torch.Generator().manual_seed(6)
+    bits = torch.randint(-32768, 32768, shape, dtype=torch.int16, generator=g)
+    if perm:
+        bits = bits.permute(perm).contiguous().permute(perm)
+    host = bits.view(torch.float16)
+    strides = host.stride()
+    want = C.to_sticks(np.lib.stride_tricks.as_strided(
+        bits.numpy().view(np.uint16), shape=host.shape, strides=[s * 2 for s in strides]),
+        L.generic_stick_layout(tuple(host.shape)), nthreads=8)
+    need = int(_abi.lib().ts_copy_staging_bytes(2, _abi.i64(tuple(host.shape)), _abi.i64(strides), host.dim()))
+    assert 0 < need <= max(2 * 8 << 20, 2 * (host[0].numel() * 2 + 255)) and need < host.numel() * 2
+    for src in (host.pin_memory() if not perm else torch.empty_strided(host.shape, strides, dtype=host.dtype)
+                .pin_memory().copy_(host), host):
+        st = K.copy_host_to_sticks(src)
+        torch.cuda.synchronize()
+        assert np.array_equal(st.image.cpu().numpy().view(np.uint16), want)
+        back = torch.empty_strided(host.shape, strides, dtype=host.dtype)
+        back = back.pin_memory() if src.is_pinned() else back
+        K.copy_sticks_to_host(st, back)
+        torch.cuda.synchronize()
+        assert torch.equal(back.view(torch.int16), bits)
+    import torch_spyre  # noqa: F401
+    xs = host.to("spyre")
+    assert torch.equal(xs.cpu().view(torch.int16), bits)
+    assert _abi.lib().ts_copy_host_to_sticks_pipelined(None, None, 0, None, 2, _abi.i64([4, 4]), _abi.i64([4, 1]), 2,
+                                                       _abi.i64([1, 4, 64]), _abi.i64([256, 64, 1]),
+                                                       _abi.i32([1, 0, 1]), 3, None) == _abi.TS_ERR_INVALID
+
+
 def test_scalar_becomes_one_element(cuda):
     t = torch.tensor(3.5, dtype=torch.float16, device=cuda)
     st = K.to_sticks(t)

@@ -200,12 +200,23 @@ void host_to_device(const at::Tensor& src_cpu, const at::Tensor& dst) {
     auto strides = src.strides().vec();
     if (strides.empty()) strides = {1};
     for (auto s : strides) TORCH_CHECK(s >= 0, "negative host strides are not supported");
-    const int64_t span = ts_host_span_bytes(ctx->elem_bytes, shape.data(), strides.data(), (int)shape.size());
-    void* staging = c10::cuda::CUDACachingAllocator::raw_alloc_with_stream(std::max<int64_t>(span, 16), st);
+    // chunks of the host span go through a small staging block, copy and relayout overlapped
+    const int64_t want = std::max<int64_t>(
+        ts_copy_staging_bytes(ctx->elem_bytes, shape.data(), strides.data(), (int)shape.size()), 256);
+    void* staging = c10::cuda::CUDACachingAllocator::raw_alloc_with_stream(want, st);
     const auto lay = layout_of(shape, ctx->elem_bytes);
-    const int rc = ts_copy_host_to_sticks(src.data_ptr(), staging, ctx->ptr, ctx->elem_bytes,
-                                          shape.data(), strides.data(), (int)shape.size(), lay.dsize,
-                                          lay.dstride, lay.dmap, lay.ndev, st);
+    int rc = ts_copy_host_to_sticks_pipelined(src.data_ptr(), staging, want, ctx->ptr, ctx->elem_bytes,
+                                              shape.data(), strides.data(), (int)shape.size(), lay.dsize,
+                                              lay.dstride, lay.dmap, lay.ndev, st);
+    if (rc == TS_ERR_TOO_LARGE) {   // not cuttable: the whole span at once
+      C10_CUDA_CHECK(cudaStreamSynchronize(st));
+      c10::cuda::CUDACachingAllocator::raw_delete(staging);
+      const int64_t span = ts_host_span_bytes(ctx->elem_bytes, shape.data(), strides.data(), (int)shape.size());
+      staging = c10::cuda::CUDACachingAllocator::raw_alloc_with_stream(std::max<int64_t>(span, 16), st);
+      rc = ts_copy_host_to_sticks(src.data_ptr(), staging, ctx->ptr, ctx->elem_bytes, shape.data(),
+                                  strides.data(), (int)shape.size(), lay.dsize, lay.dstride, lay.dmap,
+                                  lay.ndev, st);
+    }
     // the host buffer and the staging block must outlive the copy
     C10_CUDA_CHECK(cudaStreamSynchronize(st));
     c10::cuda::CUDACachingAllocator::raw_delete(staging);
@@ -233,16 +244,33 @@ void device_to_host(const at::Tensor& src, const at::Tensor& dst_cpu) {
     auto strides = dst_cpu.strides().vec();
     if (strides.size() != shape.size()) strides.assign(shape.size(), 1);
     const int64_t span = ts_host_span_bytes(ctx->elem_bytes, shape.data(), strides.data(), (int)shape.size());
-    void* staging = c10::cuda::CUDACachingAllocator::raw_alloc_with_stream(std::max<int64_t>(span, 16), st);
     const auto lay = layout_of(shape, ctx->elem_bytes);
-    // a destination with gaps keeps its gap bytes: pre-load the staging image with them
     int64_t dense = ctx->elem_bytes;
     for (auto s : shape) dense *= s;
-    if (span != dense)
-      C10_CUDA_CHECK(cudaMemcpyAsync(staging, dst_cpu.data_ptr(), span, cudaMemcpyHostToDevice, st));
-    const int rc = ts_copy_sticks_to_host(ctx->ptr, staging, dst_cpu.data_ptr(), ctx->elem_bytes,
-                                          shape.data(), strides.data(), (int)shape.size(), lay.dsize,
-                                          lay.dstride, lay.dmap, lay.ndev, st);
+    void* staging = nullptr;
+    int rc = TS_ERR_TOO_LARGE;
+    if (span == dense) {   // chunks through a small staging block, relayout and copy overlapped
+      const int64_t want = std::max<int64_t>(
+          ts_copy_staging_bytes(ctx->elem_bytes, shape.data(), strides.data(), (int)shape.size()), 256);
+      staging = c10::cuda::CUDACachingAllocator::raw_alloc_with_stream(want, st);
+      rc = ts_copy_sticks_to_host_pipelined(ctx->ptr, staging, want, dst_cpu.data_ptr(), ctx->elem_bytes,
+                                            shape.data(), strides.data(), (int)shape.size(), lay.dsize,
+                                            lay.dstride, lay.dmap, lay.ndev, st);
+      if (rc == TS_ERR_TOO_LARGE) {
+        C10_CUDA_CHECK(cudaStreamSynchronize(st));
+        c10::cuda::CUDACachingAllocator::raw_delete(staging);
+        staging = nullptr;
+      }
+    }
+    if (rc == TS_ERR_TOO_LARGE) {
+      staging = c10::cuda::CUDACachingAllocator::raw_alloc_with_stream(std::max<int64_t>(span, 16), st);
+      // a destination with gaps keeps its gap bytes: pre-load the staging image with them
+      if (span != dense)
+        C10_CUDA_CHECK(cudaMemcpyAsync(staging, dst_cpu.data_ptr(), span, cudaMemcpyHostToDevice, st));
+      rc = ts_copy_sticks_to_host(ctx->ptr, staging, dst_cpu.data_ptr(), ctx->elem_bytes, shape.data(),
+                                  strides.data(), (int)shape.size(), lay.dsize, lay.dstride, lay.dmap,
+                                  lay.ndev, st);
+    }
     C10_CUDA_CHECK(cudaStreamSynchronize(st));
     c10::cuda::CUDACachingAllocator::raw_delete(staging);
     check_status(rc, "copy device to host");

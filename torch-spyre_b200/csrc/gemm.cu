@@ -41,6 +41,12 @@ constexpr int kStagingBytes = 4 * 32 * 128;   // epilogue: 32 rows x 128 bytes p
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
+constexpr bool kOneCommit = false;             // one masked commit for both CTAs instead of two commits
+#ifdef TSB_TUNING
+#define TSB_TUNE_ONECOMMIT || P.tune_onecommit
+#else
+#define TSB_TUNE_ONECOMMIT
+#endif
 constexpr double kWideCost = 0.93;              // time of a 256 x 512 pair tile relative to two 256 x 256 ones
 constexpr long long kDrainLimit = 200000ll;     // ~0.1 ms: far longer than a TMA copy is in flight
 
@@ -69,7 +75,8 @@ struct GemmParams {
   uint32_t tiles_m, tiles_n, num_tiles, k_blocks;
   uint32_t band_tiles;   // tile columns per band of the tile order (see decode_tile)
 #ifdef TSB_TUNING
-  int tune_noload;       // experiment: arm the "full" barriers without issuing the TMA loads
+  int tune_noload;       // experiment: 1 = arm the "full" barriers without issuing the TMA loads, 2 = MMAs alone
+  int tune_onecommit;    // experiment: masked commits
 #endif
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
@@ -454,6 +461,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         const int bb = P.b_batched ? (int)b : 0;
         for (uint32_t kb = 0; kb < P.k_blocks; ++kb, ++it) {
           const uint32_t s = it % kPairStages, ph = (it / kPairStages) & 1;
+#ifdef TSB_TUNING
+          if (P.tune_noload & 2) { ok = false; break; }   // experiment: MMAs alone, no ring at all
+#endif
           TSB_PROF_BEGIN
           if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[s]), ph ^ 1, abort_flag,
                                       kWaitLimit)) { ok = false; break; }
@@ -461,7 +471,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           const uint32_t full_local = ptx::smem_u32(&bars->full[s]);
           const uint32_t full_leader = ptx::map_to_cta(full_local, 0);
 #ifdef TSB_TUNING
-          if (P.tune_noload && it >= (uint32_t)kPairStages) {
+          if ((P.tune_noload & 1) && it >= (uint32_t)kPairStages) {
             if (rank == 0) ptx::mbar_arrive(full_local);
             continue;
           }
@@ -520,6 +530,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
       const uint32_t b_step = P.b_kmajor ? (32u >> 4) : (2048u >> 4);
       const uint32_t full0 = ptx::smem_u32(&bars->full[0]);
+      const uint32_t empty_l0 = ptx::smem_u32(&bars->empty[0]);
       const uint32_t empty_c0 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 0);
       const uint32_t empty_c1 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 1);
       uint32_t s = 0, ph = 0, local_tile = 0;
@@ -528,6 +539,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
         for (uint32_t kb = 0; ok && kb < P.k_blocks; ++kb) {
           TSB_PROF_BEGIN
+#ifdef TSB_TUNING
+          if (!(P.tune_noload & 2))
+#endif
           if (!ptx::mbar_wait_bounded(full0 + s * 8, ph, abort_flag, kWaitLimit)) {
             ok = false;
             break;
@@ -557,12 +571,26 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
             if (kb + 1 == P.k_blocks) {   // this block is complete once the MMAs issued so far are
               const uint32_t f = ptx::smem_u32(&bars->acc_full[slot]);
-              ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
-              ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
+              if (kOneCommit TSB_TUNE_ONECOMMIT) {
+                ptx::umma_commit_pair_mask(f, 3);
+              } else {
+                ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
+                ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
+              }
             }
           }
-          ptx::umma_commit_pair(empty_c0 + s * 8);
-          ptx::umma_commit_pair(empty_c1 + s * 8);
+#ifdef TSB_TUNING
+          if (!(P.tune_noload & 2)) {
+#endif
+          if (kOneCommit TSB_TUNE_ONECOMMIT) {
+            ptx::umma_commit_pair_mask(empty_l0 + s * 8, 3);   // "stage free" to both CTAs at once
+          } else {
+            ptx::umma_commit_pair(empty_c0 + s * 8);
+            ptx::umma_commit_pair(empty_c1 + s * 8);
+          }
+#ifdef TSB_TUNING
+          }
+#endif
           if (++s == kPairStages) { s = 0; ph ^= 1; }
         }
       }
@@ -688,6 +716,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   if (const char* e = getenv("TS_GEMM_NH")) nh = atoi(e) == 2 && use_pair ? 2 : 1;
   if (const char* e = getenv("TS_GEMM_BAND")) band = (uint32_t)std::max(1, atoi(e));
   P.tune_noload = getenv("TS_GEMM_NOLOAD") ? atoi(getenv("TS_GEMM_NOLOAD")) : 0;
+  P.tune_onecommit = getenv("TS_GEMM_ONECOMMIT") ? atoi(getenv("TS_GEMM_ONECOMMIT")) : 0;
 #endif
   P.band_tiles = band;
   if (use_pair) P.tiles_n = (uint32_t)ceil_div(N, BN * nh);

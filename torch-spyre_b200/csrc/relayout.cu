@@ -12,6 +12,7 @@
 //   * transpose_tiles  - the unit-stride dims differ (a permuted host tensor):
 //                        64x64 fp16 tiles are transposed through shared memory.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -829,6 +830,191 @@ extern "C" int ts_copy_sticks_to_host(const void* sticks, void* staging, void* h
   if (cudaMemcpyAsync(host, staging, (size_t)bytes, cudaMemcpyDeviceToHost,
                       (cudaStream_t)stream) != cudaSuccess)
     return TS_ERR_CUDA;
+  return TS_OK;
+}
+
+// ---- pipelined host <-> device copies ------------------------------------------------------
+// The host span is moved in chunks of whole leading-dim slices through two halves of a small
+// staging buffer: the PCIe copy of chunk k+1 runs on an internal copy stream while the relayout
+// kernel of chunk k runs on the caller's stream, and the staging footprint is two chunks instead of
+// the whole span.  One copy stream and four events per device, created on first use.
+namespace tsb {
+namespace {
+
+constexpr int64_t kChunkBytes = 8ll << 20;
+constexpr int64_t kMaxChunkBytes = 128ll << 20;   // a leading slice larger than this is not worth two copies of
+constexpr int kMaxDevices = 64;
+
+struct CopyPipe {
+  std::mutex mu;
+  bool ready = false, failed = false;
+  cudaStream_t copy = nullptr;
+  cudaEvent_t copied[2] = {nullptr, nullptr}, relaid[2] = {nullptr, nullptr};
+};
+CopyPipe g_pipes[kMaxDevices];
+
+CopyPipe* pipe_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  CopyPipe* p = &g_pipes[dev];
+  std::lock_guard<std::mutex> lock(p->mu);
+  if (!p->ready && !p->failed) {
+    bool ok = cudaStreamCreateWithFlags(&p->copy, cudaStreamNonBlocking) == cudaSuccess;
+    for (int i = 0; i < 2 && ok; ++i)
+      ok = cudaEventCreateWithFlags(&p->copied[i], cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&p->relaid[i], cudaEventDisableTiming) == cudaSuccess;
+    p->ready = ok;
+    p->failed = !ok;
+  }
+  return p->ready ? p : nullptr;
+}
+
+struct ChunkPlan {
+  bool chunked = false;
+  int dev_dim = -1;           // the device dim that walks host dim 0
+  int64_t rows_per_chunk = 0, row_bytes = 0, rest_bytes = 0;
+};
+
+// Whether (and how) a copy can be cut along host dim 0: slices must be disjoint, ascending spans of
+// host memory, and host dim 0 must be one whole device dim (not the stick dim).
+ChunkPlan plan_chunks(int eb, const int64_t* hsize, const int64_t* hstr, int rank, const int32_t* dim_map,
+                      int ndev, int64_t staging_bytes) {
+  ChunkPlan c;
+  if (rank < 2 || hsize[0] < 2) return c;
+  int count = 0;
+  for (int d = 0; d < ndev; ++d)
+    if (dim_map[d] == 0) { c.dev_dim = d; ++count; }
+  if (count != 1) return c;
+  const int64_t rest = host_span_elems(hsize + 1, hstr + 1, rank - 1);
+  if (rest <= 0 || hstr[0] < rest) return c;
+  c.row_bytes = hstr[0] * eb;
+  c.rest_bytes = rest * eb;
+  // a chunk is about kChunkBytes, at least one leading slice, and fits half the staging block
+  const int64_t half = (staging_bytes / 2) & ~(int64_t)255;
+  const int64_t target = std::min(half, std::max(kChunkBytes, c.rest_bytes));
+  if (target < c.rest_bytes) return c;
+  c.rows_per_chunk = 1 + (target - c.rest_bytes) / c.row_bytes;
+  c.chunked = c.rows_per_chunk < hsize[0];
+  return c;
+}
+
+}  // namespace
+}  // namespace tsb
+
+extern "C" int64_t ts_copy_staging_bytes(int elem_bytes, const int64_t* host_size,
+                                         const int64_t* host_strides, int rank) {
+  const int64_t span = ts_host_span_bytes(elem_bytes, host_size, host_strides, rank);
+  if (span < 0) return span;
+  int64_t chunk = kChunkBytes;
+  if (rank >= 2 && host_size[0] >= 2) {   // room for at least one leading slice per half, within reason
+    const int64_t rest = host_span_elems(host_size + 1, host_strides + 1, rank - 1) * elem_bytes;
+    if (rest > chunk && rest <= kMaxChunkBytes) chunk = (rest + 255) & ~(int64_t)255;
+  }
+  return std::min<int64_t>((span + 255) & ~(int64_t)255, 2 * chunk);
+}
+
+extern "C" int ts_copy_host_to_sticks_pipelined(const void* host, void* staging, int64_t staging_bytes,
+                                                void* sticks, int elem_bytes, const int64_t* host_size,
+                                                const int64_t* host_strides, int rank,
+                                                const int64_t* device_size, const int64_t* device_strides,
+                                                const int32_t* dim_map, int ndev, void* stream) {
+  const int64_t bytes = ts_host_span_bytes(elem_bytes, host_size, host_strides, rank);
+  if (bytes < 0) return (int)bytes;
+  if (rank < 1 || rank > kMaxDims || ndev < 1 || ndev > kMaxDims || !device_size || !device_strides || !dim_map)
+    return TS_ERR_INVALID;
+  if (bytes > 0 && (!host || !staging || !sticks)) return TS_ERR_INVALID;
+  const ChunkPlan c = plan_chunks(elem_bytes, host_size, host_strides, rank, dim_map, ndev, staging_bytes);
+  CopyPipe* pipe = c.chunked ? pipe_for_current_device() : nullptr;
+  if (!pipe) {
+    if (staging_bytes < bytes) return TS_ERR_TOO_LARGE;
+    return ts_copy_host_to_sticks(host, staging, sticks, elem_bytes, host_size, host_strides, rank,
+                                  device_size, device_strides, dim_map, ndev, stream);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  std::lock_guard<std::mutex> lock(pipe->mu);
+  const int64_t half = (staging_bytes / 2) & ~(int64_t)255;
+  int64_t hs[kMaxDims], ds[kMaxDims];
+  for (int i = 0; i < rank; ++i) hs[i] = host_size[i];
+  for (int i = 0; i < ndev; ++i) ds[i] = device_size[i];
+  // the copy stream may not touch the staging block before work already queued on `stream` is done with it
+  if (cudaEventRecord(pipe->relaid[0], st) != cudaSuccess ||
+      cudaStreamWaitEvent(pipe->copy, pipe->relaid[0], 0) != cudaSuccess) return TS_ERR_CUDA;
+  int k = 0;
+  for (int64_t r0 = 0; r0 < host_size[0]; r0 += c.rows_per_chunk, ++k) {
+    const int slot = k & 1;
+    const int64_t rows = std::min(c.rows_per_chunk, host_size[0] - r0);
+    const int64_t span = (rows - 1) * c.row_bytes + c.rest_bytes;
+    char* stage = (char*)staging + slot * half;
+    if (k >= 2 && cudaStreamWaitEvent(pipe->copy, pipe->relaid[slot], 0) != cudaSuccess) return TS_ERR_CUDA;
+    if (cudaMemcpyAsync(stage, (const char*)host + r0 * c.row_bytes, (size_t)span, cudaMemcpyHostToDevice,
+                        pipe->copy) != cudaSuccess ||
+        cudaEventRecord(pipe->copied[slot], pipe->copy) != cudaSuccess ||
+        cudaStreamWaitEvent(st, pipe->copied[slot], 0) != cudaSuccess)
+      return TS_ERR_CUDA;
+    hs[0] = rows;
+    ds[c.dev_dim] = rows;
+    const int rc = ts_relayout_to_sticks(stage, (char*)sticks + r0 * device_strides[c.dev_dim] * elem_bytes,
+                                         elem_bytes, hs, host_strides, rank, ds, device_strides, dim_map, ndev,
+                                         stream);
+    if (rc != TS_OK) return rc;
+    if (cudaEventRecord(pipe->relaid[slot], st) != cudaSuccess) return TS_ERR_CUDA;
+  }
+  return TS_OK;
+}
+
+extern "C" int ts_copy_sticks_to_host_pipelined(const void* sticks, void* staging, int64_t staging_bytes,
+                                                void* host, int elem_bytes, const int64_t* host_size,
+                                                const int64_t* host_strides, int rank,
+                                                const int64_t* device_size, const int64_t* device_strides,
+                                                const int32_t* dim_map, int ndev, void* stream) {
+  const int64_t bytes = ts_host_span_bytes(elem_bytes, host_size, host_strides, rank);
+  if (bytes < 0) return (int)bytes;
+  if (bytes == 0) return TS_OK;
+  if (rank < 1 || rank > kMaxDims || ndev < 1 || ndev > kMaxDims || !device_size || !device_strides || !dim_map)
+    return TS_ERR_INVALID;
+  if (!host || !staging || !sticks) return TS_ERR_INVALID;
+  ChunkPlan c = plan_chunks(elem_bytes, host_size, host_strides, rank, dim_map, ndev, staging_bytes);
+  // a host tensor with gaps keeps its gap bytes only on the single-shot path (whose caller
+  // preloads the staging image with them)
+  int64_t dense = elem_bytes;
+  for (int i = 0; i < rank; ++i) dense *= host_size[i];
+  if (dense != bytes) c.chunked = false;
+  CopyPipe* pipe = c.chunked ? pipe_for_current_device() : nullptr;
+  if (!pipe) {
+    if (staging_bytes < bytes) return TS_ERR_TOO_LARGE;
+    return ts_copy_sticks_to_host(sticks, staging, host, elem_bytes, host_size, host_strides, rank, device_size,
+                                  device_strides, dim_map, ndev, stream);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  std::lock_guard<std::mutex> lock(pipe->mu);
+  const int64_t half = (staging_bytes / 2) & ~(int64_t)255;
+  int64_t hs[kMaxDims], ds[kMaxDims];
+  for (int i = 0; i < rank; ++i) hs[i] = host_size[i];
+  for (int i = 0; i < ndev; ++i) ds[i] = device_size[i];
+  int k = 0;
+  for (int64_t r0 = 0; r0 < host_size[0]; r0 += c.rows_per_chunk, ++k) {
+    const int slot = k & 1;
+    const int64_t rows = std::min(c.rows_per_chunk, host_size[0] - r0);
+    const int64_t span = (rows - 1) * c.row_bytes + c.rest_bytes;
+    char* stage = (char*)staging + slot * half;
+    // the slot's previous contents must have left for the host
+    if (k >= 2 && cudaStreamWaitEvent(st, pipe->copied[slot], 0) != cudaSuccess) return TS_ERR_CUDA;
+    hs[0] = rows;
+    ds[c.dev_dim] = rows;
+    const int rc = ts_relayout_from_sticks((const char*)sticks + r0 * device_strides[c.dev_dim] * elem_bytes, stage,
+                                           elem_bytes, hs, host_strides, rank, ds, device_strides, dim_map, ndev,
+                                           stream);
+    if (rc != TS_OK) return rc;
+    if (cudaEventRecord(pipe->relaid[slot], st) != cudaSuccess ||
+        cudaStreamWaitEvent(pipe->copy, pipe->relaid[slot], 0) != cudaSuccess ||
+        cudaMemcpyAsync((char*)host + r0 * c.row_bytes, stage, (size_t)span, cudaMemcpyDeviceToHost,
+                        pipe->copy) != cudaSuccess ||
+        cudaEventRecord(pipe->copied[slot], pipe->copy) != cudaSuccess)
+      return TS_ERR_CUDA;
+  }
+  // synchronising `stream` must cover the copies
+  for (int slot = 0; slot < 2 && slot < k; ++slot)
+    if (cudaStreamWaitEvent(st, pipe->copied[slot], 0) != cudaSuccess) return TS_ERR_CUDA;
   return TS_OK;
 }
 

@@ -51,6 +51,11 @@ SIGNATURES = {
     "ts_host_span_bytes": (ctypes.c_int64, [ctypes.c_int, c_i64p, c_i64p, ctypes.c_int]),
     "ts_copy_host_to_sticks": (ctypes.c_int, _COPY_SIG),
     "ts_copy_sticks_to_host": (ctypes.c_int, _COPY_SIG),
+    "ts_copy_staging_bytes": (ctypes.c_int64, [ctypes.c_int, c_i64p, c_i64p, ctypes.c_int]),
+    "ts_copy_host_to_sticks_pipelined": (ctypes.c_int, [vp, vp, ctypes.c_int64, vp, ctypes.c_int, c_i64p, c_i64p,
+                                                        ctypes.c_int, c_i64p, c_i64p, c_i32p, ctypes.c_int, vp]),
+    "ts_copy_sticks_to_host_pipelined": (ctypes.c_int, [vp, vp, ctypes.c_int64, vp, ctypes.c_int, c_i64p, c_i64p,
+                                                        ctypes.c_int, c_i64p, c_i64p, c_i32p, ctypes.c_int, vp]),
     "ts_transpose_tiles": (ctypes.c_int, [vp, c_i64p, ctypes.c_int, c_i64p, ctypes.c_int64, vp, c_i64p,
                                           ctypes.c_int, c_i64p, ctypes.c_int64, c_i64p, ctypes.c_int,
                                           ctypes.c_int, vp]),

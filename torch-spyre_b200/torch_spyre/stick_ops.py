@@ -108,23 +108,37 @@ def host_span(t: torch.Tensor) -> int:
     return int(n)
 
 
+def _staging_for(t: torch.Tensor, staging: Optional[torch.Tensor], device) -> torch.Tensor:
+    """A staging block for the pipelined copies: the caller's if it is large enough for two
+    chunks, else a fresh one of the size the library asks for."""
+    shape = tuple(t.shape) if t.dim() else (1,)
+    strides = tuple(t.stride()) if t.dim() else (1,)
+    want = int(_abi.lib().ts_copy_staging_bytes(t.element_size(), _abi.i64(shape), _abi.i64(strides), len(shape)))
+    if want < 0:
+        _abi.check(want, "ts_copy_staging_bytes")
+    if staging is not None and staging.numel() * staging.element_size() >= want:
+        return staging
+    return torch.empty(max(want, 256), dtype=torch.uint8, device=device)
+
+
 def copy_host_to_sticks(host: torch.Tensor, out: Optional[StickTensor] = None,
                         staging: Optional[torch.Tensor] = None) -> StickTensor:
     """Host tensor (any non-negative strides; pinned memory makes the copy asynchronous)
-    -> stick image on the current CUDA device."""
+    -> stick image on the current CUDA device, in chunks whose PCIe copies overlap the relayout
+    kernels.  A tensor that cannot be cut into chunks goes in one piece."""
     shape = tuple(host.shape) if host.dim() else (1,)
     strides = tuple(host.stride()) if host.dim() else (1,)
     lay = SpyreTensorLayout(list(shape), host.dtype)
     if out is None:
         out = empty(shape, host.dtype)
-    span = host_span(host)
-    if staging is None or staging.numel() * staging.element_size() < span:
-        staging = torch.empty(max(span, 16), dtype=torch.uint8, device=out.image.device)
+    staging = _staging_for(host, staging, out.image.device)
+    nbytes = staging.numel() * staging.element_size()
     ds, dst, dm, nd = _layout_args(lay)
-    rc = _abi.lib().ts_copy_host_to_sticks(host.data_ptr(), staging.data_ptr(), out.ptr(),
-                                           host.element_size(), _abi.i64(shape),
-                                           _abi.i64(strides), len(shape), ds, dst, dm, nd,
-                                           _stream())
+    args = (host.element_size(), _abi.i64(shape), _abi.i64(strides), len(shape), ds, dst, dm, nd, _stream())
+    rc = _abi.lib().ts_copy_host_to_sticks_pipelined(host.data_ptr(), staging.data_ptr(), nbytes, out.ptr(), *args)
+    if rc == _abi.TS_ERR_TOO_LARGE:      # not cuttable: the whole span through one staging block
+        staging = torch.empty(max(host_span(host), 16), dtype=torch.uint8, device=out.image.device)
+        rc = _abi.lib().ts_copy_host_to_sticks(host.data_ptr(), staging.data_ptr(), out.ptr(), *args)
     _abi.check(rc, "ts_copy_host_to_sticks")
     return out
 
@@ -133,14 +147,14 @@ def copy_sticks_to_host(st: StickTensor, host: torch.Tensor,
                         staging: Optional[torch.Tensor] = None) -> torch.Tensor:
     shape = st.shape if st.shape else (1,)
     strides = tuple(host.stride()) if host.dim() else (1,)
-    span = host_span(host)
-    if staging is None or staging.numel() * staging.element_size() < span:
-        staging = torch.empty(max(span, 16), dtype=torch.uint8, device=st.image.device)
+    staging = _staging_for(host, staging, st.image.device)
+    nbytes = staging.numel() * staging.element_size()
     ds, dst, dm, nd = _layout_args(st.layout)
-    rc = _abi.lib().ts_copy_sticks_to_host(st.ptr(), staging.data_ptr(), host.data_ptr(),
-                                           host.element_size(), _abi.i64(shape),
-                                           _abi.i64(strides), len(shape), ds, dst, dm, nd,
-                                           _stream())
+    args = (host.element_size(), _abi.i64(shape), _abi.i64(strides), len(shape), ds, dst, dm, nd, _stream())
+    rc = _abi.lib().ts_copy_sticks_to_host_pipelined(st.ptr(), staging.data_ptr(), nbytes, host.data_ptr(), *args)
+    if rc == _abi.TS_ERR_TOO_LARGE:
+        staging = torch.empty(max(host_span(host), 16), dtype=torch.uint8, device=st.image.device)
+        rc = _abi.lib().ts_copy_sticks_to_host(st.ptr(), staging.data_ptr(), host.data_ptr(), *args)
     _abi.check(rc, "ts_copy_sticks_to_host")
     return host
 
