@@ -42,6 +42,15 @@ constexpr long long kAttnWaitLimit = 4000000000ll;  // ~2 s of SM clocks
 constexpr long long kAttnDrainLimit = 200000ll;   // ~0.1 ms: far longer than a TMA copy is in flight
 
 __device__ int g_attn_error;  // sticky: set when a bounded wait gave up
+#ifdef TSB_TUNING
+// experiment counters of the tuning build (two-tile kernel): cycles group A's MMA thread waited for
+// K [0], for S to be taken [1], for V [2], for P [3], its loop [4]; cycles the first softmax warp of
+// group A waited for S [5], for the previous P V [6], its loop [7]
+__device__ unsigned long long g_attn_prof[8];
+#define ATTN_PROF(idx, stmt) { const long long t0__ = clock64(); stmt; prof[idx] += clock64() - t0__; }
+#else
+#define ATTN_PROF(idx, stmt) { stmt; }
+#endif
 
 struct AttnParams {
   __half* out;
@@ -575,10 +584,17 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
         return ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag, kAttnWaitLimit);
       };
       // S_x = Q_x K^T for the next key tile, then its ring slot is released on this thread's behalf
+#ifdef TSB_TUNING
+      long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      const long long prof_start = clock64();
+#endif
       auto issue_scores = [&](bool has_work) -> bool {
-        if (!wait(&bars->kv_full[kpos.slot], kpos.parity)) return false;
+        bool w_ok;
+        ATTN_PROF(0, w_ok = wait(&bars->kv_full[kpos.slot], kpos.parity))
+        if (!w_ok) return false;
         if (has_work) {
-          if (!wait(&bars->s_empty[x], (gs & 1) ^ 1)) return false;   // the group has taken S_x
+          ATTN_PROF(1, w_ok = wait(&bars->s_empty[x], (gs & 1) ^ 1))   // the group has taken S_x
+          if (!w_ok) return false;
           ptx::tc_fence_after_sync();
           const uint32_t kb = skv + kpos.slot * kTileBytes;
 #pragma unroll
@@ -611,9 +627,12 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (!issue_scores(j + 1 < nx)) { ok = false; break; }
             if (j + 2 == nx) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
           }
-          if (!wait(&bars->kv_full[vpos.slot], vpos.parity)) { ok = false; break; }
+          bool w_ok;
+          ATTN_PROF(2, w_ok = wait(&bars->kv_full[vpos.slot], vpos.parity))
+          if (!w_ok) { ok = false; break; }
           if (j < nx) {
-            if (!wait(&bars->p_full[x], gp & 1)) { ok = false; break; }
+            ATTN_PROF(3, w_ok = wait(&bars->p_full[x], gp & 1))
+            if (!w_ok) { ok = false; break; }
             ptx::tc_fence_after_sync();
             const uint32_t vb = skv + vpos.slot * kTileBytes;
 #pragma unroll
@@ -630,6 +649,12 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
           vpos.advance();
         }
       }
+#ifdef TSB_TUNING
+      if (x == 0) {
+        for (int i = 0; i < 4; ++i) atomicAdd(&g_attn_prof[i], (unsigned long long)prof[i]);
+        atomicAdd(&g_attn_prof[4], (unsigned long long)(clock64() - prof_start));
+      }
+#endif
     }
     __syncwarp();
   } else {
@@ -647,13 +672,19 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
     };
     uint32_t g = 0;   // key tiles this group has processed (phases of s_full / p_full / pv_done)
     bool ok = true;
+#ifdef TSB_TUNING
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_start = clock64();
+#endif
     for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
       uint32_t pr, b, h;
       if (!decode_pair_item(P, item, pr, b, h)) continue;
       const uint32_t qt = 2 * pr + x, n = qt + 1;
       float m = -1e30f, l = 0.f;
       for (uint32_t j = 0; j < n; ++j, ++g) {
-        if (!warp_wait(&bars->s_full[x], g & 1)) { ok = false; break; }
+        bool w_ok;
+        ATTN_PROF(5, w_ok = warp_wait(&bars->s_full[x], g & 1))
+        if (!w_ok) { ok = false; break; }
         ptx::tc_fence_after_sync();
         uint32_t r[4][32];
 #pragma unroll
@@ -680,7 +711,11 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
                                      fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
         // The previous P V of this group has read the P tile about to be overwritten and is the
         // last writer of O, which a rescale touches; it was issued a whole tile ago.
-        if (j > 0 && !warp_wait(&bars->pv_done[x], (g - 1) & 1)) { ok = false; break; }
+        if (j > 0) {
+          bool w_ok2;
+          ATTN_PROF(6, w_ok2 = warp_wait(&bars->pv_done[x], (g - 1) & 1))
+          if (!w_ok2) { ok = false; break; }
+        }
         if (j == 0) {
           m = tile_max;
         } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
@@ -754,6 +789,13 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
       }
       ptx::tc_fence_before_sync();
     }
+#ifdef TSB_TUNING
+    if (warp == 2 && lane == 0) {
+      atomicAdd(&g_attn_prof[5], (unsigned long long)prof[5]);
+      atomicAdd(&g_attn_prof[6], (unsigned long long)prof[6]);
+      atomicAdd(&g_attn_prof[7], (unsigned long long)(clock64() - prof_start));
+    }
+#endif
   }
 
   ptx::tc_fence_before_sync();
@@ -838,3 +880,13 @@ extern "C" int ts_attention_error_state(void) {
   }
   return v;
 }
+
+#ifdef TSB_TUNING
+// tuning build only: reads and clears the experiment counters
+extern "C" int ts_attn_prof(unsigned long long* out8) {
+  if (cudaMemcpyFromSymbol(out8, g_attn_prof, sizeof(unsigned long long) * 8) != cudaSuccess) return TS_ERR_CUDA;
+  unsigned long long zero[8] = {0};
+  cudaMemcpyToSymbol(g_attn_prof, zero, sizeof(zero));
+  return TS_OK;
+}
+#endif
