@@ -15,10 +15,14 @@ DEV = "spyre"
 SEED = 0xAFFE
 
 
-@pytest.fixture(autouse=True)
-def _fresh(cuda):
+@pytest.fixture(autouse=True, params=["inductor", "plan"])
+def _fresh(cuda, request):
+    """Every case runs through both compilation routes: Inductor itself with the spyre scheduling
+    and wrapper classes, and the FX-level plan it falls back to."""
     torch._dynamo.reset()
+    saved, compiler.backend_mode = compiler.backend_mode, request.param
     yield
+    compiler.backend_mode = saved
 
 
 def rnd(*shape, seed=SEED, positive=False):
@@ -95,7 +99,23 @@ def test_layer_norm_graph():
 def test_config2_compiles_to_one_fused_kernel():
     x, a, b = math_ref.fused_inputs(256, 2048)
     plan = check(lambda x, a, b: torch.exp(x * a + b).sum(-1), x, a, b)
-    assert len(plan.kernel_specs) == 1 and plan.fused_nodes == 4
+    assert plan.route == compiler.backend_mode        # Inductor takes this graph without falling back
+    assert len(plan.kernel_specs) == 1
     spec = plan.kernel_specs[0]
     assert spec.is_reduction and spec.dimensions == [256, 2048]
     assert [i[0] for i in spec.op_info["insns"]] == ["LOAD", "MUL", "ADD", "EXP"]
+
+
+def test_routes_and_fallback():
+    """A graph whose loop bodies the spyre scheduling cannot express (a transposed read) is
+    compiled by the FX-level plan instead, with the same result."""
+    if compiler.backend_mode != "inductor":
+        pytest.skip("only meaningful when Inductor is tried first")
+    check(lambda x, y: torch.relu(x.t() + y), rnd(64, 128), rnd(128, 64, seed=1))
+    assert compiler.last_compiled[-1].route == "plan" and compiler.last_routes[-1].startswith("plan")
+    check(lambda x, y: torch.relu(x + y) * 2.0, rnd(64, 128), rnd(64, 128, seed=1))
+    assert compiler.last_compiled[-1].route == "inductor" and compiler.last_routes[-1] == "inductor"
+    check(lambda x: (x * 2.0 + 1.0).mean(-1), rnd(67, 256))                  # mean: one kernel, scale folded in
+    rec = compiler.last_compiled[-1]
+    assert rec.route == "inductor" and len(rec.kernel_specs) == 1
+    assert abs(rec.kernel_specs[0].op_info["reduce_scale"] - 1 / 256) < 1e-9

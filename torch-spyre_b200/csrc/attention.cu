@@ -58,6 +58,9 @@ struct AttnParams {
   int64_t stick_stride;   // elements between stick columns of the packed images
   float scale_log2;       // softmax scale * log2(e)
   uint32_t heads_per_round;   // two-tile kernel: (batch, head) slices in flight together; 0 = linear order
+#ifdef TSB_TUNING
+  int tune_mode;              // experiment: 1 = MMAs without the softmax (its warps leave at once)
+#endif
 };
 
 struct AttnBars {
@@ -397,36 +400,27 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // and P tile.  While one group is in its exponentials the other one's waits and the MMAs of
 // both run underneath, which is what the one-tile kernel above cannot do.
 //   tensor memory: S_A | S_B | O_A | O_B (4 x 128 columns)
-//   shared memory: Q_A Q_B | K / V ring (3 slots) | P_A P_B
+//   shared memory: Q_A Q_B | K (2 buffers) | V (1 buffer) | P_A P_B
 // Each group has its own MMA-issuing thread (warps 1 and 10), so that neither waits on the
 // other's softmax: S_x(t+1) is issued as soon as group x has taken S_x(t) into registers, and
 // P_x(t) V(t) as soon as P_x(t) has arrived.  K / V / Q buffers are released by both threads.
-// K and V tiles travel through one ring in the order K0 V0 K1 V1 ...: a K tile is released as
-// soon as both score products of its step have run, early in the step, so the slot it leaves takes
-// V of the next step while the current step's softmax is still working, and the slot V(t) leaves
-// takes K(t+2).  With separate K and V buffers the same shared memory holds only one V tile,
-// whose reload (a DRAM / L2 round trip) then sits between every two steps.
+// K tiles alternate between two buffers and V tiles use one, and the two streams are loaded by two
+// different threads of the TMA warp, each waiting only for its own buffers: a K buffer is
+// released as soon as both score products of its key tile have run (early in the step before the
+// one that needs the next tile in it), so K loads run two steps ahead; the V buffer is released
+// when both P V products of a step are done and its reload has the next step's softmax to hide
+// behind.  (One thread loading K and V in turn would hold every K load back behind the V buffer.)
 constexpr int kPairAttnThreads = 352;   // TMA warp, MMA warp A, 8 softmax warps, MMA warp B
-constexpr int kKvSlots = 3;
-constexpr int kPairSmemTiles = 4 + kKvSlots;   // Q_A Q_B | ring | P_A P_B
+constexpr int kPairSmemTiles = 7;       // Q_A Q_B K0 K1 V P_A P_B
 constexpr int kPairAttnSmem = kPairSmemTiles * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 struct PairAttnBars {
-  uint64_t q_full, q_empty, kv_full[kKvSlots], kv_empty[kKvSlots], s_full[2], s_empty[2], p_full[2],
+  uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_empty[2], p_full[2],
       pv_done[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 static_assert(sizeof(PairAttnBars) <= 256, "barrier block outgrew its shared-memory reservation");
-
-// Position in the K / V ring of the load with running number n (K of key tile t is load 2t, V
-// is load 2t + 1): slot and the parity of the slot's current use.
-struct RingPos {
-  uint32_t slot, parity;
-  __device__ __forceinline__ void advance() {
-    if (++slot == (uint32_t)kKvSlots) { slot = 0; parity ^= 1; }
-  }
-};
 
 // Work order of the two-tile kernel.  The grid is heads_per_round x (pairs per head) CTAs; in
 // round r CTA c works on (batch, head) slice r * heads_per_round + c / pairs and on tile pair
@@ -489,7 +483,7 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw);
-  const uint32_t sq = base, skv = sq + 2 * kTileBytes, sp = skv + kKvSlots * kTileBytes;
+  const uint32_t sq = base, sk = sq + 2 * kTileBytes, sv = sk + 2 * kTileBytes, sp = sv + kTileBytes;
   uint8_t* gen_p = gen_base + (sp - base);
   PairAttnBars* bars = reinterpret_cast<PairAttnBars*>(gen_base + kPairSmemTiles * kTileBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -499,11 +493,11 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
   if (threadIdx.x == 0) {
     ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 2);        // released by both MMA threads
-    for (int i = 0; i < kKvSlots; ++i) {
-      ptx::mbar_init(ptx::smem_u32(&bars->kv_full[i]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->kv_empty[i]), 2);    // released by both MMA threads
-    }
+    ptx::mbar_init(ptx::smem_u32(&bars->v_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->v_empty), 2);          // released by both MMA threads
     for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->k_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->k_empty[i]), 2);
       ptx::mbar_init(ptx::smem_u32(&bars->s_full[i]), 1);
       ptx::mbar_init(ptx::smem_u32(&bars->s_empty[i]), 4);   // one arrival per softmax warp of the group
       ptx::mbar_init(ptx::smem_u32(&bars->p_full[i]), 4);
@@ -527,8 +521,8 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t item_n = 0, loads = 0;   // loads: K / V tiles issued so far
-      RingPos pos{0, 0};
+      // lane 0: the query tiles and the K stream
+      uint32_t kt = 0, item_n = 0;   // kt: key tiles loaded so far (K buffer and phase)
       bool ok = true;
       for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
         uint32_t pr, b, h;
@@ -544,30 +538,44 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
           ptx::tma_load_5d(sq + x * kTileBytes + kBlockBytes, &map_q, qf, 0, qrow, (int)b, (int)(2 * h + 1), 0);
         }
         const uint32_t n = 2 * pr + 2;
-        for (uint32_t j = 0; ok && j < n; ++j) {
-#pragma unroll
-          for (int part = 0; part < 2; ++part, ++loads, pos.advance()) {   // K of the tile, then V
-            if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->kv_empty[pos.slot]), pos.parity ^ 1, abort_flag,
-                                        kAttnWaitLimit)) { ok = false; break; }
-            const uint32_t f = ptx::smem_u32(&bars->kv_full[pos.slot]);
-            const uint32_t dst = skv + pos.slot * kTileBytes;
-            const CUtensorMap* map = part == 0 ? &map_k : &map_v;
-            ptx::mbar_arrive_expect_tx(f, kTileBytes);
-            ptx::tma_load_5d(dst, map, f, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
-            ptx::tma_load_5d(dst + kBlockBytes, map, f, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
-          }
+        for (uint32_t j = 0; j < n; ++j, ++kt) {
+          const uint32_t st = kt & 1, ph = (kt >> 1) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_empty[st]), ph ^ 1, abort_flag,
+                                      kAttnWaitLimit)) { ok = false; break; }
+          const uint32_t kf = ptx::smem_u32(&bars->k_full[st]);
+          ptx::mbar_arrive_expect_tx(kf, kTileBytes);
+          ptx::tma_load_5d(sk + st * kTileBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sk + st * kTileBytes + kBlockBytes, &map_k, kf, 0, (int)(j * kTile), (int)b,
+                           (int)(2 * h + 1), 0);
         }
       }
       if (*abort_flag) {   // after an abort only: let copies in flight land before the CTA exits
-        // the last kKvSlots loads, newest first: walk the ring backwards from `pos`
-        RingPos back = pos;
-        for (uint32_t k = 0; k < (loads < (uint32_t)kKvSlots ? loads : (uint32_t)kKvSlots); ++k) {
-          if (back.slot == 0) { back.slot = kKvSlots - 1; back.parity ^= 1; } else { --back.slot; }
-          ptx::mbar_wait_drain(ptx::smem_u32(&bars->kv_full[back.slot]), back.parity, kAttnDrainLimit);
+        for (uint32_t k = 0; k < (kt < 2u ? kt : 2u); ++k) {
+          const uint32_t t = kt - 1 - k;
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[t & 1]), (t >> 1) & 1, kAttnDrainLimit);
         }
         if (item_n > 0)
           ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
       }
+    } else if (lane == 1) {
+      // lane 1: the V stream
+      uint32_t kt = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        uint32_t pr, b, h;
+        if (!decode_pair_item(P, item, pr, b, h)) continue;
+        const uint32_t n = 2 * pr + 2;
+        for (uint32_t j = 0; j < n; ++j, ++kt) {
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_empty), (kt & 1) ^ 1, abort_flag,
+                                      kAttnWaitLimit)) { ok = false; break; }
+          const uint32_t vf = ptx::smem_u32(&bars->v_full);
+          ptx::mbar_arrive_expect_tx(vf, kTileBytes);
+          ptx::tma_load_5d(sv, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sv + kBlockBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
+        }
+      }
+      if (*abort_flag && kt > 0)
+        ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full), (kt - 1) & 1, kAttnDrainLimit);
     }
     __syncwarp();
   } else if (warp == 1 || warp == 10) {
@@ -577,26 +585,20 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
       const uint32_t idesc_s = ptx::idesc_f16_f32(kTile, kTile, 0, 0);
       const uint32_t idesc_pv = ptx::idesc_f16_f32(kTile, kTile, 0, 1);
       const uint32_t qb = sq + x * kTileBytes, pb = sp + x * kTileBytes;
-      uint32_t item_n = 0;           // items done
+      uint32_t kt = 0, item_n = 0;   // key tiles of finished items; items done
       uint32_t gs = 0, gp = 0;       // this group's score tiles / P V products issued so far
-      RingPos kpos{0, 0}, vpos{1, 0};   // ring positions of the next K tile and the next V tile to consume
-      auto wait = [&](uint64_t* bar, uint32_t parity) {
-        return ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag, kAttnWaitLimit);
-      };
-      // S_x = Q_x K^T for the next key tile, then its ring slot is released on this thread's behalf
 #ifdef TSB_TUNING
       long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       const long long prof_start = clock64();
 #endif
-      auto issue_scores = [&](bool has_work) -> bool {
-        bool w_ok;
-        ATTN_PROF(0, w_ok = wait(&bars->kv_full[kpos.slot], kpos.parity))
-        if (!w_ok) return false;
+      auto ready = [&](uint64_t* bar, uint32_t parity) { return ptx::mbar_test_wait(ptx::smem_u32(bar), parity); };
+      // S_x = Q_x K_t^T for global key tile t (the group uses it: has_work), then the K buffer is
+      // released on this thread's behalf.  Only called once the operands are there.
+      auto issue_scores = [&](uint32_t t, bool has_work) {
+        const uint32_t ks = t & 1;
         if (has_work) {
-          ATTN_PROF(1, w_ok = wait(&bars->s_empty[x], (gs & 1) ^ 1))   // the group has taken S_x
-          if (!w_ok) return false;
           ptx::tc_fence_after_sync();
-          const uint32_t kb = skv + kpos.slot * kTileBytes;
+          const uint32_t kb = sk + ks * kTileBytes;
 #pragma unroll
           for (int k16 = 0; k16 < kTile / 16; ++k16) {
             const uint32_t off = (k16 >> 2) * kBlockBytes + (k16 & 3) * 32;
@@ -606,10 +608,13 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
           ptx::umma_commit(ptx::smem_u32(&bars->s_full[x]));
           ++gs;
         }
-        ptx::umma_commit(ptx::smem_u32(&bars->kv_empty[kpos.slot]));
-        kpos.advance();
-        kpos.advance();
-        return true;
+        ptx::umma_commit(ptx::smem_u32(&bars->k_empty[ks]));
+      };
+      auto scores_ready = [&](uint32_t t, bool has_work) {
+#ifdef TSB_TUNING
+        if (P.tune_mode == 1) return ready(&bars->k_full[t & 1], (t >> 1) & 1);
+#endif
+        return ready(&bars->k_full[t & 1], (t >> 1) & 1) && (!has_work || ready(&bars->s_empty[x], (gs & 1) ^ 1));
       };
       bool ok = true;
       for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
@@ -617,37 +622,61 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (!decode_pair_item(P, item, pr, b, h)) continue;
         const uint32_t n = 2 * pr + 2;          // key tiles loaded for the item
         const uint32_t nx = n - 1 + x;          // key tiles this group uses (A stops one short)
-        if (!wait(&bars->q_full, item_n & 1)) break;
-        ptx::tc_fence_after_sync();
-        if (!issue_scores(true)) break;
-        if (nx == 1) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
-        for (uint32_t j = 0; j < n; ++j) {
-          // next tile's scores first (a tile this group does not use is still waited for and released)
-          if (j + 1 < n) {
-            if (!issue_scores(j + 1 < nx)) { ok = false; break; }
-            if (j + 2 == nx) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), item_n & 1, abort_flag, kAttnWaitLimit)) break;
+        // Per key tile j two things are issued: the scores of tile j + 1 and the P V product of tile
+        // j, whichever has its operands first (a tile this group does not use is still waited for
+        // and released).  The first tile's scores go before the loop.
+        uint32_t next_s = 0;   // next key tile of the item whose scores are to be issued
+        const long long t_item = clock64();
+#ifdef TSB_TUNING
+        prof[7] = t_item;
+#endif
+        for (uint32_t j = 0; ok && j < n;) {
+          bool progress = false;
+          if (next_s < n && next_s <= j + 1 && scores_ready(kt + next_s, next_s < nx)) {
+            issue_scores(kt + next_s, next_s < nx);
+            ++next_s;
+            if (next_s == nx) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));   // Q_x is not read again
+            progress = true;
           }
-          bool w_ok;
-          ATTN_PROF(2, w_ok = wait(&bars->kv_full[vpos.slot], vpos.parity))
-          if (!w_ok) { ok = false; break; }
-          if (j < nx) {
-            ATTN_PROF(3, w_ok = wait(&bars->p_full[x], gp & 1))
-            if (!w_ok) { ok = false; break; }
-            ptx::tc_fence_after_sync();
-            const uint32_t vb = skv + vpos.slot * kTileBytes;
+          bool p_ready = j >= nx || ready(&bars->p_full[x], gp & 1);
+#ifdef TSB_TUNING
+          if (P.tune_mode == 1) p_ready = true;
+#endif
+          if (next_s > j && ready(&bars->v_full, (kt + j) & 1) && p_ready) {
+            if (j < nx) {
+              ptx::tc_fence_after_sync();
 #pragma unroll
-            for (int k16 = 0; k16 < kTile / 16; ++k16) {
-              const uint64_t da = ptx::smem_desc_sw128(pb + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
-              const uint64_t db = ptx::smem_desc_sw128(vb + k16 * 2048, kBlockBytes, 1024);
-              ptx::umma_f16(tmem_base + (2 + x) * kTile, da, db, idesc_pv, (j ? 1u : 0u) | (uint32_t)k16);
+              for (int k16 = 0; k16 < kTile / 16; ++k16) {
+                const uint64_t da = ptx::smem_desc_sw128(pb + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
+                const uint64_t db = ptx::smem_desc_sw128(sv + k16 * 2048, kBlockBytes, 1024);
+                ptx::umma_f16(tmem_base + (2 + x) * kTile, da, db, idesc_pv, (j ? 1u : 0u) | (uint32_t)k16);
+              }
+              ptx::umma_commit(ptx::smem_u32(&bars->pv_done[x]));
+              ++gp;
             }
-            ptx::umma_commit(ptx::smem_u32(&bars->pv_done[x]));
-            ++gp;
+            ptx::umma_commit(ptx::smem_u32(&bars->v_empty));
+            ++j;
+            progress = true;
           }
-          ptx::umma_commit(ptx::smem_u32(&bars->kv_empty[vpos.slot]));
-          vpos.advance();
-          vpos.advance();
+          if (!progress) {
+            if (*abort_flag) { ok = false; break; }
+            if (clock64() - t_item > kAttnWaitLimit) { *abort_flag = 1; ok = false; break; }
+          }
+#ifdef TSB_TUNING
+          {   // attribute the time of a round without progress to the first thing that was missing
+            const long long now = clock64();
+            if (!progress) {
+              int why;
+              if (next_s > j) why = !ready(&bars->v_full, (kt + j) & 1) ? 2 : 3;
+              else why = !ready(&bars->k_full[(kt + next_s) & 1], ((kt + next_s) >> 1) & 1) ? 0 : 1;
+              prof[why] += now - prof[7];
+            }
+            prof[7] = now;
+          }
+#endif
         }
+        kt += n;
       }
 #ifdef TSB_TUNING
       if (x == 0) {
@@ -675,6 +704,7 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #ifdef TSB_TUNING
     long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     const long long prof_start = clock64();
+    if (P.tune_mode == 1) ok = false;
 #endif
     for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
       uint32_t pr, b, h;
@@ -845,6 +875,9 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
         cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
       g_attn_sm_count = n;
   }
+#ifdef TSB_TUNING
+  P.tune_mode = getenv("TS_ATTN_MODE") ? atoi(getenv("TS_ATTN_MODE")) : 0;
+#endif
   static const int pair_env = getenv("TS_ATTN_PAIR") ? atoi(getenv("TS_ATTN_PAIR")) : -1;
   if (q_tiles % 2 == 0 && pair_env != 0) {
     // two query tiles per CTA (TS_ATTN_PAIR=0 in the environment selects the one-tile kernel)

@@ -15,7 +15,7 @@
 // columns is one 128-byte stick.
 //
 // Kernel shape: persistent, one CTA per SM, tile 128 x 256 x 64, kStages-deep
-// TMA->smem ring.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-5 drain the
+// TMA->smem ring.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-9 drain the
 // accumulator (TMEM -> registers -> fp16 -> global).  TMEM holds two 128x256 fp32
 // accumulators so the epilogue of tile i overlaps the main loop of tile i+1.
 // When M > 128 the same roles run on pairs of CTAs (clusters of two, tcgen05
@@ -33,11 +33,12 @@ namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64;
 constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;               // two per tensor-memory lane quarter, 128 accumulator columns each
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kABytes = BM * BK * 2;          // 16 KiB
 constexpr int kBBytes = BN * BK * 2;          // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kStagingBytes = 4 * 32 * 128;   // epilogue: 32 rows x 128 bytes per warp
+constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;   // epilogue: 32 rows x 128 bytes per warp
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
@@ -77,6 +78,7 @@ struct GemmParams {
 #ifdef TSB_TUNING
   int tune_noload;       // experiment: 1 = arm the "full" barriers without issuing the TMA loads, 2 = MMAs alone
   int tune_onecommit;    // experiment: masked commits
+  int tune_hint;         // experiment: suspend-time hint (ns) for the epilogue's and the producers' waits
 #endif
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
@@ -103,71 +105,104 @@ __device__ __forceinline__ void decode_tile(const GemmParams& P, uint32_t tile, 
   tn = band * P.band_tiles + (r - tm * width);
 }
 
-// Drains one warp's 32 accumulator rows x BN columns: tensor memory -> registers -> fp16 ->
-// a per-warp shared-memory staging block (32 rows x 128 bytes, 16-byte chunks XOR-swizzled by
-// row so that neither side has bank conflicts) -> global memory with every store instruction
-// covering four whole 128-byte sticks instead of 16 bytes of 32 different ones.
+// 64 accumulator columns of this warp's 32 rows: tensor memory -> registers (no wait).
+__device__ __forceinline__ void load_stick(uint32_t taddr, uint32_t (&r)[2][32]) {
+  ptx::tmem_ld_32x32(taddr, r[0]);
+  ptx::tmem_ld_32x32(taddr + 32, r[1]);
+}
+
+// Registers of one stick (fp32, one row per lane) -> fp16 -> the warp's shared-memory staging block
+// (32 rows x 128 bytes, 16-byte chunks XOR-swizzled by row so that neither side has bank
+// conflicts) -> global memory with every store instruction covering four whole 128-byte sticks
+// instead of 16 bytes of 32 different ones.  `res` holds the residual rows this lane will store
+// (fetched by the caller ahead of the tensor-memory wait), already in the store layout.
+template <bool RES>
+__device__ __forceinline__ void store_stick(const GemmParams& P, const uint32_t (&r)[2][32], uint8_t* stage,
+                                            __half* dst, uint32_t row0, uint32_t col, const uint4 (&res)[RES ? 8 : 1],
+                                            int lane) {
+  const int srow = lane >> 3, piece = lane & 7;
+#pragma unroll
+  for (int sub = 0; sub < 2; ++sub) {
+    Vec8h bv[4];
+    if (P.bias) {
+#pragma unroll
+      for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + sub * 32 + v * 8);
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      Vec8h o;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float x0 = __uint_as_float(r[sub][v * 8 + 2 * e]), x1 = __uint_as_float(r[sub][v * 8 + 2 * e + 1]);
+        if (P.bias) {
+          x0 += __half2float(bv[v].h[2 * e]);
+          x1 += __half2float(bv[v].h[2 * e + 1]);
+        }
+        o.h2[e] = __floats2half2_rn(x0, x1);
+      }
+      *reinterpret_cast<uint4*>(stage + lane * 128 + (((sub * 4 + v) ^ (lane & 7)) * 16)) = o.u;
+    }
+  }
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + srow;
+    Vec8h v;
+    v.u = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
+    if (row0 + rr < P.M) {
+      if (RES) {   // fp16 sum of the rounded product and the residual: what add(r, mm(a, b)) gives
+        Vec8h q;
+        q.u = res[RES ? i : 0];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v.h2[e] = __hadd2(v.h2[e], q.h2[e]);
+      }
+      st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
+    }
+  }
+  __syncwarp();
+}
+
+// Drains one warp's share of an accumulator: 32 rows x 128 columns (two sticks).  A stick's
+// residual rows are fetched while its tensor-memory loads are in flight.
+template <bool RES>
 __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, uint8_t* stage,
                                            uint32_t row0, uint32_t col0, uint32_t b, uint32_t h,
                                            int lane) {
   const uint32_t c_sticks = (P.N + 63) / 64;
   const int srow = lane >> 3, piece = lane & 7;
+  const uint32_t stick0 = col0 >> 6;
+  if (stick0 >= c_sticks) return;   // warp-uniform
+  const bool two = stick0 + 1 < c_sticks;
+  __half* dst0 = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick0 * P.c_stick_stride +
+                 ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
+  uint4 res[RES ? 8 : 1];
+  auto fetch_residual = [&](const __half* dst) {
+    if (RES) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = i * 4 + srow;
+        res[RES ? i : 0] = make_uint4(0, 0, 0, 0);
+        if (row0 + rr < P.M) res[RES ? i : 0] = ld_global_v4(P.residual + (dst - P.c) + (int64_t)rr * kStickHalfs);
+      }
+    }
+  };
+  // (320 threads leave 168 registers a thread: one stick of accumulator values at a time; the other
+  // epilogue warp of the lane quarter works on its own sticks meanwhile)
+  uint32_t r[2][32];
 #pragma unroll 1
-  for (int half = 0; half < BN / 64; ++half) {
-    const uint32_t col = col0 + half * 64;
-    const uint32_t stick = col >> 6;
-    if (stick >= c_sticks) break;   // warp-uniform
-#pragma unroll
-    for (int sub = 0; sub < 2; ++sub) {
-      uint32_t r[32];
-      ptx::tmem_ld_32x32(taddr + half * 64 + sub * 32, r);
-      ptx::tmem_ld_wait();
-      Vec8h bv[4];
-      if (P.bias) {
-#pragma unroll
-        for (int v = 0; v < 4; ++v) bv[v].u = ld_global_v4(P.bias + col + sub * 32 + v * 8);
-      }
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        Vec8h o;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float x0 = __uint_as_float(r[v * 8 + 2 * e]), x1 = __uint_as_float(r[v * 8 + 2 * e + 1]);
-          if (P.bias) {
-            x0 += __half2float(bv[v].h[2 * e]);
-            x1 += __half2float(bv[v].h[2 * e + 1]);
-          }
-          o.h2[e] = __floats2half2_rn(x0, x1);
-        }
-        *reinterpret_cast<uint4*>(stage + lane * 128 + (((sub * 4 + v) ^ (lane & 7)) * 16)) = o.u;
-      }
-    }
-    __syncwarp();
-    __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
-                  ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int rr = i * 4 + srow;
-      Vec8h v;
-      v.u = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
-      if (row0 + rr < P.M) {
-        if (P.residual) {   // fp16 sum of the rounded product and the residual: what add(r, mm(a, b)) gives
-          Vec8h r;
-          r.u = ld_global_v4(P.residual + (dst - P.c) + (int64_t)rr * kStickHalfs);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) v.h2[e] = __hadd2(v.h2[e], r.h2[e]);
-        }
-        st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
-      }
-    }
-    __syncwarp();
+  for (int k = 0; k < (two ? 2 : 1); ++k) {
+    __half* dst = dst0 + k * P.c_stick_stride;
+    load_stick(taddr + k * 64, r);
+    fetch_residual(dst);
+    ptx::tmem_ld_wait();
+    store_stick<RES>(P, r, stage, dst, row0, col0 + k * 64, res, lane);
   }
 }
 
 // The drain for a gate/up projection pair computed as one product whose stick columns alternate
-// gate, up, gate, up: every pair of accumulator sticks becomes one output stick
-// silu(gate) * up, with the roundings of the unfused sequence (product -> fp16, silu -> fp16,
-// multiply -> fp16).
+// gate, up, gate, up: a warp's 128 product columns are one (gate, up) pair of sticks and become one
+// output stick silu(gate) * up, with the roundings of the unfused sequence (product -> fp16,
+// silu -> fp16, multiply -> fp16).
 __device__ __forceinline__ float silu_of(float x) {
   float e;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
@@ -178,42 +213,39 @@ __device__ __forceinline__ void drain_rows_swiglu(const GemmParams& P, uint32_t 
                                                   int lane) {
   const uint32_t c_sticks = (P.N / 2 + 63) / 64;
   const int srow = lane >> 3, piece = lane & 7;
-#pragma unroll 1
-  for (int pair = 0; pair < BN / 128; ++pair) {
-    const uint32_t stick = (col0 >> 7) + pair;
-    if (stick >= c_sticks) break;   // warp-uniform
+  const uint32_t stick = col0 >> 7;
+  if (stick >= c_sticks) return;   // warp-uniform
+  uint32_t g[2][32], u[2][32];
+  load_stick(taddr, g);
+  load_stick(taddr + 64, u);
+  ptx::tmem_ld_wait();
 #pragma unroll
-    for (int sub = 0; sub < 2; ++sub) {
-      uint32_t g[32], u[32];
-      ptx::tmem_ld_32x32(taddr + pair * 128 + sub * 32, g);
-      ptx::tmem_ld_32x32(taddr + pair * 128 + 64 + sub * 32, u);
-      ptx::tmem_ld_wait();
+  for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        Vec8h o;
+    for (int v = 0; v < 4; ++v) {
+      Vec8h o;
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i = v * 8 + 2 * e;
-          const __half2 g16 = __floats2half2_rn(__uint_as_float(g[i]), __uint_as_float(g[i + 1]));
-          const __half2 u16 = __floats2half2_rn(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
-          const float2 gf = __half22float2(g16);
-          const __half2 s16 = __floats2half2_rn(silu_of(gf.x), silu_of(gf.y));
-          o.h2[e] = __hmul2(s16, u16);
-        }
-        *reinterpret_cast<uint4*>(stage + lane * 128 + (((sub * 4 + v) ^ (lane & 7)) * 16)) = o.u;
+      for (int e = 0; e < 4; ++e) {
+        const int i = v * 8 + 2 * e;
+        const __half2 g16 = __floats2half2_rn(__uint_as_float(g[sub][i]), __uint_as_float(g[sub][i + 1]));
+        const __half2 u16 = __floats2half2_rn(__uint_as_float(u[sub][i]), __uint_as_float(u[sub][i + 1]));
+        const float2 gf = __half22float2(g16);
+        const __half2 s16 = __floats2half2_rn(silu_of(gf.x), silu_of(gf.y));
+        o.h2[e] = __hmul2(s16, u16);
       }
+      *reinterpret_cast<uint4*>(stage + lane * 128 + (((sub * 4 + v) ^ (lane & 7)) * 16)) = o.u;
     }
-    __syncwarp();
-    __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
-                  ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int rr = i * 4 + srow;
-      const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
-      if (row0 + rr < P.M) st_global_v4(dst + (int64_t)rr * kStickHalfs, v);
-    }
-    __syncwarp();
   }
+  __syncwarp();
+  __half* dst = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick * P.c_stick_stride +
+                ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int rr = i * 4 + srow;
+    const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((piece ^ (rr & 7)) * 16));
+    if (row0 + rr < P.M) st_global_v4(dst + (int64_t)rr * kStickHalfs, v);
+  }
+  __syncwarp();
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -235,7 +267,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 4);
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), kEpilogueWarps);
     }
     bars->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -333,8 +365,10 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
     const uint32_t q = warp & 3;  // TMEM lane quarter this warp may read
+    const uint32_t ch = (uint32_t)(warp - 2) >> 2;   // which 128 columns of the accumulator
+    uint8_t* my_stage = staging + (warp - 2) * (32 * 128);
     uint32_t local_tile = 0;
     for (uint32_t tile = blockIdx.x; tile < P.num_tiles; tile += gridDim.x, ++local_tile) {
       uint32_t tm, tn, b, h;
@@ -344,11 +378,14 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                                   kWaitLimit)) break;
       ptx::tc_fence_after_sync();
       if (P.swiglu)
-        drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
-                          tm * BM + q * 32, tn * BN, b, h, lane);
+        drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + acc * BN + ch * 128, my_stage,
+                          tm * BM + q * 32, tn * BN + ch * 128, b, h, lane);
+      else if (P.residual)
+        drain_rows<true>(P, tmem_base + ((q * 32u) << 16) + acc * BN + ch * 128, my_stage,
+                         tm * BM + q * 32, tn * BN + ch * 128, b, h, lane);
       else
-        drain_rows(P, tmem_base + ((q * 32u) << 16) + acc * BN, staging + q * (32 * 128),
-                   tm * BM + q * 32, tn * BN, b, h, lane);
+        drain_rows<false>(P, tmem_base + ((q * 32u) << 16) + acc * BN + ch * 128, my_stage,
+                          tm * BM + q * 32, tn * BN + ch * 128, b, h, lane);
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
@@ -430,7 +467,7 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(ptx::smem_u32(&bars->acc_full[a]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 8);   // 4 epilogue warps in each CTA
+      ptx::mbar_init(ptx::smem_u32(&bars->acc_empty[a]), 2 * kEpilogueWarps);   // the epilogue warps of both CTAs
     }
     bars->abort_flag = 0;
     ptx::fence_barrier_init();
@@ -465,6 +502,12 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
           if (P.tune_noload & 2) { ok = false; break; }   // experiment: MMAs alone, no ring at all
 #endif
           TSB_PROF_BEGIN
+#ifdef TSB_TUNING
+          if (P.tune_hint) {
+            if (!ptx::mbar_wait_bounded_idle(ptx::smem_u32(&bars->empty[s]), ph ^ 1, abort_flag, kWaitLimit,
+                                             (uint32_t)P.tune_hint)) { ok = false; break; }
+          } else
+#endif
           if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->empty[s]), ph ^ 1, abort_flag,
                                       kWaitLimit)) { ok = false; break; }
           TSB_PROF_END(prof_a)
@@ -602,8 +645,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    // ------------------------------------------------------------ epilogue (warps 2..9, both CTAs)
     const uint32_t q = warp & 3;
+    const uint32_t ch = (uint32_t)(warp - 2) >> 2;   // which 128 columns of a 256-column block
+    uint8_t* my_stage = staging + (warp - 2) * (32 * 128);
     uint32_t local_tile = 0;
     bool ok = true;
     for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
@@ -613,15 +658,24 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       for (int half = 0; half < NH; ++half) {
         uint32_t slot, use;
         acc_slot<NH>(local_tile, half, slot, use);
+#ifdef TSB_TUNING
+        if (P.tune_hint) {
+          if (!ptx::mbar_wait_bounded_idle(ptx::smem_u32(&bars->acc_full[slot]), use & 1, abort_flag, kWaitLimit,
+                                           (uint32_t)P.tune_hint)) { ok = false; break; }
+        } else
+#endif
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[slot]), use & 1, abort_flag,
                                     kWaitLimit)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         if (P.swiglu)
-          drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + slot * BN, staging + q * (32 * 128),
-                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN, b, h, lane);
+          drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + slot * BN + ch * 128, my_stage,
+                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane);
+        else if (P.residual)
+          drain_rows<true>(P, tmem_base + ((q * 32u) << 16) + slot * BN + ch * 128, my_stage,
+                           tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane);
         else
-          drain_rows(P, tmem_base + ((q * 32u) << 16) + slot * BN, staging + q * (32 * 128),
-                     tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN, b, h, lane);
+          drain_rows<false>(P, tmem_base + ((q * 32u) << 16) + slot * BN + ch * 128, my_stage,
+                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0)
@@ -717,6 +771,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   if (const char* e = getenv("TS_GEMM_BAND")) band = (uint32_t)std::max(1, atoi(e));
   P.tune_noload = getenv("TS_GEMM_NOLOAD") ? atoi(getenv("TS_GEMM_NOLOAD")) : 0;
   P.tune_onecommit = getenv("TS_GEMM_ONECOMMIT") ? atoi(getenv("TS_GEMM_ONECOMMIT")) : 0;
+  P.tune_hint = getenv("TS_GEMM_HINT") ? atoi(getenv("TS_GEMM_HINT")) : 0;
 #endif
   P.band_tiles = band;
   if (use_pair) P.tiles_n = (uint32_t)ceil_div(N, BN * nh);

@@ -40,6 +40,53 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint (nanoseconds): the thread may stay suspended that long before
+// the instruction returns false, instead of the short default, so a waiting warp issues far fewer
+// instructions; it still wakes as soon as the phase completes.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait for warps that have nothing else to do for a long time (epilogue warps during a
+// main loop, producers with a full ring): as mbar_wait_bounded, polling with a long suspend hint.
+__device__ __forceinline__ bool mbar_wait_bounded_idle(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                       long long limit_cycles, uint32_t hint_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// Non-blocking test of a barrier phase (try_wait may suspend the thread for a while; this never does).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: gives up after `limit_cycles` clock cycles (or as soon as another
 // thread has raised *abort_flag) and returns false; the caller then unwinds.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,

@@ -78,7 +78,14 @@ class _SpyreImpl:
         return int(self._C.device_count())
 
     def current_device(self) -> int:
-        return int(self._C.current_device())
+        # on a machine without a device (compile-only use with fake tensors) index 0 is reported
+        return int(self._C.current_device()) if self.is_available() else 0
+
+    def is_initialized(self) -> bool:
+        return self._initialized
+
+    def init(self) -> None:
+        self._lazy_init()
 
     def set_device(self, idx: int) -> None:
         self._C.set_device(int(idx))
@@ -92,7 +99,7 @@ def make_spyre_module() -> types.ModuleType:
     mod = types.ModuleType(DEVICE_NAME)
     mod.__doc__ = "Spyre backend module (CUDA-backed)."
     for name in ("_is_in_bad_fork", "manual_seed", "manual_seed_all", "is_available",
-                 "device_count", "current_device", "set_device", "synchronize"):
+                 "device_count", "current_device", "set_device", "synchronize", "is_initialized", "init"):
         setattr(mod, name, getattr(impl, name))
     mod._is_compiled = lambda: True
 

@@ -18,7 +18,11 @@ def _autoload():
 
     register_interface_for_device(DEVICE_NAME, SpyreInterface)
 
-    from torch._inductor.codegen.common import register_backend_for_device
+    from torch._inductor.codegen.common import register_backend_for_device, register_device_op_overrides
+
+    from torch_spyre.utils.device_op_overrides import SpyreDeviceOpOverrides
+
+    register_device_op_overrides(device=DEVICE_NAME, device_op_overrides=SpyreDeviceOpOverrides())
 
     from .dsc import SuperDSCScheduling
     from .wrapper import SpyrePythonWrapperCodegen

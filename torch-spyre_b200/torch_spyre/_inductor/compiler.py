@@ -96,6 +96,8 @@ class CompiledGraph:
     into slot reads, and a value's slot is cleared after its last reader so that its memory goes
     back to the allocator while the graph is still running."""
 
+    route = "plan"
+
     def __init__(self, gm: GraphModule):
         self.gm = gm
         self.steps: List[Callable[[list], None]] = []
@@ -259,10 +261,72 @@ class CompiledGraph:
         return torch.fx.node.map_arg(self.output_node.args[0], lambda a: env[slot[a]])
 
 
+# "inductor": lower through Inductor itself (scheduler fusion, generated wrapper calling
+# async_compile.sdsc / runner.run), falling back to the FX-level plan below when Inductor meets
+# something the spyre scheduling cannot express; "plan": always the FX-level plan.
+backend_mode = "inductor"
+# what the last compilations used, newest last ("inductor" / "plan: <why>"), for tests
+last_routes: List[str] = []
+
+
 def compile_graph(gm: GraphModule, example_inputs) -> Callable:
     from . import patterns
 
     patterns.rewrite_aten_graph(gm)
+    if backend_mode == "inductor":
+        try:
+            run = compile_with_inductor(gm, example_inputs)
+            last_routes.append("inductor")
+            del last_routes[:-8]
+            return run
+        except Exception as e:  # Unsupported from the scheduling, or an Inductor lowering that has no spyre form
+            last_routes.append(f"plan: {type(e).__name__}: {str(e)[:200]}")
+            del last_routes[:-8]
+    return compile_with_plan(gm, example_inputs)
+
+
+def compile_with_inductor(gm: GraphModule, example_inputs) -> Callable:
+    """The aten graph goes through stock Inductor: lowering, its scheduler's fusion, then
+    SuperDSCScheduling / SpyrePythonWrapperCodegen (registered for the device) write the wrapper."""
+    import copy
+
+    import torch._inductor.config as inductor_config
+    from torch._inductor.compile_fx import compile_fx_inner
+    from torch._inductor.virtualized import V
+
+    from .choices import SpyreHeuristics
+
+    patches = {"split_reductions": False, "keep_output_stride": False, "benchmark_harness": False,
+               "permute_fusion": False, "fx_graph_cache": False, "implicit_fallbacks": True,
+               "triton.cudagraphs": False, "size_asserts": False, "nan_asserts": False}
+    gm_copy = copy.deepcopy(gm)     # Inductor edits the graph it is given; the plan fallback wants the original
+    from .lowering import spyre_lowerings
+
+    from .runtime import async_compile
+
+    specs: List[KernelSpec] = []
+    saved_capture, async_compile.capture = async_compile.capture, specs
+    try:
+        with inductor_config.patch(patches), V.set_choices_handler(SpyreHeuristics()), spyre_lowerings():
+            run = compile_fx_inner(gm_copy, example_inputs)
+    finally:
+        async_compile.capture = saved_capture
+    last_compiled.append(InductorCompiled(gm, specs))
+    del last_compiled[:-4]
+    return run
+
+
+class InductorCompiled:
+    """What a compilation through Inductor left behind, for tests and debugging: the aten graph it
+    was given and the specs of the kernels its wrapper defined."""
+
+    route = "inductor"
+
+    def __init__(self, gm: GraphModule, kernel_specs: List[KernelSpec]):
+        self.gm, self.kernel_specs = gm, kernel_specs
+
+
+def compile_with_plan(gm: GraphModule, example_inputs) -> Callable:
     compiled = CompiledGraph(gm)
 
     def run(args):

@@ -9,11 +9,18 @@ from . import KernelSpec, UnimplementedOp
 from .kernel_runner import SpyreFusedKernelRunner, SpyreUnimplementedRunner
 
 
+# When a list is installed here, every spec handed to sdsc() is appended to it (the compiler uses
+# this to know which kernels a generated wrapper defined).
+capture = None
+
+
 class SpyreAsyncCompile:
     def __init__(self) -> None:
         pass
 
     def sdsc(self, kernel_name: str, ks):
+        if capture is not None:
+            capture.append(ks)
         if isinstance(ks, UnimplementedOp):
             print(f"WARNING: Compiling unimplemented {ks.op} to runtime exception")
             return SpyreUnimplementedRunner(kernel_name, ks.op)

@@ -34,28 +34,54 @@ class SpyreFusedKernelRunner:
         self.reduce_scale = info["reduce_scale"]
         self.keepdim = info["keepdim"]
 
-    def run(self, *inputs: torch.Tensor) -> List[torch.Tensor]:
+    def run(self, *tensors: torch.Tensor) -> List[torch.Tensor]:
+        """run(*inputs) allocates and returns the results; run(*inputs, *outputs[, reduced output])
+        writes into the given buffers, outputs last: the convention of a generated wrapper
+        (torch_spyre/_inductor/spyre_kernel.py:362-369 of the reference)."""
         from ... import ops
 
-        like = inputs[0]
+        info = self.spec.op_info
+        n_in = info["n_inputs"]
+        inputs, given = tensors[:n_in], tensors[n_in:]
+        like = inputs[0] if inputs else given[0]
+        n_results = self.n_outputs + (1 if self.reduce else 0)
+        if given and len(given) != n_results:
+            raise RuntimeError(f"{self.name}: expected {n_in} inputs and {n_results} outputs, got {len(tensors)} tensors")
+        shapes = info.get("input_shapes") or [None] * n_in
         with torch.cuda.device(like.device.index or 0):
-            sticks = [ops._st(t) for t in inputs]
+            # an operand is the buffer viewed with the shape its index expression walks
+            sticks = [ops._st(t if s is None or tuple(t.shape) == tuple(s) else t.reshape(tuple(s)))
+                      for t, s in zip(inputs, shapes)]
             chain = K.Chain()
             chain.inputs = sticks
             for op, a, b in self.insns:
                 chain.emit(op, a, b)
-            outs = [torch.empty(self.shape, dtype=torch.float16, device=like.device)
-                    for _ in range(self.n_outputs)]
-            red = None
-            if self.reduce:
-                lead = list(self.shape[:-1])
-                rshape = lead + [1] if self.keepdim else (lead or [1])
-                red = torch.empty(rshape, dtype=torch.float16, device=like.device)
+            lead = list(self.shape[:-1])
+            rshape = lead + [1] if self.keepdim else (lead or [1])
+            if given:
+                outs = [self._as_image(t, self.shape) for t in given[:self.n_outputs]]
+                red = self._as_image(given[-1], rshape) if self.reduce else None
+            else:
+                outs = [torch.empty(self.shape, dtype=torch.float16, device=like.device)
+                        for _ in range(self.n_outputs)]
+                red = torch.empty(rshape, dtype=torch.float16, device=like.device) if self.reduce else None
             K.run_chain(chain, self.shape, n_outputs=self.n_outputs, reduce=self.reduce,
                         reduce_scale=self.reduce_scale, keepdim=self.keepdim,
                         outputs=[ops._st(o) for o in outs],
                         red_out=ops._st(red) if red is not None else None)
-        return outs + ([red] if red is not None else [])
+        return list(outs) + ([red] if red is not None else [])
+
+    @staticmethod
+    def _as_image(buffer: torch.Tensor, shape) -> torch.Tensor:
+        """An output buffer the wrapper allocated, viewed with the kernel's iteration shape.  The
+        kernel writes the stick image of that shape, so the buffer's own image must be the same
+        bytes: equal innermost extents (leading dims merge freely)."""
+        from ... import _C
+
+        t = buffer if tuple(buffer.shape) == tuple(shape) else buffer.view(tuple(shape))
+        if not _C.is_canonical(t):
+            raise RuntimeError(f"output buffer of shape {tuple(buffer.shape)} cannot hold the stick image of {tuple(shape)}")
+        return t
 
 
 def launch_kernel(spec, args):

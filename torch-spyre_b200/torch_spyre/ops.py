@@ -528,11 +528,25 @@ def _weight_operand(b: torch.Tensor) -> Tuple[StickTensor, bool]:
 
 
 def _matmul(a: torch.Tensor, b: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+            residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _check_fp16(a, b)
     if a.shape[-1] != b.shape[-2]:
         raise RuntimeError(f"mat1 and mat2 shapes cannot be multiplied ({tuple(a.shape)} and {tuple(b.shape)})")
-    out = _new(tuple(a.shape[:-1]) + (b.shape[-1],), a)
+    shape = tuple(a.shape[:-1]) + (b.shape[-1],)
+    given = out
+    if out is None or tuple(out.shape) != shape or out.dtype != a.dtype or not _C.is_canonical(out) or \
+            (residual is not None and out.data_ptr() == residual.data_ptr()):
+        out = _new(shape, a)      # written here, then copied into the caller's tensor below
+    if out.numel() == 0:
+        return out if given is None else given
+    out = _matmul_into(a, b, bias, residual, out)
+    if given is not None and given is not out:
+        given.copy_(out)
+        return given
+    return out
+
+
+def _matmul_into(a, b, bias, residual, out):
     if out.numel() == 0:
         return out
     if a.shape[-1] == 0:
@@ -555,18 +569,23 @@ def _bmm(a, b):
 
 
 @_impl("addmm")
-def _addmm(bias, a, b, *, beta=1, alpha=1):
+def _addmm(bias, a, b, *, beta=1, alpha=1, out=None):
     if float(beta) == 1.0 and float(alpha) == 1.0 and bias.dim() == 1 and bias.shape[0] == b.shape[-1]:
-        return _matmul(a, b, bias)
+        return _matmul(a, b, bias, out=out)
     if float(beta) == 1.0 and float(alpha) == 1.0 and a.dim() == 2 and a.shape[-1] > 0 and \
             tuple(bias.shape) == (a.shape[0], b.shape[-1]) and bias.dtype == torch.float16:
-        return _matmul(a, b, residual=bias)     # matrix-shaped bias: added in the GEMM epilogue
+        return _matmul(a, b, residual=bias, out=out)     # matrix-shaped bias: added in the GEMM epilogue
     prod = _matmul(a, b)
     if float(alpha) != 1.0:
         prod = _binary("MUL", prod, float(alpha))
-    if float(beta) == 0.0:
-        return prod
-    return _binary("ADD", prod, bias, alpha=float(beta))
+    res = prod if float(beta) == 0.0 else _binary("ADD", prod, bias, alpha=float(beta))
+    return res if out is None else _copy_into(out, res)
+
+
+# the out= forms are what a generated Inductor wrapper calls (extern_kernels.mm / bmm / addmm)
+_impl("mm.out")(lambda a, b, *, out: _matmul(a, b, out=out))
+_impl("bmm.out")(lambda a, b, *, out: _matmul(a, b, out=out))
+_impl("addmm.out")(lambda bias, a, b, *, beta=1, alpha=1, out: _addmm(bias, a, b, beta=beta, alpha=alpha, out=out))
 
 
 _CONVERTIBLE = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}

@@ -4,6 +4,26 @@ import torch
 from torch._dynamo.device_interface import DeviceInterface, caching_worker_current_devices
 
 
+class _B200Properties:
+    """What Inductor's heuristics ask a device for, for compile-only use on a machine without the
+    device (a B200's figures)."""
+    name = "NVIDIA B200"
+    multi_processor_count = 148
+    total_memory = 180 * 1024 ** 3
+    major, minor = 10, 0
+    max_threads_per_multi_processor = 2048
+    warp_size = 32
+    regs_per_multiprocessor = 65536
+    shared_memory_per_block_optin = 232448
+
+
+def _device_properties(device=None):
+    if torch.cuda.is_available():
+        index = device.index if isinstance(device, torch.device) else device
+        return torch.cuda.get_device_properties(index or 0)
+    return _B200Properties()
+
+
 class SpyreInterface(DeviceInterface):
     class Worker:
         @staticmethod
@@ -16,7 +36,11 @@ class SpyreInterface(DeviceInterface):
 
         @staticmethod
         def get_device_properties(device=None):
-            return torch.cuda.get_device_properties(device or 0)
+            return _device_properties(device)
+
+    @staticmethod
+    def get_device_properties(device=None):
+        return _device_properties(device)
 
     @staticmethod
     def current_device() -> int:
