@@ -341,7 +341,10 @@ int ts_softmax_mid(const void* x, void* y, int64_t outer, int64_t red, int64_t i
  * share the one array and it keeps whatever the previous call left there; nothing in
  * it needs to start at zero, since every partial is written before it is read, but two
  * calls whose kernels overlap on the GPU (different streams) would overwrite each
- * other's partials: run them on one stream or order them with events. */
+ * other's partials: run them on one stream or order them with events.  The address
+ * looked up by that first call is kept for the life of the process: it does not follow
+ * a device whose primary context is destroyed (cudaDeviceReset) and created again, so
+ * a process that resets a device must not call this entry on it afterwards. */
 int ts_reduce_mid_static(const void* x, void* y, int64_t outer, int64_t red, int64_t inner,
                          int reduce_op, float scale, void* stream);
 int64_t ts_reduce_mid_static_max_bytes(void);
@@ -365,6 +368,37 @@ int64_t ts_reduce_mid_static_max_bytes(void);
 int ts_gemm_f16(const void* a, const void* b, const void* bias, void* c, int64_t batch, int64_t M,
                 int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream);
 int ts_gemm_error_state(void);
+/* Row-parallel linear with the reduce-scatter in the GEMM's epilogue: the tensor-parallel half of
+ * a linear layer whose reduction dim K is split over ranks (the sharded decoder layer of
+ * tests/test_modules.py:133-211 is the reference's own goal; it has no such kernel).  This rank's
+ * partial product a[M, K_local] x b (as ts_gemm_f16) is not stored: its rows belong, in `owners`
+ * equal blocks of M / owners rows, to `owners` result buffers c_owner[r], each the fp16 stick image
+ * of [M / owners, N] in this GPU's memory or in a peer's (a pointer obtained through CUDA IPC or
+ * symmetric memory), and every tile is ADDED into its owner's buffer with 16-byte fp16x2
+ * reductions at system scope as soon as it leaves the tensor cores, so the exchange over NVLink
+ * runs under the rest of the GEMM.  The caller initialises each buffer (zeros, or the residual the
+ * layer adds) before any rank's launch and orders the ranks around the launches (a barrier before
+ * and after); the sum is formed in fp16 in arrival order, so results may differ from the
+ * unsharded product in the last bits.  M / owners must be a multiple of 32, owners <= 8.
+ * No TMA copy touches a peer's memory: peers are reached with plain vector reductions only. */
+int ts_gemm_f16_scatter_add(const void* a, const void* b, void* const* c_owner, int owners, int64_t M,
+                            int64_t N, int64_t K, int b_kmajor, void* stream);
+
+/* The all-gather half of the same layer: a 2-D device-to-device copy on `stream` whose destination
+ * (or source) may be a peer GPU's memory.  A rank's block of rows of a stick image is one
+ * contiguous piece of `width` bytes per stick column, `height` of them, `spitch` / `dpitch` bytes
+ * apart; each rank copies its block into every rank's full image.  No counterpart in the
+ * reference (single device, torch_spyre/__init__.py:87-89). */
+int ts_peer_copy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width,
+                    int64_t height, void* stream);
+
+/* Diagnostic for the give-up path of those bounded waits, without anything that could be left
+ * in flight: one warp of a one-block launch waits `limit_cycles` SM clocks (clamped to
+ * [1000, 10^7]) on a barrier nothing arrives on, gives up, and raises the same sticky word, so
+ * ts_gemm_error_state() returns 1 once afterwards.  The reference reports runtime failures as
+ * exceptions from launch_kernel (torch_spyre/csrc/module.cpp:86-109); this is the hook a test uses
+ * to see the equivalent status path work end to end. */
+int ts_gemm_wait_selftest(int64_t limit_cycles, void* stream);
 
 /* ts_gemm_f16 with a residual: c = fp16(a x b [+ bias]) + residual, the sum taken in fp16 exactly
  * as a separate add of the rounded product would (residual: stick image shaped like c, may be c

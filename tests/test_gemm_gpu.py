@@ -137,3 +137,48 @@ def test_swiglu_gemm(m, k, n, cuda):
     upp = down(K.matmul(up(a, cuda), up(wu, cuda), b_kmajor=True))
     assert_close(fused, F.silu(gate) * upp)
     assert_close(fused, F.silu(F.linear(a, wg)) * F.linear(a, wu))
+
+
+def test_a_wait_that_gives_up_reports_and_leaves_the_device_usable(cuda):
+    """The bounded waits' give-up path, driven without a fault: a warp waits a few thousand cycles
+    on a barrier nothing arrives on, the kernel returns, the sticky status reads 1 then 0, and the
+    next GEMM is correct."""
+    lib = _abi.lib()
+    assert lib.ts_gemm_error_state() == 0
+    assert lib.ts_gemm_wait_selftest(5000, None) == 0
+    torch.cuda.synchronize()
+    assert lib.ts_gemm_error_state() == 1
+    assert lib.ts_gemm_error_state() == 0
+    g = torch.Generator().manual_seed(21)
+    a, b = torch.randn(300, 256, generator=g).half(), (torch.randn(256, 192, generator=g) * 0.1).half()
+    got = K.from_sticks(K.matmul(K.to_sticks(a.to(cuda)), K.to_sticks(b.to(cuda)))).cpu()
+    assert_close(got, a @ b)
+    assert lib.ts_gemm_error_state() == 0
+
+
+@pytest.mark.parametrize("owners,m,k,n", [(2, 512, 256, 320), (4, 1024, 512, 256), (8, 2048, 384, 1024), (1, 256, 128, 128)])
+def test_scatter_add_epilogue_on_one_gpu(owners, m, k, n, cuda):
+    """The reduce-scatter epilogue with every owner's buffer on this GPU: two "ranks", each holding
+    half of K, add their partial products into the owners' buffers, which start out holding a
+    residual.  Result: residual + a @ w^T, block of rows by block of rows."""
+    g = torch.Generator().manual_seed(31)
+    a = torch.randn(m, 2 * k, generator=g).half()
+    w = (torch.randn(n, 2 * k, generator=g) * 0.05).half()
+    res = torch.randn(m, n, generator=g).half()
+    rows = m // owners
+    outs = [up(res[r * rows:(r + 1) * rows].contiguous(), cuda) for r in range(owners)]
+    ptrs = [o.ptr() for o in outs]
+    for half in range(2):      # the two ranks' launches, one after the other on this stream
+        sa = up(a[:, half * k:(half + 1) * k].contiguous(), cuda)
+        sw = up(w[:, half * k:(half + 1) * k].contiguous(), cuda)
+        K.matmul_scatter_add(sa, sw, ptrs, b_kmajor=True)
+    torch.cuda.synchronize()
+    no_kernel_timeout()
+    got = torch.cat([down(o) for o in outs], 0)
+    want = (res.float() + a.float() @ w.float().t()).half()
+    assert_close(got, want, atol=4e-3)       # three fp16 roundings (residual + two partial sums) instead of one
+    lib = _abi.lib()
+    p = outs[0].ptr()
+    assert lib.ts_gemm_f16_scatter_add(p, p, _abi.ptrs([p]), 1, 48, 64, 64, 1, None) == _abi.TS_ERR_UNSUPPORTED   # rows % 32
+    assert lib.ts_gemm_f16_scatter_add(p, p, _abi.ptrs([p] * 9), 9, 288, 64, 64, 1, None) == _abi.TS_ERR_INVALID
+    assert lib.ts_gemm_f16_scatter_add(p, p, _abi.ptrs([0]), 1, 64, 64, 64, 1, None) == _abi.TS_ERR_ALIGNMENT

@@ -42,12 +42,6 @@ constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;   // epilogue: 32 rows 
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
-constexpr bool kOneCommit = false;             // one masked commit for both CTAs instead of two commits
-#ifdef TSB_TUNING
-#define TSB_TUNE_ONECOMMIT || P.tune_onecommit
-#else
-#define TSB_TUNE_ONECOMMIT
-#endif
 constexpr double kWideCost = 0.93;              // time of a 256 x 512 pair tile relative to two 256 x 256 ones
 constexpr long long kDrainLimit = 200000ll;     // ~0.1 ms: far longer than a TMA copy is in flight
 
@@ -57,7 +51,7 @@ __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
 // operands [0] and for a drained accumulator [1], their total loop cycles [2], cycles the
 // producers waited for a free stage [3], producer loop cycles [4]
 __device__ unsigned long long g_gemm_prof[8];
-#define TSB_PROF_DECL long long prof_t0 = 0, prof_a = 0, prof_b = 0; const long long prof_start = clock64();
+#define TSB_PROF_DECL long long prof_t0 = 0, prof_a = 0, prof_b = 0; const long long prof_start = clock64(); (void)prof_b;
 #define TSB_PROF_BEGIN prof_t0 = clock64();
 #define TSB_PROF_END(acc) acc += clock64() - prof_t0;
 #else
@@ -77,11 +71,15 @@ struct GemmParams {
   uint32_t band_tiles;   // tile columns per band of the tile order (see decode_tile)
 #ifdef TSB_TUNING
   int tune_noload;       // experiment: 1 = arm the "full" barriers without issuing the TMA loads, 2 = MMAs alone
-  int tune_onecommit;    // experiment: masked commits
   int tune_hint;         // experiment: suspend-time hint (ns) for the epilogue's and the producers' waits
 #endif
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
+  // Reduce-scatter epilogue: the rows of the product are owned in equal blocks by `owners`
+  // buffers (this GPU's and its peers'), and a tile is added into its owner's buffer with
+  // fp16x2 reductions instead of being stored.  owners == 0: plain stores into c.
+  uint32_t owners, rows_per_owner;
+  __half* c_owner[8];
 };
 
 struct Barriers {
@@ -103,6 +101,14 @@ __device__ __forceinline__ void decode_tile(const GemmParams& P, uint32_t tile, 
   const uint32_t width = min(P.band_tiles, P.tiles_n - band * P.band_tiles);
   tm = r / width;
   tn = band * P.band_tiles + (r - tm * width);
+}
+
+// Adds eight fp16 values to memory (this GPU's or, over NVLink, a peer's) without reading them
+// back: a vector reduction at system scope.
+__device__ __forceinline__ void red_add_v4(void* p, uint4 v) {
+  asm volatile("red.relaxed.sys.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
 }
 
 // 64 accumulator columns of this warp's 32 rows: tensor memory -> registers (no wait).
@@ -156,7 +162,8 @@ __device__ __forceinline__ void store_stick(const GemmParams& P, const uint32_t 
 #pragma unroll
         for (int e = 0; e < 4; ++e) v.h2[e] = __hadd2(v.h2[e], q.h2[e]);
       }
-      st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
+      if (P.owners) red_add_v4(dst + (int64_t)rr * kStickHalfs, v.u);
+      else st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
     }
   }
   __syncwarp();
@@ -164,17 +171,26 @@ __device__ __forceinline__ void store_stick(const GemmParams& P, const uint32_t 
 
 // Drains one warp's share of an accumulator: 32 rows x 128 columns (two sticks).  A stick's
 // residual rows are fetched while its tensor-memory loads are in flight.
-template <bool RES>
+// `release` tells the MMA thread that this warp no longer needs the accumulator; it is called as
+// soon as the values are in registers wherever the registers allow that (the accumulator is the
+// scarce thing: the next tile's MMAs wait for it, the stores can trail behind).
+template <bool RES, class Release>
 __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, uint8_t* stage,
                                            uint32_t row0, uint32_t col0, uint32_t b, uint32_t h,
-                                           int lane) {
+                                           int lane, Release release) {
   const uint32_t c_sticks = (P.N + 63) / 64;
   const int srow = lane >> 3, piece = lane & 7;
   const uint32_t stick0 = col0 >> 6;
-  if (stick0 >= c_sticks) return;   // warp-uniform
+  if (stick0 >= c_sticks) { release(); return; }   // warp-uniform
   const bool two = stick0 + 1 < c_sticks;
   __half* dst0 = P.c + (int64_t)h * P.c_head_stride + (int64_t)stick0 * P.c_stick_stride +
                  ((int64_t)b * P.M + row0) * kStickHalfs + piece * 8;
+  if (P.owners) {   // the warp's 32 rows lie in one owner's block (rows_per_owner is a multiple of 32)
+    const uint32_t owner = row0 / P.rows_per_owner;
+    if (owner >= P.owners) { release(); return; }
+    dst0 = P.c_owner[owner] + (int64_t)stick0 * P.c_stick_stride +
+           (int64_t)(row0 - owner * P.rows_per_owner) * kStickHalfs + piece * 8;
+  }
   uint4 res[RES ? 8 : 1];
   auto fetch_residual = [&](const __half* dst) {
     if (RES) {
@@ -186,8 +202,10 @@ __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, 
       }
     }
   };
-  // (320 threads leave 168 registers a thread: one stick of accumulator values at a time; the other
-  // epilogue warp of the lane quarter works on its own sticks meanwhile)
+  // One stick of accumulator values at a time (320 threads leave 168 registers a thread; holding
+  // both sticks to release the accumulator earlier spills and measured slower); the other epilogue
+  // warp of the lane quarter works on its own sticks meanwhile.  A stick's residual rows are
+  // fetched while its tensor-memory loads are in flight.
   uint32_t r[2][32];
 #pragma unroll 1
   for (int k = 0; k < (two ? 2 : 1); ++k) {
@@ -195,6 +213,7 @@ __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, 
     load_stick(taddr + k * 64, r);
     fetch_residual(dst);
     ptx::tmem_ld_wait();
+    if (k == (two ? 1 : 0)) release();
     store_stick<RES>(P, r, stage, dst, row0, col0 + k * 64, res, lane);
   }
 }
@@ -208,17 +227,19 @@ __device__ __forceinline__ float silu_of(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(-x * 1.4426950408889634f));
   return x * __fdividef(1.f, 1.f + e);
 }
+template <class Release>
 __device__ __forceinline__ void drain_rows_swiglu(const GemmParams& P, uint32_t taddr, uint8_t* stage,
                                                   uint32_t row0, uint32_t col0, uint32_t b, uint32_t h,
-                                                  int lane) {
+                                                  int lane, Release release) {
   const uint32_t c_sticks = (P.N / 2 + 63) / 64;
   const int srow = lane >> 3, piece = lane & 7;
   const uint32_t stick = col0 >> 7;
-  if (stick >= c_sticks) return;   // warp-uniform
+  if (stick >= c_sticks) { release(); return; }   // warp-uniform
   uint32_t g[2][32], u[2][32];
   load_stick(taddr, g);
   load_stick(taddr + 64, u);
   ptx::tmem_ld_wait();
+  release();
 #pragma unroll
   for (int sub = 0; sub < 2; ++sub) {
 #pragma unroll
@@ -377,18 +398,20 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[acc]), acc_ph, abort_flag,
                                   kWaitLimit)) break;
       ptx::tc_fence_after_sync();
+      auto release = [&] {
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
+      };
       if (P.swiglu)
         drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + acc * BN + ch * 128, my_stage,
-                          tm * BM + q * 32, tn * BN + ch * 128, b, h, lane);
+                          tm * BM + q * 32, tn * BN + ch * 128, b, h, lane, release);
       else if (P.residual)
         drain_rows<true>(P, tmem_base + ((q * 32u) << 16) + acc * BN + ch * 128, my_stage,
-                         tm * BM + q * 32, tn * BN + ch * 128, b, h, lane);
+                         tm * BM + q * 32, tn * BN + ch * 128, b, h, lane, release);
       else
         drain_rows<false>(P, tmem_base + ((q * 32u) << 16) + acc * BN + ch * 128, my_stage,
-                          tm * BM + q * 32, tn * BN + ch * 128, b, h, lane);
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->acc_empty[acc]));
+                          tm * BM + q * 32, tn * BN + ch * 128, b, h, lane, release);
     }
   }
 
@@ -573,7 +596,6 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       const uint32_t a_hi = (uint32_t)(da0 >> 32), b_hi = (uint32_t)(db0 >> 32);
       const uint32_t b_step = P.b_kmajor ? (32u >> 4) : (2048u >> 4);
       const uint32_t full0 = ptx::smem_u32(&bars->full[0]);
-      const uint32_t empty_l0 = ptx::smem_u32(&bars->empty[0]);
       const uint32_t empty_c0 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 0);
       const uint32_t empty_c1 = ptx::map_to_cta(ptx::smem_u32(&bars->empty[0]), 1);
       uint32_t s = 0, ph = 0, local_tile = 0;
@@ -614,23 +636,16 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             }
             if (kb + 1 == P.k_blocks) {   // this block is complete once the MMAs issued so far are
               const uint32_t f = ptx::smem_u32(&bars->acc_full[slot]);
-              if (kOneCommit TSB_TUNE_ONECOMMIT) {
-                ptx::umma_commit_pair_mask(f, 3);
-              } else {
-                ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
-                ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
-              }
+              ptx::umma_commit_pair(ptx::map_to_cta(f, 0));
+              ptx::umma_commit_pair(ptx::map_to_cta(f, 1));
             }
           }
 #ifdef TSB_TUNING
           if (!(P.tune_noload & 2)) {
 #endif
-          if (kOneCommit TSB_TUNE_ONECOMMIT) {
-            ptx::umma_commit_pair_mask(empty_l0 + s * 8, 3);   // "stage free" to both CTAs at once
-          } else {
-            ptx::umma_commit_pair(empty_c0 + s * 8);
-            ptx::umma_commit_pair(empty_c1 + s * 8);
-          }
+          // (one masked commit for both CTAs instead of these two measured the same)
+          ptx::umma_commit_pair(empty_c0 + s * 8);
+          ptx::umma_commit_pair(empty_c1 + s * 8);
 #ifdef TSB_TUNING
           }
 #endif
@@ -667,19 +682,21 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
         if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->acc_full[slot]), use & 1, abort_flag,
                                     kWaitLimit)) { ok = false; break; }
         ptx::tc_fence_after_sync();
+        auto release = [&] {
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[slot]), 0));
+        };
         if (P.swiglu)
           drain_rows_swiglu(P, tmem_base + ((q * 32u) << 16) + slot * BN + ch * 128, my_stage,
-                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane);
+                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane, release);
         else if (P.residual)
           drain_rows<true>(P, tmem_base + ((q * 32u) << 16) + slot * BN + ch * 128, my_stage,
-                           tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane);
+                           tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane, release);
         else
           drain_rows<false>(P, tmem_base + ((q * 32u) << 16) + slot * BN + ch * 128, my_stage,
-                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane);
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0)
-          ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&bars->acc_empty[slot]), 0));
+                            tm * 2 * BM + rank * BM + q * 32, tn * BNT + half * BN + ch * 128, b, h, lane, release);
       }
     }
   }
@@ -708,8 +725,16 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
                        const void* bias, const void* residual, void* c, int64_t c_stick_stride,
                        int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
                        int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream,
-                       int swiglu = 0) {
+                       int swiglu = 0, void* const* c_owner = nullptr, int owners = 0) {
   if ((uintptr_t)residual % 16) return TS_ERR_ALIGNMENT;
+  if (owners) {
+    if (owners < 1 || owners > 8 || !c_owner || residual || bias || swiglu || batch != 1 || heads != 1)
+      return TS_ERR_INVALID;
+    if (M % owners || (M / owners) % 32) return TS_ERR_UNSUPPORTED;
+    for (int r = 0; r < owners; ++r)
+      if (!c_owner[r] || (uintptr_t)c_owner[r] % 128) return TS_ERR_ALIGNMENT;
+    c = c_owner[0];
+  }
   if (swiglu && (N % 128 != 0 || bias || residual)) return TS_ERR_UNSUPPORTED;
   if (heads < 0 || batch < 0 || M < 0 || N < 0 || K < 0) return TS_ERR_INVALID;
   if (heads == 0 || batch == 0 || M == 0 || N == 0) return TS_OK;
@@ -736,6 +761,12 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   P.batch = (uint32_t)batch; P.heads = (uint32_t)heads;
   P.c_stick_stride = c_stick_stride;
   P.c_head_stride = c_head_stride;
+  P.owners = (uint32_t)owners;
+  if (owners) {
+    P.rows_per_owner = (uint32_t)(M / owners);
+    P.c_stick_stride = (int64_t)P.rows_per_owner * kStickHalfs;   // every owner's buffer is the image of [M / owners, N]
+    for (int r = 0; r < owners; ++r) P.c_owner[r] = (__half*)c_owner[r];
+  }
   P.tiles_m = (uint32_t)ceil_div(M, BM);
   P.tiles_n = (uint32_t)ceil_div(N, BN);
   const int64_t tiles = (int64_t)P.tiles_m * P.tiles_n * batch * heads;
@@ -770,7 +801,6 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   if (const char* e = getenv("TS_GEMM_NH")) nh = atoi(e) == 2 && use_pair ? 2 : 1;
   if (const char* e = getenv("TS_GEMM_BAND")) band = (uint32_t)std::max(1, atoi(e));
   P.tune_noload = getenv("TS_GEMM_NOLOAD") ? atoi(getenv("TS_GEMM_NOLOAD")) : 0;
-  P.tune_onecommit = getenv("TS_GEMM_ONECOMMIT") ? atoi(getenv("TS_GEMM_ONECOMMIT")) : 0;
   P.tune_hint = getenv("TS_GEMM_HINT") ? atoi(getenv("TS_GEMM_HINT")) : 0;
 #endif
   P.band_tiles = band;
@@ -851,6 +881,44 @@ extern "C" int ts_gemm_error_state(void) {
     cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int));
   }
   return v;
+}
+
+namespace tsb {
+namespace {
+// One warp waits, with the given limit, on a barrier nothing will ever arrive on: the unwinding
+// path of the GEMM's bounded waits in isolation (no TMA copy, no MMA, no tensor memory involved).
+__global__ void gemm_wait_selftest_kernel(long long limit_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  volatile int* flag = &abort_flag;
+  const bool done = ptx::mbar_wait_bounded(ptx::smem_u32(&bar), 0, flag, limit_cycles);
+  __syncthreads();
+  if (threadIdx.x == 0 && (!done || abort_flag)) atomicExch(&g_gemm_error, 1);
+}
+}  // namespace
+}  // namespace tsb
+
+// Diagnostic: exercises the give-up path of the kernels' bounded waits.  A single warp waits
+// `limit_cycles` SM clocks (clamped to [1000, 10^7]) for an arrival that never comes, then raises
+// the same sticky error word a real kernel would: ts_gemm_error_state() reports 1 afterwards (and
+// clears it).  Nothing else is in flight in that launch, so the device stays fully usable.
+extern "C" int ts_gemm_wait_selftest(int64_t limit_cycles, void* stream) {
+  const long long limit = limit_cycles < 1000 ? 1000 : (limit_cycles > 10000000 ? 10000000 : limit_cycles);
+  gemm_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit);
+  TSB_CHECK_LAUNCH();
+  return TS_OK;
+}
+
+extern "C" int ts_gemm_f16_scatter_add(const void* a, const void* b, void* const* c_owner, int owners,
+                                       int64_t M, int64_t N, int64_t K, int b_kmajor, void* stream) {
+  return gemm_launch(a, 0, 0, b, 0, 0, nullptr, nullptr, nullptr, 0, 0, 1, 1, M, N, K, b_kmajor, 0, stream, 0,
+                     c_owner, owners);
 }
 
 extern "C" int ts_gemm_f16_swiglu(const void* a, const void* w_gate_up, void* c, int64_t batch,

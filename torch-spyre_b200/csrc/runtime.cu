@@ -29,3 +29,21 @@ extern "C" const char* ts_status_string(int status) {
 extern "C" int ts_abi_version(void) { return 1; }
 
 extern "C" const char* ts_last_cuda_error(void) { return g_last_cuda_error; }
+
+// 2-D device-to-device copy on `stream`; either side may be a peer GPU's memory reachable from
+// this device (an address obtained through CUDA IPC or symmetric memory).  `height` pieces of
+// `width` bytes, `spitch` / `dpitch` bytes apart: a block of rows of a stick image is one such
+// piece per stick column, which is how the tensor-parallel layer gathers its activations.
+extern "C" int ts_peer_copy_2d(void* dst, int64_t dpitch, const void* src, int64_t spitch, int64_t width,
+                               int64_t height, void* stream) {
+  if (width < 0 || height < 0 || dpitch < width || spitch < width) return TS_ERR_INVALID;
+  if (width == 0 || height == 0) return TS_OK;
+  if (!dst || !src) return TS_ERR_INVALID;
+  const cudaError_t e = cudaMemcpy2DAsync(dst, (size_t)dpitch, src, (size_t)spitch, (size_t)width, (size_t)height,
+                                          cudaMemcpyDeviceToDevice, (cudaStream_t)stream);
+  if (e != cudaSuccess) {
+    tsb::note_cuda_error(e);
+    return TS_ERR_CUDA;
+  }
+  return TS_OK;
+}

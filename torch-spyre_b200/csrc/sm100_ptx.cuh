@@ -284,15 +284,6 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                : "memory");
 }
 
-// The same arrival delivered to the barrier at this shared-memory offset in every CTA of the
-// pair named by `cta_mask` (bit r = CTA rank r): one instruction where two commits would do.
-__device__ __forceinline__ void umma_commit_pair_mask(uint32_t local_bar, uint16_t cta_mask) {
-  asm volatile(
-      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-      ::"r"(local_bar), "h"(cta_mask)
-      : "memory");
-}
-
 // ---- descriptors ----------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
 // Addresses and offsets are given in bytes.

@@ -409,6 +409,17 @@ def matmul(a: StickTensor, b: StickTensor, bias: Optional[StickTensor] = None,
     return out
 
 
+def matmul_scatter_add(a: StickTensor, b: StickTensor, owner_ptrs: Sequence[int], b_kmajor: bool = True) -> None:
+    """Partial product a[M, K_local] @ b added, block of rows by block of rows, into the result
+    buffers at `owner_ptrs` (device addresses of fp16 stick images of [M / len(owner_ptrs), N]; this
+    GPU's or peers').  See ts_gemm_f16_scatter_add for what the caller has to order."""
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-2] if b_kmajor else b.shape[-1]
+    rc = _abi.lib().ts_gemm_f16_scatter_add(a.ptr(), b.ptr(), _abi.ptrs(list(owner_ptrs)), len(owner_ptrs), M, N, K,
+                                            int(b_kmajor), _stream())
+    _abi.check(rc, "ts_gemm_f16_scatter_add")
+
+
 def swiglu_matmul(a: StickTensor, w_gate_up: StickTensor, out: Optional[StickTensor] = None) -> StickTensor:
     """silu(a @ Wg^T) * (a @ Wu^T) in one GEMM.  a: [..., M, K]; w_gate_up: [2*N, K], rows alternating
     between Wg and Wu in blocks of 64 (see ``interleave_gate_up``)."""
