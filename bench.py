@@ -729,7 +729,12 @@ class Runner:
 
     def barrier(self):
         if self.dist is not None:
-            self.dist.barrier()
+            # an all-reduce of a CUDA tensor: dist.barrier() resolves its device through the process's
+            # accelerator type, which is spyre once the backend is loaded, and NCCL serves cuda tensors
+            self._token = getattr(self, "_token", None)
+            if self._token is None:
+                self._token = torch.zeros(1, device=self.dev)
+            self.dist.all_reduce(self._token)
         torch.cuda.synchronize()
 
     def max_over_ranks(self, *values):
@@ -870,7 +875,7 @@ def main():
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl")     # no device_id: with spyre registered it is the process's accelerator type, not cuda
 
     run = Runner(args, rank, world, local, dev, dist)
     head_name = HEADLINE if args.workload == "all" else args.workload

@@ -9,9 +9,16 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_pip_install_and_autoload(tmp_path):
+    # install from a copy: pip builds in the source directory and would leave an egg-info there, whose
+    # entry point any later `import torch` with that directory on sys.path would pick up
+    import shutil
+    src = tmp_path / "src"
+    shutil.copytree(os.path.join(ROOT, "torch-spyre_b200"), src,
+                    ignore=shutil.ignore_patterns("build", "*.egg-info", "__pycache__"))
+    shutil.copytree(os.path.join(ROOT, "include"), tmp_path / "include")     # build.py looks for ../include
     target = tmp_path / "site"
     out = subprocess.run([sys.executable, "-m", "pip", "install", "--no-deps", "--no-build-isolation", "--no-index",
-                          "--quiet", "--target", str(target), os.path.join(ROOT, "torch-spyre_b200")],
+                          "--quiet", "--target", str(target), str(src)],
                          capture_output=True, text=True, timeout=900)
     assert out.returncode == 0, out.stderr[-2000:]
     eps = (target / "torch_spyre-0.2.0.dist-info" / "entry_points.txt").read_text()

@@ -15,7 +15,7 @@ import torch.distributed as dist  # noqa: E402
 def main():
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dist.init_process_group("nccl")     # (no device_id: with spyre registered it is the accelerator type, not cuda)
     from oracle import llama_ref as L, math_ref
     from torch_spyre import _abi, stick_ops as K, tensor_parallel as TP
 

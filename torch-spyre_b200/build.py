@@ -38,6 +38,11 @@ def build_library(force: bool = False, verbose_ptxas: bool = False) -> str:
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers += [os.path.join(INCLUDE, f) for f in os.listdir(INCLUDE)]
     flags = NVCC_FLAGS + (["-Xptxas", "-v"] if verbose_ptxas else [])
+    if not force and not verbose_ptxas and os.path.exists(LIB_PATH):
+        # an up-to-date library needs no objects (a copy of the tree made without build/ has none)
+        newest = max(os.path.getmtime(p) for p in [os.path.join(CSRC, f) for f in sources] + headers)
+        if os.path.getmtime(LIB_PATH) >= newest:
+            return LIB_PATH
     jobs = []
     for f in sources:
         src = os.path.join(CSRC, f)

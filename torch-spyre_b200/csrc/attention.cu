@@ -412,7 +412,7 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // behind.  (One thread loading K and V in turn would hold every K load back behind the V buffer.)
 constexpr int kPairAttnThreads = 352;   // TMA warp, MMA warp A, 8 softmax warps, MMA warp B
 constexpr int kPairSmemTiles = 7;       // Q_A Q_B K0 K1 V P_A P_B
-constexpr int kPairAttnSmem = kPairSmemTiles * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
+[[maybe_unused]] constexpr int kPairAttnSmem = kPairSmemTiles * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
 
 struct PairAttnBars {
   uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_empty[2], p_full[2],
@@ -476,6 +476,7 @@ __device__ __forceinline__ bool decode_pair_item(const AttnParams& P, uint32_t i
   return true;
 }
 
+#ifdef TSB_TUNING   // kept for experiments only: the variant with P in shared memory
 __global__ void __launch_bounds__(kPairAttnThreads, 1)
 attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams P) {
@@ -837,6 +838,351 @@ attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __
   if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
 }
 
+#endif  // TSB_TUNING
+
+// ---- two query tiles per CTA, 64 keys at a time, probabilities in tensor memory ----------------
+// The kernel above keeps P in shared memory, which makes shared-memory bandwidth its limit: per
+// 128-key step the tensor cores read 256 KiB of operands, the softmax threads store 64 KiB of P and
+// TMA fills 64 KiB, 3000 cycles' worth at 128 B per clock for 2048 cycles of MMAs.  Here P never
+// touches shared memory: the softmax threads write it (fp16, two per 32-bit column) over the
+// scores they have just read, and the P V product takes its A operand from tensor memory.  So that
+// scores can still be computed ahead of the softmax, a step is 64 keys: per group two 64-column
+// score buffers (S(u+1) is computed while the softmax works on S(u)) plus the 128-column output,
+// 256 columns, 512 for the two groups.
+//   tensor memory: group A: S0 S1 O | group B: S0 S1 O   (64 + 64 + 128 columns each)
+//   shared memory: Q_A Q_B | K (3 tiles of 128 keys) | V (2 tiles)
+// A score buffer is free again once the P V product that read P from it has finished, so S(u+2)
+// waits for P V(u).  K and V tiles are loaded whole (128 keys) by the two producer lanes and
+// consumed in halves.
+constexpr int kHalfKeys = 64;
+constexpr int kP64KStages = 3, kP64VStages = 2;
+constexpr int kP64SmemTiles = 2 + kP64KStages + kP64VStages;
+constexpr int kP64Smem = kP64SmemTiles * kTileBytes + 1024 /*align*/ + 512 /*barriers*/;
+
+struct P64Bars {
+  uint64_t q_full, q_empty, k_full[kP64KStages], k_empty[kP64KStages], v_full[kP64VStages], v_empty[kP64VStages];
+  uint64_t s_full[2][2], p_full[2][2], pv_done[2][2];   // [group][score buffer]
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(P64Bars) <= 512, "barrier block outgrew its shared-memory reservation");
+
+__global__ void __launch_bounds__(kPairAttnThreads, 1)
+attention_causal_pair64_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                               const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t sq = base, sk = sq + 2 * kTileBytes, sv = sk + kP64KStages * kTileBytes;
+  P64Bars* bars = reinterpret_cast<P64Bars*>(gen_base + kP64SmemTiles * kTileBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+  const uint32_t num_items = pair_item_count(P);
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 2);        // released by both MMA threads
+    for (int i = 0; i < kP64KStages; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->k_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->k_empty[i]), 2);
+    }
+    for (int i = 0; i < kP64VStages; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->v_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->v_empty[i]), 2);
+    }
+    for (int x = 0; x < 2; ++x)
+      for (int b = 0; b < 2; ++b) {
+        ptx::mbar_init(ptx::smem_u32(&bars->s_full[x][b]), 1);
+        ptx::mbar_init(ptx::smem_u32(&bars->p_full[x][b]), 4);   // one arrival per softmax warp of the group
+        ptx::mbar_init(ptx::smem_u32(&bars->pv_done[x][b]), 1);
+      }
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kAttnTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producers: lane 0 Q and K, lane 1 V
+    if (lane == 0) {
+      uint32_t kt = 0, item_n = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
+        uint32_t pr, b, h;
+        if (!decode_pair_item(P, item, pr, b, h)) continue;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_empty), (item_n & 1) ^ 1, abort_flag, kAttnWaitLimit)) break;
+        const uint32_t qf = ptx::smem_u32(&bars->q_full);
+        ptx::mbar_arrive_expect_tx(qf, 2 * kTileBytes);
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int qrow = (int)((2 * pr + x) * kTile);
+          ptx::tma_load_5d(sq + x * kTileBytes, &map_q, qf, 0, qrow, (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sq + x * kTileBytes + kBlockBytes, &map_q, qf, 0, qrow, (int)b, (int)(2 * h + 1), 0);
+        }
+        const uint32_t n = 2 * pr + 2;
+        for (uint32_t j = 0; j < n; ++j, ++kt) {
+          const uint32_t st = kt % kP64KStages, ph = (kt / kP64KStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_empty[st]), ph ^ 1, abort_flag, kAttnWaitLimit)) {
+            ok = false;
+            break;
+          }
+          const uint32_t kf = ptx::smem_u32(&bars->k_full[st]);
+          ptx::mbar_arrive_expect_tx(kf, kTileBytes);
+          ptx::tma_load_5d(sk + st * kTileBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sk + st * kTileBytes + kBlockBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
+        }
+      }
+      if (*abort_flag) {   // after an abort only: let copies in flight land before the CTA exits
+        for (uint32_t k = 0; k < (kt < (uint32_t)kP64KStages ? kt : (uint32_t)kP64KStages); ++k) {
+          const uint32_t t = kt - 1 - k;
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[t % kP64KStages]), (t / kP64KStages) & 1, kAttnDrainLimit);
+        }
+        if (item_n > 0) ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
+      }
+    } else if (lane == 1) {
+      uint32_t kt = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        uint32_t pr, b, h;
+        if (!decode_pair_item(P, item, pr, b, h)) continue;
+        const uint32_t n = 2 * pr + 2;
+        for (uint32_t j = 0; j < n; ++j, ++kt) {
+          const uint32_t st = kt % kP64VStages, ph = (kt / kP64VStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_empty[st]), ph ^ 1, abort_flag, kAttnWaitLimit)) {
+            ok = false;
+            break;
+          }
+          const uint32_t vf = ptx::smem_u32(&bars->v_full[st]);
+          ptx::mbar_arrive_expect_tx(vf, kTileBytes);
+          ptx::tma_load_5d(sv + st * kTileBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sv + st * kTileBytes + kBlockBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
+        }
+      }
+      if (*abort_flag)
+        for (uint32_t k = 0; k < (kt < (uint32_t)kP64VStages ? kt : (uint32_t)kP64VStages); ++k) {
+          const uint32_t t = kt - 1 - k;
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full[t % kP64VStages]), (t / kP64VStages) & 1, kAttnDrainLimit);
+        }
+    }
+    __syncwarp();
+  } else if (warp == 1 || warp == 10) {
+    // ------------------------------------------------------------ MMA issuers: warp 1 for group A, warp 10 for B
+    if (lane == 0) {
+      const int x = warp == 1 ? 0 : 1;
+      const uint32_t idesc_s = ptx::idesc_f16_f32(kTile, kHalfKeys, 0, 0);     // 128 queries x 64 keys
+      const uint32_t idesc_pv = ptx::idesc_f16_f32(kTile, kTile, 0, 1);       // 128 queries x 128 dims, V MN-major
+      const uint32_t qb = sq + x * kTileBytes;
+      const uint32_t tg = tmem_base + x * 256;    // this group's columns: S0 S1 O
+      uint32_t kt = 0, item_n = 0;   // key tiles of finished items; items done
+      uint32_t U = 0;                // half-steps (64 keys) of finished items: phases of the per-buffer barriers
+      auto ready = [&](uint64_t* bar, uint32_t parity) { return ptx::mbar_test_wait(ptx::smem_u32(bar), parity); };
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
+        uint32_t pr, b, h;
+        if (!decode_pair_item(P, item, pr, b, h)) continue;
+        const uint32_t n = 2 * pr + 2;          // key tiles loaded for the item
+        const uint32_t nx = n - 1 + x;          // key tiles this group uses (A stops one short)
+        const uint32_t hx = 2 * nx, hn = 2 * n; // in half-steps
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), item_n & 1, abort_flag, kAttnWaitLimit)) break;
+        uint32_t s_next = 0, p_next = 0;        // next half-step whose scores / whose P V product is to be issued
+        const long long t_item = clock64();
+        while (ok && p_next < hn) {
+          bool progress = false;
+          // scores of half-step s_next: at most two ahead of the P V products (two score buffers)
+          if (s_next < hn && s_next < p_next + 2) {
+            const uint32_t t = kt + (s_next >> 1), ks = t % kP64KStages, hf = s_next & 1, ug = U + s_next;
+            bool can = ready(&bars->k_full[ks], (t / kP64KStages) & 1);
+            if (can && s_next < hx && ug >= 2)   // the buffer's previous P has been consumed
+              can = ready(&bars->pv_done[x][ug & 1], ((ug - 2) >> 1) & 1);
+            if (can) {
+              if (s_next < hx) {
+                ptx::tc_fence_after_sync();
+                const uint32_t kb = sk + ks * kTileBytes + hf * (kHalfKeys * 128);
+#pragma unroll
+                for (int k16 = 0; k16 < kTile / 16; ++k16) {
+                  const uint32_t off = (k16 >> 2) * kBlockBytes + (k16 & 3) * 32;
+                  ptx::umma_f16(tg + (ug & 1) * kHalfKeys, ptx::smem_desc_sw128(qb + off, 16, 1024),
+                                ptx::smem_desc_sw128(kb + off, 16, 1024), idesc_s, k16 != 0);
+                }
+                ptx::umma_commit(ptx::smem_u32(&bars->s_full[x][ug & 1]));
+                if (s_next + 1 == hx) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));   // Q_x is not read again
+              }
+              if (hf == 1) ptx::umma_commit(ptx::smem_u32(&bars->k_empty[ks]));   // both halves of the K tile are done with
+              ++s_next;
+              progress = true;
+            }
+          }
+          // P V product of half-step p_next
+          if (p_next < s_next) {
+            const uint32_t t = kt + (p_next >> 1), vs = t % kP64VStages, hf = p_next & 1, ug = U + p_next;
+            bool can = ready(&bars->v_full[vs], (t / kP64VStages) & 1);
+            if (can && p_next < hx) can = ready(&bars->p_full[x][ug & 1], (ug >> 1) & 1);
+#ifdef TSB_TUNING
+            if (P.tune_mode == 1) can = ready(&bars->v_full[vs], (t / kP64VStages) & 1);
+#endif
+            if (can) {
+              if (p_next < hx) {
+                ptx::tc_fence_after_sync();
+                const uint32_t vb = sv + vs * kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < kHalfKeys / 16; ++kk) {
+                  const uint64_t db = ptx::smem_desc_sw128(vb + (hf * 4 + kk) * 2048, kBlockBytes, 1024);
+                  ptx::umma_f16_ts(tg + 128, tg + (ug & 1) * kHalfKeys + kk * 8, db, idesc_pv,
+                                   (p_next ? 1u : 0u) | (uint32_t)kk);
+                }
+                ptx::umma_commit(ptx::smem_u32(&bars->pv_done[x][ug & 1]));
+              }
+              if (hf == 1) ptx::umma_commit(ptx::smem_u32(&bars->v_empty[vs]));
+              ++p_next;
+              progress = true;
+            }
+          }
+          if (!progress) {
+            if (*abort_flag) { ok = false; break; }
+            if (clock64() - t_item > kAttnWaitLimit) { *abort_flag = 1; ok = false; break; }
+          }
+        }
+        kt += n;
+        U += hx;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax + output: group A = warps 2-5, B = 6-9
+    const uint32_t x = (uint32_t)(warp - 2) >> 2;
+    const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
+    const uint32_t row = quarter * 32 + lane;
+    const uint32_t tg = tmem_base + ((quarter * 32u) << 16) + x * 256, to = tg + 128;
+    const float c = P.scale_log2;
+    auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag,
+                                                            kAttnWaitLimit)) != 0;
+    };
+    uint32_t U = 0;   // half-steps this group has processed in earlier items
+    bool ok = true;
+#ifdef TSB_TUNING
+    if (P.tune_mode == 1) ok = false;
+#endif
+    for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+      uint32_t pr, b, h;
+      if (!decode_pair_item(P, item, pr, b, h)) continue;
+      const uint32_t qt = 2 * pr + x, hx = 2 * (qt + 1);
+      float m = -1e30f, l = 0.f;
+      for (uint32_t u = 0; u < hx; ++u) {
+        const uint32_t ug = U + u, buf = ug & 1, ts = tg + buf * kHalfKeys;
+        if (!warp_wait(&bars->s_full[x][buf], (ug >> 1) & 1)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        uint32_t r[2][32];
+        ptx::tmem_ld_32x32(ts, r[0]);
+        ptx::tmem_ld_32x32(ts + 32, r[1]);
+        ptx::tmem_ld_wait();
+        if ((u >> 1) == qt) {   // diagonal tile: keys after the query do not exist
+          const uint32_t key0 = (u & 1) * kHalfKeys;
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (key0 + (uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
+        }
+        float mx[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(r[ch][i]));
+        const float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                     fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        if (u == 0) {
+          m = tile_max;   // key 0 exists for every query, so this is finite
+        } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
+          // raise the exponent offset (lazily): O and l shrink by alpha.  O must be at rest: the latest
+          // P V product of this group is the one of the previous half-step.
+          if (!warp_wait(&bars->pv_done[x][(ug - 1) & 1], ((ug - 1) >> 1) & 1)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const float m_new = fmaxf(m, tile_max);
+          const float alpha = ex2f((m - m_new) * c);
+          l *= alpha;
+          m = m_new;
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32(to + ch * 32, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ptx::tmem_st_32x32(to + ch * 32, o);
+          }
+          ptx::tmem_st_wait();
+        }
+        const float mc = m * c;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t packed[32];
+#pragma unroll
+        for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = ex2f(fmaf(__uint_as_float(r[ch][i]), c, -mc));
+            const float p1 = ex2f(fmaf(__uint_as_float(r[ch][i + 1]), c, -mc));
+            sum[(i >> 1) & 3] += p0 + p1;
+            const __half2 hp = __floats2half2_rn(p0, p1);
+            packed[ch * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hp);
+          }
+        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+        ptx::tmem_st_32x32(ts, packed);   // P over the scores just read: keys 2c, 2c+1 in column c
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[x][buf]));
+      }
+      if (!ok) break;
+      U += hx;
+      // both score buffers' last P V products (hx is even and at least 2)
+      if (!warp_wait(&bars->pv_done[x][0], ((U - 2) >> 1) & 1) || !warp_wait(&bars->pv_done[x][1], ((U - 1) >> 1) & 1)) break;
+      ptx::tc_fence_after_sync();
+      const float inv = 1.f / l;
+      const bool row_ok = qt * kTile + row < P.seq;
+      const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t o[32];
+        ptx::tmem_ld_32x32(to + ch * 32, o);
+        ptx::tmem_ld_wait();
+        __half* dst = P.out + (int64_t)(2 * h + (ch >> 1)) * P.stick_stride + grow * kStickHalfs + (ch & 1) * 32;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          Vec8h ov;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i = v * 8 + 2 * e;
+            ov.h2[e] = __floats2half2_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+          }
+          if (row_ok) st_global_v4(dst + v * 8, ov.u);
+        }
+      }
+      ptx::tc_fence_before_sync();
+    }
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kAttnTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
+}
+
 int g_attn_sm_count = 0;
 
 }  // namespace
@@ -878,18 +1224,27 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
 #ifdef TSB_TUNING
   P.tune_mode = getenv("TS_ATTN_MODE") ? atoi(getenv("TS_ATTN_MODE")) : 0;
 #endif
-  static const int pair_env = getenv("TS_ATTN_PAIR") ? atoi(getenv("TS_ATTN_PAIR")) : -1;
-  if (q_tiles % 2 == 0 && pair_env != 0) {
-    // two query tiles per CTA (TS_ATTN_PAIR=0 in the environment selects the one-tile kernel)
-    const cudaError_t e2 = cudaFuncSetAttribute(attention_causal_pair_kernel,
-                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kPairAttnSmem);
-    if (e2 != cudaSuccess) { note_cuda_error(e2); return TS_ERR_CUDA; }
+  if (q_tiles % 2 == 0) {
+    // two query tiles per CTA
     const int64_t pair_items = items / 2, pairs = q_tiles / 2;
     const int64_t sms = g_attn_sm_count > 0 ? g_attn_sm_count : 148;
     P.heads_per_round = (uint32_t)std::min<int64_t>(sms / pairs, batch * heads);
     // every SM gets a CTA: those beyond heads_per_round * pairs are the spares of pair_layout()
     const uint32_t grid2 = (uint32_t)std::min<int64_t>(pair_items, sms);
-    attention_causal_pair_kernel<<<grid2, kPairAttnThreads, kPairAttnSmem, (cudaStream_t)stream>>>(mq, mk, mv, P);
+#ifdef TSB_TUNING
+    if (getenv("TS_ATTN_KERNEL") && atoi(getenv("TS_ATTN_KERNEL")) == 1) {   // experiment: P through shared memory
+      const cudaError_t e1 = cudaFuncSetAttribute(attention_causal_pair_kernel,
+                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kPairAttnSmem);
+      if (e1 != cudaSuccess) { note_cuda_error(e1); return TS_ERR_CUDA; }
+      attention_causal_pair_kernel<<<grid2, kPairAttnThreads, kPairAttnSmem, (cudaStream_t)stream>>>(mq, mk, mv, P);
+      TSB_CHECK_LAUNCH();
+      return TS_OK;
+    }
+#endif
+    const cudaError_t e2 = cudaFuncSetAttribute(attention_causal_pair64_kernel,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kP64Smem);
+    if (e2 != cudaSuccess) { note_cuda_error(e2); return TS_ERR_CUDA; }
+    attention_causal_pair64_kernel<<<grid2, kPairAttnThreads, kP64Smem, (cudaStream_t)stream>>>(mq, mk, mv, P);
     TSB_CHECK_LAUNCH();
     return TS_OK;
   }
