@@ -44,7 +44,7 @@ MIN_TIMED_S = 0.050
 HEADLINE = "fused"
 OTHER_CONFIGS = ("softmax", "softmax_scaled", "relayout", "relayout_permuted", "bmm", "llama_layer",
                  "hf_llama_layer")
-EXTRA_WORKLOADS = ("pointwise", "attention")      # not part of the default line
+EXTRA_WORKLOADS = ("pointwise", "attention", "restickify")      # not part of the default line
 
 
 def measured_peaks():
@@ -245,6 +245,22 @@ def cpu_side(name: str, rank: int = 0, world: int = 1, rows=None, strong: bool =
                          "causal-useful flops (the attention block of BASELINE configs[4])",
                     sample="torch CPU eager attention (fp16 matmuls, fp32 softmax) on 1 batch entry x 4 heads",
                     sharding="the batch of 8 split over the ranks, no collective")
+    if name == "restickify":
+        outer = rows or shard(64, rank, world)
+        bits = torch.randint(-32768, 32768, (1, 2048, 4096), dtype=torch.int16,
+                             generator=torch.Generator().manual_seed(7 + rank))
+        host = bits.view(torch.float16).repeat(outer, 1, 1)
+        nbytes = host.numel() * 2
+
+        def cpu_step():
+            return host[:4].transpose(1, 2).contiguous()
+
+        return dict(host=(host,), cpu_step=cpu_step, work=2 * nbytes, cpu_work=2 * nbytes * 4 / outer, unit="GB/s",
+                    scaling="strong",
+                    desc=f"device-side restickify: fp16 [{outer}, 2048, 4096] spyre tensor, .transpose(1, 2).contiguous() "
+                         "(stick image to stick image in one pass)",
+                    sample="torch CPU x.transpose(1, 2).contiguous() on 4 outer entries",
+                    sharding="the outer 64 split over the ranks, no collective")
     raise SystemExit(f"unknown workload {name}")
 
 
@@ -423,6 +439,31 @@ def gpu_side(name: str, dev, cpu: dict):
                   l2=f"{nbytes >> 20} MiB tensors, far larger than L2", check=check)
         return wl
 
+    if name == "restickify":
+        import torch_spyre  # noqa: F401
+        (host,) = cpu["host"]
+        sdev = torch.device("spyre", dev.index)
+        hp = host.pin_memory()
+        xs = hp.to(sdev)
+
+        def step_dev():
+            return xs.transpose(1, 2).contiguous()
+
+        out_host = torch.empty(host.shape[0], host.shape[2], host.shape[1], dtype=torch.float16).pin_memory()
+
+        def step_e2e():
+            return out_host.copy_(hp.to(sdev).transpose(1, 2).contiguous())
+
+        def check():
+            got = step_dev()
+            if not torch.equal(got[-1].cpu().view(torch.int16), host[-1].transpose(0, 1).contiguous().view(torch.int16)):
+                raise AssertionError("restickified transpose differs from the host transpose")
+
+        nbytes = host.numel() * 2
+        wl.update(step_dev=step_dev, step_e2e=step_e2e, launches=1, h2d=nbytes, d2h=nbytes, traffic=None,
+                  l2=f"{nbytes >> 20} MiB tensor, far larger than L2", check=check)
+        return wl
+
     if name == "bmm":
         a1, b1 = cpu["host"]
         batch, (m, k), n = cpu["batch"], a1.shape[1:], b1.shape[2]
@@ -455,10 +496,33 @@ def gpu_side(name: str, dev, cpu: dict):
             if K._abi.lib().ts_gemm_error_state() != 0:
                 raise AssertionError("GEMM kernel gave up on an internal wait")
 
-        wl.update(step_dev=step_dev, step_e2e=step_e2e, launches=1,
+        def library_gemm(steps, warmup, sampler):
+            """cuBLAS (torch.bmm) on the same shape in the same process, timed the same way: a
+            yardstick beside the kernel's own figure, not part of any product path."""
+            la = torch.randn(batch, m, k, device=dev, dtype=torch.float16)
+            lb = torch.randn(batch, k, n, device=dev, dtype=torch.float16)
+            lc = torch.empty(batch, m, n, device=dev, dtype=torch.float16)
+            t_end = time.perf_counter() + 0.3
+            while time.perf_counter() < t_end:
+                torch.bmm(la, lb, out=lc)
+                torch.cuda.synchronize()
+            t0 = sampler.mark() if sampler else 0.0
+            regions = time_device(lambda: torch.bmm(la, lb, out=lc), steps, warmup, 0)
+            t1 = sampler.mark() if sampler else 0.0
+            dt = median(regions) / steps
+            out = {"what": "torch.bmm fp16 (cuBLAS), same shape, same process", "ms_per_step": dt * 1e3,
+                   "value": cpu["work"] / dt / 1e12, "unit": "TFLOP/s"}
+            if sampler:
+                clk = sampler.summary(t0, t1)
+                out["sm_mhz"] = clk.get("sm_mhz")
+                if clk.get("sm_mhz"):
+                    out["tflops_per_ghz"] = out["value"] / (clk["sm_mhz"] / 1e3)
+            return out
+
+        wl.update(step_dev=step_dev, step_e2e=step_e2e, launches=1, library_gemm=library_gemm,
                   h2d=(ah.numel() + bh.numel()) * 2, d2h=ch.numel() * 2,
-                  # ncu at batch 4: 248,113,408 B read + 52,386,048 B written, scaled by batch
-                  traffic=int(300499456 * batch / 4),
+                  # ncu at batch 8: 577,565,440 B read + 119,217,664 B written, scaled by batch
+                  traffic=int(696783104 * batch / 8),
                   l2=f"operands {(ah.numel() + bh.numel()) * 2 >> 20} MiB, far larger than L2", check=check)
         return wl
 
@@ -808,6 +872,10 @@ class Runner:
                "parity": "ok"}
         if "parity_detail" in wl:
             res["parity_detail"] = wl["parity_detail"]
+        if "library_gemm" in wl and self.world == 1:
+            lib = wl["library_gemm"](args.steps, args.warmup, self.sampler)
+            lib["ratio_ours_to_library"] = per_gpu / lib["value"]
+            res["library_gemm"] = lib
         if is_flops:
             res["roofline"]["frac_of_burst"] = per_gpu / burst
             res["roofline"]["frac_of_sustained"] = per_gpu / sustained
@@ -829,6 +897,136 @@ class Runner:
                                              "torch CPU eager / C oracle on the host cores"}
         res["_wl"] = wl
         return res
+
+
+def host_overheads(dev):
+    """Host time per launch, in microseconds, of each way into the library: a prepared C-ABI launch
+    (ctypes), one eager op on spyre tensors, and a compiled one-kernel graph by either compile
+    route.  Tiny tensors, many calls, one synchronize at the end: the device is never the limit."""
+    import torch_spyre  # noqa: F401
+    from torch_spyre import stick_ops as K
+    from torch_spyre._inductor import compiler
+
+    sdev = torch.device("spyre", dev.index)
+    g = torch.Generator().manual_seed(5)
+    x, a, b = (torch.randn(64, 128, generator=g).half(), torch.rand(128, generator=g).half(),
+               torch.rand(128, generator=g).half())
+    xs, as_, bs = x.to(sdev), a.to(sdev), b.to(sdev)
+
+    def per_call(fn, n=300):
+        for _ in range(20):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        host = time.perf_counter() - t0
+        torch.cuda.synchronize()
+        return host / n * 1e6
+
+    sx, sa, sb = K.copy_host_to_sticks(x), K.copy_host_to_sticks(a), K.copy_host_to_sticks(b)
+    c = K.Chain()
+    c.emit("LOAD", c.tensor(sx)).emit("MUL", c.tensor(sa)).emit("ADD", c.tensor(sb)).emit("EXP")
+    prepared = K.prepare_chain(c, (64, 128), n_outputs=0, reduce="sum")[0]
+    out = {"c_abi_prepared_launch": per_call(prepared), "eager_op": per_call(lambda: torch.add(xs, xs))}
+    fn = lambda t, u, v: torch.exp(t * u + v).sum(-1)      # noqa: E731
+    before = compiler.backend_mode
+    try:
+        for mode in ("inductor", "plan"):
+            compiler.backend_mode = mode
+            torch._dynamo.reset()
+            del compiler.last_routes[:]
+            compiled = torch.compile(fn)
+            compiled(xs, as_, bs)
+            out[f"compiled_graph_{mode}"] = per_call(lambda: compiled(xs, as_, bs))
+            if mode == "inductor":      # says so if the graph fell back to the plan
+                out["compiled_graph_inductor_route"] = compiler.last_routes[-1] if compiler.last_routes else "plan"
+    finally:
+        compiler.backend_mode = before
+        torch._dynamo.reset()
+    out["unit"] = "us of host time per call (1 kernel launch each)"
+    return out
+
+
+def measure_tp(run):
+    """config 5's layer as ONE layer split over the ranks (tensor parallel, sequence-parallel
+    activations): each rank holds 1/N of every weight and of the rows, the two reduce-scatters run in
+    the GEMM epilogues over NVLink peer memory, the two all-gathers are peer copies.  Every rank makes
+    the same number of calls (the layer's barriers are collective), so the region count is agreed
+    on before timing."""
+    from oracle import llama_ref as LR, math_ref
+    from torch_spyre import stick_ops as K
+    from torch_spyre.tensor_parallel import TPDecoderLayer, TPGroup
+
+    args, rank, world = run.args, run.rank, run.world
+    cfg = LR.LayerConfig()
+    batch, seq = 8, 2048
+    w = LR.make_weights(cfg)
+    x1 = torch.randn(1, seq, cfg.d_model, generator=torch.Generator().manual_seed(0)).half()
+    cos, sin = LR.rope_tables(seq, cfg.head_dim)
+    tp = TPGroup()
+    layer = TPDecoderLayer(tp, w, cfg.heads, cfg.eps, cos, sin, batch, seq)
+    rows = batch * seq // world
+    x_all = x1.repeat(batch, 1, 1).reshape(batch * seq, cfg.d_model)
+    mine = x_all[rank * rows:(rank + 1) * rows].contiguous().pin_memory()
+    xs = K.copy_host_to_sticks(mine)
+    y = layer(xs)
+    y = layer(xs)
+    torch.cuda.synchronize()
+    detail = None
+    if rank == 0:      # rank 0's first rows are a causal prefix of batch entry 0
+        n = 64
+        got = K.from_sticks(y).cpu()[:n]
+        cpu16 = LR.layer_forward(x1[:, :n], w, cfg)[0]
+        truth = LR.layer_forward_fp32(x1[:, :n], w, cfg)[0]
+        detail = math_ref.assert_no_worse_than_cpu_fp16(got, cpu16, truth, factor=2.0, what="TP layer")
+    if K._abi.lib().ts_gemm_error_state() != 0 or K._abi.lib().ts_attention_error_state() != 0:
+        raise AssertionError("a tensor-core kernel gave up on an internal wait")
+    run.barrier()
+
+    def region():
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            layer(xs)
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / 1e3
+
+    for _ in range(args.warmup):
+        layer(xs)
+    (first,) = run.max_over_ranks(region())
+    n_regions = int(min(max(MIN_TIMED_S / first, 1.0), 50.0) + 0.999)
+    t0 = run.sampler.mark() if run.sampler else 0.0
+    regions = [region() for _ in range(n_regions)]
+    t1 = run.sampler.mark() if run.sampler else 0.0
+    run.barrier()
+    (dt,) = run.max_over_ranks(median(regions) / args.steps)
+    flops = LR.layer_flops(batch, seq, cfg, causal=True)
+    hbm, burst, sustained, which = run.peaks
+    per_gpu = flops / world / dt / 1e12
+    # NVLink roofline: the slower of the layer's flops at the measured GEMM peak and the bytes a
+    # rank must send at the measured 770 GB/s per direction
+    link_s = layer.nvlink_bytes_per_call / 770e9
+    res = {"value": flops / dt / 1e12, "unit": "TFLOP/s", "ms_per_step": dt * 1e3, "scaling": "strong",
+           "timed": {"regions": n_regions, "steps_per_region": args.steps, "device_ms_total": sum(regions) * 1e3,
+                     "statistic": "median region / steps, max over ranks"},
+           "workload": "Llama-style decoder layer, batch 8 x seq 2048, d_model 4096, 32 heads x 128, SwiGLU 11008, as one "
+                       f"tensor-parallel layer over {world} GPUs (column-parallel q/k/v/gate/up, row-parallel o/down with the "
+                       "reduce-scatter in the GEMM epilogue over NVLink peer memory, all-gathers by peer copies)",
+           "sharding": "weights, heads and rows split over the ranks; 2 all-gathers + 2 reduce-scatters per layer",
+           "nvlink_bytes_per_step_per_rank": layer.nvlink_bytes_per_call,
+           "nvlink_gbs_per_rank": layer.nvlink_bytes_per_call / dt / 1e9,
+           "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": burst, "unit": "TFLOP/s",
+                        "frac": per_gpu / burst, "frac_of_sustained": per_gpu / sustained, "traffic": None,
+                        "peak_source": which + " (bf16 cuBLAS, burst)",
+                        "link_time_ms": link_s * 1e3, "link_frac_of_step": link_s / dt},
+           "gpu_launches": 15 * args.steps * n_regions, "parity": "ok"}
+    if detail:
+        res["parity_detail"] = detail
+    if run.sampler:
+        res["clocks"] = run.sampler.summary(t0, t1)
+    return res
 
 
 def release():
@@ -893,6 +1091,9 @@ def main():
             line[key] = head[key]
     del wl, head
     release()
+    if world == 1 and not args.no_e2e:
+        line["host_us_per_launch"] = host_overheads(dev)
+        release()
 
     if args.workload == "all":
         if world > 1:
@@ -913,6 +1114,10 @@ def main():
                     raise       # the other ranks are waiting at a barrier: end the job
                 r = {"parity": f"FAILED: {e}"}
             line["configs"][name] = r
+            release()
+        if world > 1 and 32 % world == 0:
+            line["configs"]["tp_llama_layer"] = measure_tp(run)
+            line["gpu_launches"] += line["configs"]["tp_llama_layer"]["gpu_launches"]
             release()
     if run.sampler:
         run.sampler.stop()

@@ -60,7 +60,7 @@ def test_every_workload_has_a_cpu_side():
         # small leading extents keep this quick; the shapes below the leading dim are the real ones
         rows = {"fused": 64, "pointwise": None, "softmax": None, "softmax_scaled": 512, "relayout": 1,
                 "relayout_permuted": 1, "bmm": 1, "llama_layer": 1, "hf_llama_layer": 1,
-                "attention": 1}[name]
+                "attention": 1, "restickify": 4}[name]
         if name in ("llama_layer", "hf_llama_layer", "bmm", "pointwise"):
             cpu = bench.cpu_side(name, rows=rows)       # built, not run: seconds of CPU time each
             assert callable(cpu["cpu_step"])

@@ -142,3 +142,15 @@ def test_attention_wrapper_refuses_before_any_launch():
     with pytest.raises(_abi.SpyreKernelError, match="does not match"):
         K.causal_attention(st(1, 128, 256), st(1, 128, 256), st(1, 128, 256), 2, 128, 2, 0.1)
     K.check_attention_args((2, 128, 256), (2, 128, 256), (2, 128, 256), 2, (torch.float16,) * 3)
+
+
+def test_device_only_custom_ops_refuse_host_tensors():
+    """swap / slice / exx2 / layernormscale / layernormnorm are registered for the spyre device
+    only, as in the reference (torch_spyre/_inductor/customops.py:38,56,102,116,133)."""
+    x = torch.arange(8.0).half()
+    for call in (lambda: torch.ops.spyre.swap(x), lambda: torch.ops.spyre.slice(x.reshape(-1, 1)),
+                 lambda: torch.ops.spyre.exx2(x.reshape(2, 4), 0.25, False),
+                 lambda: torch.ops.spyre.layernormscale(x.reshape(4, 2), 1e-5)):
+        with pytest.raises(NotImplementedError):
+            call()
+    assert torch.equal(torch.ops.spyre.compact(x.reshape(-1, 1)), x)       # compact has no device restriction

@@ -408,3 +408,27 @@ def test_dropout_forward_and_backward_ops():
     gsp = torch.ops.aten.native_dropout_backward(xs, m.to(DEV), 2.0).cpu()
     assert_close(gsp, x * m * 2.0)
     assert torch.equal(F.dropout(xs, 0.5, training=False).cpu(), x)
+
+
+def test_reference_custom_ops_on_the_device():
+    """torch.ops.spyre.{compact, swap, slice, layer_norm, exx2, layernormscale, layernormnorm} with
+    the reference's schemas (torch_spyre/_inductor/customops.py:22-154): the three layer-norm
+    stages chained give the fused layer norm."""
+    g = torch.Generator().manual_seed(19)
+    v = torch.randn(200, generator=g).half()
+    vs = v.to(DEV)
+    sw = torch.ops.spyre.swap(vs)
+    assert sw.shape == (200, 1) and torch.equal(sw.cpu().reshape(-1), v)
+    assert torch.equal(torch.ops.spyre.compact(sw).cpu(), v)
+    assert torch.equal(torch.ops.spyre.slice(sw).cpu(), v)
+    x = torch.randn(96, 256, generator=g).half()
+    w, b = torch.randn(256, generator=g).half(), torch.randn(256, generator=g).half()
+    xs, ws, bs = x.to(DEV), w.to(DEV), b.to(DEV)
+    ref = F.layer_norm(x, (256,), w, b, 1e-5)
+    assert_close(torch.ops.spyre.layer_norm(xs, [256], ws, bs, 1e-5).cpu(), ref)
+    stats = torch.ops.spyre.exx2(xs, 1.0 / 256, False)
+    assert stats.shape == (96, 2)
+    assert_close(stats.cpu()[:, 0], x.float().mean(-1).half(), atol=2e-3)
+    scaled = torch.ops.spyre.layernormscale(stats, 1e-5)
+    got = torch.ops.spyre.layernormnorm(xs, stats, scaled, ws, bs)
+    assert_close(got.cpu(), ref, atol=1e-2)

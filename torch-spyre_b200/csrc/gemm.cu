@@ -52,8 +52,8 @@ __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
 // producers waited for a free stage [3], producer loop cycles [4]
 __device__ unsigned long long g_gemm_prof[8];
 #define TSB_PROF_DECL long long prof_t0 = 0, prof_a = 0, prof_b = 0; const long long prof_start = clock64(); (void)prof_b;
-#define TSB_PROF_BEGIN prof_t0 = clock64();
-#define TSB_PROF_END(acc) acc += clock64() - prof_t0;
+#define TSB_PROF_BEGIN if (!(P.tune_noload & 8)) prof_t0 = clock64();
+#define TSB_PROF_END(acc) if (!(P.tune_noload & 8)) acc += clock64() - prof_t0;
 #else
 #define TSB_PROF_DECL
 #define TSB_PROF_BEGIN
@@ -72,6 +72,8 @@ struct GemmParams {
 #ifdef TSB_TUNING
   int tune_noload;       // experiment: 1 = arm the "full" barriers without issuing the TMA loads, 2 = MMAs alone
   int tune_hint;         // experiment: suspend-time hint (ns) for the epilogue's and the producers' waits
+  int tune_epi;          // experiment: 1 = epilogue releases without draining, 2 = tensor-memory loads only,
+                         // 3 = loads and staging but no global stores
 #endif
   int b_kmajor;          // 1: B given as [batch, N, K] (K contiguous)
   int b_batched;         // 0: one B shared by every batch
@@ -162,6 +164,9 @@ __device__ __forceinline__ void store_stick(const GemmParams& P, const uint32_t 
 #pragma unroll
         for (int e = 0; e < 4; ++e) v.h2[e] = __hadd2(v.h2[e], q.h2[e]);
       }
+#ifdef TSB_TUNING
+      if (P.tune_epi == 3) { if (v.u.x == 0x7fff7fffu) st_global_v4(dst, v.u); continue; }
+#endif
       if (P.owners) red_add_v4(dst + (int64_t)rr * kStickHalfs, v.u);
       else st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
     }
@@ -207,6 +212,9 @@ __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, 
   // warp of the lane quarter works on its own sticks meanwhile.  A stick's residual rows are
   // fetched while its tensor-memory loads are in flight.
   uint32_t r[2][32];
+#ifdef TSB_TUNING
+  if (P.tune_epi == 1) { release(); return; }
+#endif
 #pragma unroll 1
   for (int k = 0; k < (two ? 2 : 1); ++k) {
     __half* dst = dst0 + k * P.c_stick_stride;
@@ -214,6 +222,9 @@ __device__ __forceinline__ void drain_rows(const GemmParams& P, uint32_t taddr, 
     fetch_residual(dst);
     ptx::tmem_ld_wait();
     if (k == (two ? 1 : 0)) release();
+#ifdef TSB_TUNING
+    if (P.tune_epi == 2) continue;
+#endif
     store_stick<RES>(P, r, stage, dst, row0, col0 + k * 64, res, lane);
   }
 }
@@ -601,6 +612,10 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       uint32_t s = 0, ph = 0, local_tile = 0;
       bool ok = true;
       TSB_PROF_DECL
+#ifdef TSB_TUNING
+      unsigned long long prof_ns0;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_ns0));
+#endif
       for (uint32_t tile = pair; ok && tile < num_tiles; tile += num_pairs, ++local_tile) {
         for (uint32_t kb = 0; ok && kb < P.k_blocks; ++kb) {
           TSB_PROF_BEGIN
@@ -612,6 +627,9 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
             break;
           }
           TSB_PROF_END(prof_a)
+#ifdef TSB_TUNING
+          if (!(P.tune_noload & 4))
+#endif
           ptx::tc_fence_after_sync();
           const uint32_t so = s * (kPairStageBytes >> 4);
 #pragma unroll
@@ -656,6 +674,13 @@ gemm_f16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_con
       atomicAdd(&g_gemm_prof[0], (unsigned long long)prof_a);
       atomicAdd(&g_gemm_prof[1], (unsigned long long)prof_b);
       atomicAdd(&g_gemm_prof[2], (unsigned long long)(clock64() - prof_start));
+      if (pair == 0) {   // SM cycles against wall-clock nanoseconds: the clock this launch really ran at
+        unsigned long long ns1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(ns1));
+        atomicAdd(&g_gemm_prof[5], (unsigned long long)(clock64() - prof_start));
+        atomicAdd(&g_gemm_prof[6], ns1 - prof_ns0);
+        atomicAdd(&g_gemm_prof[7], 1ull);
+      }
 #endif
     }
     __syncwarp();
@@ -802,6 +827,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   if (const char* e = getenv("TS_GEMM_BAND")) band = (uint32_t)std::max(1, atoi(e));
   P.tune_noload = getenv("TS_GEMM_NOLOAD") ? atoi(getenv("TS_GEMM_NOLOAD")) : 0;
   P.tune_hint = getenv("TS_GEMM_HINT") ? atoi(getenv("TS_GEMM_HINT")) : 0;
+  P.tune_epi = getenv("TS_GEMM_EPI") ? atoi(getenv("TS_GEMM_EPI")) : 0;
 #endif
   P.band_tiles = band;
   if (use_pair) P.tiles_n = (uint32_t)ceil_div(N, BN * nh);

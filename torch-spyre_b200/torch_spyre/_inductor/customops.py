@@ -21,7 +21,7 @@ def _(input):
     return input.new_empty(input.numel())
 
 
-@torch.library.custom_op("spyre::swap", mutates_args=())
+@torch.library.custom_op("spyre::swap", mutates_args=(), device_types="spyre")
 def swap(input: torch.Tensor) -> torch.Tensor:
     return input.reshape(-1, 1).clone()
 
@@ -31,7 +31,7 @@ def _(input):
     return input.new_empty(input.numel(), 1)
 
 
-@torch.library.custom_op("spyre::slice", mutates_args=())
+@torch.library.custom_op("spyre::slice", mutates_args=(), device_types="spyre")
 def slice(input: torch.Tensor) -> torch.Tensor:
     return input.reshape(-1).clone()
 
@@ -56,7 +56,7 @@ def _(x, normalized_shape, weight=None, bias=None, eps=1e-5):
     return x.new_empty(x.size())
 
 
-@torch.library.custom_op("spyre::exx2", mutates_args=())
+@torch.library.custom_op("spyre::exx2", mutates_args=(), device_types="spyre")
 def exx2(x: torch.Tensor, exx2Scale: float, useZeroMean: bool) -> torch.Tensor:
     """Per row: [mean, mean of squares] scaled by exx2Scale * n, as a [rows..., 2] tensor."""
     n = x.shape[-1]
@@ -72,7 +72,7 @@ def _(x, exx2Scale, useZeroMean):
     return x.new_empty(list(x.shape[:-1]) + [2])
 
 
-@torch.library.custom_op("spyre::layernormscale", mutates_args=())
+@torch.library.custom_op("spyre::layernormscale", mutates_args=(), device_types="spyre")
 def layernormscale(x: torch.Tensor, eps: float) -> torch.Tensor:
     """From [mean, E[x^2]] to [mean, rsqrt(var + eps)]."""
     mean, sq = x[..., 0:1], x[..., 1:2]
@@ -84,7 +84,7 @@ def _(x, eps):
     return x.new_empty(x.size())
 
 
-@torch.library.custom_op("spyre::layernormnorm", mutates_args=())
+@torch.library.custom_op("spyre::layernormnorm", mutates_args=(), device_types="spyre")
 def layernormnorm(x: torch.Tensor, mean: torch.Tensor, norm_mean: torch.Tensor,
                   weight: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     y = (x - norm_mean[..., 0:1]) * norm_mean[..., 1:2]
@@ -157,10 +157,18 @@ def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor
 _gate_up_cache: dict = {}
 
 
+def invalidate_gate_up_cache() -> None:
+    """Forget every interleaved gate / up weight (after weights were changed through ``.data``)."""
+    _gate_up_cache.clear()
+
+
 def _cached_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
     """The interleaved weight for this pair of weight tensors, rebuilt whenever either tensor is a
     different object, lives elsewhere or has been written to (an address alone could be a new
-    tensor in recycled memory)."""
+    tensor in recycled memory).  Entries die with their weights (weak references) and at most 16
+    are kept.  A write through a detached alias (``w.data.copy_(...)``) changes neither the address
+    nor the parameter's version counter and is therefore not seen: call
+    ``invalidate_gate_up_cache()`` after such a write."""
     import weakref
 
     key = (id(w_gate), id(w_up))
