@@ -8,19 +8,21 @@
 // (its decoder-layer test, tests/test_modules.py:178-211, is skipped); this stands in for the
 // bmm / where / _softmax / bmm sequence its compiled path would emit.
 //
-// One CTA works on one (batch, head, 128-query tile) at a time and walks the key tiles up to
-// the diagonal.  Warp 0 issues TMA, warp 1 issues MMAs, warps 2-9 run the online softmax: two
-// threads per query row, each owning 64 of the tile's 128 key (and output) columns, so that
-// every scheduler has two softmax warps to alternate between:
-//     S_j = Q K_j^T            (tensor memory, two buffers so S_{j+1} is computed during softmax j)
-//     P_j = exp2((S_j - m) c) -> fp16 -> shared memory (two buffers), l += rowsum P_j
-//     O  += P_j V_j            (accumulated in tensor memory)
+// Two kernels, both with the probabilities kept in tensor memory (written over the scores they
+// were computed from; the P V product takes its A operand from there):
+//   * attention_causal_pair64_kernel, sequences of an even number of 128-row tiles: two query
+//     tiles of one (batch, head) per CTA, 64-key steps, per tile two score buffers and the output;
+//   * attention_causal_tmem_kernel, any other sequence: one query tile per CTA, 128-key steps, three
+//     score buffers and the output.
+// In both, one thread per tile issues the MMAs, producer lanes of warp 0 issue TMA (Q and K on one
+// lane, V on another), and one softmax thread per query row runs the online softmax:
+//     S_j = Q K_j^T,   P_j = exp2((S_j - m) c) -> fp16 over S_j,   l += rowsum P_j,   O += P_j V_j
 // and at the end out = O / l.  m is the row maximum used as the exponent offset; it is only
 // raised (and O, l rescaled, by the softmax threads through tcgen05.ld/st) when a row's new
 // maximum exceeds it by more than 8 in the exponent, i.e. P stays <= 256, so in steady state
-// the softmax threads never touch O and run a full tile ahead of the P V MMA.  Every wait is
-// bounded; on a timeout the CTA raises a flag, every role leaves its loops, tensor memory is
-// released and a sticky error word is set.
+// the softmax threads never touch O.  Every wait is bounded; on a timeout the CTA raises a flag,
+// every role leaves its loops, the producers wait (bounded) for their copies in flight, tensor
+// memory is released and a sticky error word is set.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_map.cuh"
@@ -29,14 +31,9 @@ namespace tsb {
 namespace {
 
 constexpr int kTile = 128;                      // queries per tile = keys per tile = head dim
-constexpr int kAttnThreads = 320;                // TMA warp, MMA warp, 8 softmax warps
 constexpr int kBlockBytes = kTile * 128;        // one 128-row x 64-lane box: 16 KiB
 constexpr int kTileBytes = 2 * kBlockBytes;     // 32 KiB
-constexpr int kKvStages = 2;
-// Q | K stages | V stages | P0 P1
-constexpr int kSmemTiles = 3 + 2 * kKvStages;
-constexpr int kAttnSmem = kSmemTiles * kTileBytes + 1024 /*align*/ + 1280 /*barriers, exchange*/;
-constexpr uint32_t kAttnTmemCols = 512;         // S0 | S1 | O | (unused)
+constexpr uint32_t kAttnTmemCols = 512;         // every kernel here uses all of tensor memory
 constexpr float kRescaleThreshold = 8.f;        // in units of the exponent (log2)
 constexpr long long kAttnWaitLimit = 4000000000ll;  // ~2 s of SM clocks
 constexpr long long kAttnDrainLimit = 200000ll;   // ~0.1 ms: far longer than a TMA copy is in flight
@@ -63,334 +60,10 @@ struct AttnParams {
 #endif
 };
 
-struct AttnBars {
-  uint64_t q_full, q_empty, k_full[kKvStages], k_empty[kKvStages], v_full[kKvStages],
-      v_empty[kKvStages], s_full[2], p_full[2], pv_done[2];
-  uint32_t tmem_base;
-  int abort_flag;
-  float exchange[2][kTile];   // the two threads of a row swap their partial maximum / sum here
-};
-static_assert(sizeof(AttnBars) <= 1280, "barrier block outgrew its shared-memory reservation");
-
-// Heaviest tiles (most key tiles) first, so that the static round-robin over CTAs balances.
-__device__ __forceinline__ void decode_item(const AttnParams& P, uint32_t item, uint32_t& qt,
-                                            uint32_t& b, uint32_t& h) {
-  const uint32_t bh_count = P.batch * P.heads;
-  qt = P.q_tiles - 1 - item / bh_count;
-  const uint32_t bh = item % bh_count;
-  b = bh % P.batch;
-  h = bh / P.batch;
-}
-
 __device__ __forceinline__ float ex2f(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-__global__ void __launch_bounds__(kAttnThreads, 1)
-attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams P) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = ptx::smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* gen_base = smem_raw + (base - raw);
-  const uint32_t sq = base, sk = base + kTileBytes, sv = sk + kKvStages * kTileBytes,
-                 sp = sv + kKvStages * kTileBytes;
-  uint8_t* gen_p = gen_base + (sp - base);
-  AttnBars* bars = reinterpret_cast<AttnBars*>(gen_base + kSmemTiles * kTileBytes);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  volatile int* abort_flag = &bars->abort_flag;
-
-  if (threadIdx.x == 0) {
-    ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 1);
-    for (int s = 0; s < kKvStages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&bars->k_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->k_empty[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->v_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->v_empty[s]), 1);
-    }
-    for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(ptx::smem_u32(&bars->s_full[i]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[i]), 8);   // one arrival per softmax warp
-      ptx::mbar_init(ptx::smem_u32(&bars->pv_done[i]), 1);
-    }
-    bars->abort_flag = 0;
-    ptx::fence_barrier_init();
-    ptx::prefetch_tensormap(&map_q);
-    ptx::prefetch_tensormap(&map_k);
-    ptx::prefetch_tensormap(&map_v);
-  }
-  if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kAttnTmemCols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t g = 0, item_n = 0;
-      bool ok = true;
-      for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x, ++item_n) {
-        uint32_t qt, b, h;
-        decode_item(P, item, qt, b, h);
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_empty), (item_n & 1) ^ 1, abort_flag,
-                                    kAttnWaitLimit)) break;
-        const uint32_t qf = ptx::smem_u32(&bars->q_full);
-        ptx::mbar_arrive_expect_tx(qf, kTileBytes);
-        ptx::tma_load_5d(sq, &map_q, qf, 0, (int)(qt * kTile), (int)b, (int)(2 * h), 0);
-        ptx::tma_load_5d(sq + kBlockBytes, &map_q, qf, 0, (int)(qt * kTile), (int)b, (int)(2 * h + 1), 0);
-        for (uint32_t j = 0; j <= qt; ++j, ++g) {
-          const uint32_t s = g % kKvStages, ph = (g / kKvStages) & 1;
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_empty[s]), ph ^ 1, abort_flag,
-                                      kAttnWaitLimit)) { ok = false; break; }
-          const uint32_t kf = ptx::smem_u32(&bars->k_full[s]);
-          ptx::mbar_arrive_expect_tx(kf, kTileBytes);
-          ptx::tma_load_5d(sk + s * kTileBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
-          ptx::tma_load_5d(sk + s * kTileBytes + kBlockBytes, &map_k, kf, 0, (int)(j * kTile), (int)b,
-                           (int)(2 * h + 1), 0);
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_empty[s]), ph ^ 1, abort_flag,
-                                      kAttnWaitLimit)) { ok = false; break; }
-          const uint32_t vf = ptx::smem_u32(&bars->v_full[s]);
-          ptx::mbar_arrive_expect_tx(vf, kTileBytes);
-          ptx::tma_load_5d(sv + s * kTileBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
-          ptx::tma_load_5d(sv + s * kTileBytes + kBlockBytes, &map_v, vf, 0, (int)(j * kTile), (int)b,
-                           (int)(2 * h + 1), 0);
-        }
-      }
-      // Let copies still in flight land before the CTA can exit (matters after an abort only:
-      // otherwise the MMA warp has consumed every tile).
-      if (*abort_flag) {
-        const uint32_t issued = g < (uint32_t)kKvStages ? g : (uint32_t)kKvStages;
-        for (uint32_t k = 0; k < issued; ++k) {
-          const uint32_t t = g - 1 - k, s = t % kKvStages, ph = (t / kKvStages) & 1;
-          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[s]), ph, kAttnDrainLimit);
-          ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full[s]), ph, kAttnDrainLimit);
-        }
-        if (item_n > 0)
-          ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc_s = ptx::idesc_f16_f32(kTile, kTile, 0, 0);    // Q K^T: both K-major
-      const uint32_t idesc_pv = ptx::idesc_f16_f32(kTile, kTile, 0, 1);   // P V: V is MN-major
-      uint32_t g = 0, item_n = 0;
-      bool ok = true;
-      // S_t = Q K_t^T into score buffer t & 1
-      auto issue_scores = [&](uint32_t t) -> bool {
-        const uint32_t s = t % kKvStages, ph = (t / kKvStages) & 1;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_full[s]), ph, abort_flag, kAttnWaitLimit))
-          return false;
-        ptx::tc_fence_after_sync();
-        const uint32_t kb = sk + s * kTileBytes;
-#pragma unroll
-        for (int k16 = 0; k16 < kTile / 16; ++k16) {
-          const uint32_t off = (k16 >> 2) * kBlockBytes + (k16 & 3) * 32;
-          ptx::umma_f16(tmem_base + (t & 1) * kTile, ptx::smem_desc_sw128(sq + off, 16, 1024),
-                        ptx::smem_desc_sw128(kb + off, 16, 1024), idesc_s, k16 != 0);
-        }
-        ptx::umma_commit(ptx::smem_u32(&bars->s_full[t & 1]));
-        ptx::umma_commit(ptx::smem_u32(&bars->k_empty[s]));
-        return true;
-      };
-      for (uint32_t item = blockIdx.x; ok && item < P.num_items; item += gridDim.x, ++item_n) {
-        uint32_t qt, b, h;
-        decode_item(P, item, qt, b, h);
-        const uint32_t n = qt + 1;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), item_n & 1, abort_flag,
-                                    kAttnWaitLimit)) break;
-        ptx::tc_fence_after_sync();
-        if (!issue_scores(g)) break;
-        if (n == 1) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
-        for (uint32_t j = 0; j < n; ++j) {
-          const uint32_t t = g + j;
-          if (j + 1 < n) {
-            if (!issue_scores(t + 1)) { ok = false; break; }
-            if (j + 2 == n) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
-          }
-          const uint32_t s = t % kKvStages, ph = (t / kKvStages) & 1;
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->p_full[t & 1]), (t >> 1) & 1, abort_flag,
-                                      kAttnWaitLimit) ||
-              !ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_full[s]), ph, abort_flag, kAttnWaitLimit)) {
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after_sync();
-          const uint32_t vb = sv + s * kTileBytes;
-#pragma unroll
-          for (int k16 = 0; k16 < kTile / 16; ++k16) {
-            // P, K-major: 16 keys = 32 bytes along the swizzled row, 64-key blocks 16 KiB apart.
-            // V, MN-major: 16 keys = 16 rows = 2048 bytes; the two 64-wide d blocks are 16 KiB
-            // apart (leading offset), 8-row groups 1024 bytes apart.
-            const uint64_t da = ptx::smem_desc_sw128(
-                sp + (t & 1) * kTileBytes + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
-            const uint64_t db = ptx::smem_desc_sw128(vb + k16 * 2048, kBlockBytes, 1024);
-            ptx::umma_f16(tmem_base + 2 * kTile, da, db, idesc_pv, (j | (uint32_t)k16) != 0);
-          }
-          ptx::umma_commit(ptx::smem_u32(&bars->pv_done[t & 1]));
-          ptx::umma_commit(ptx::smem_u32(&bars->v_empty[s]));
-        }
-        g += n;
-      }
-    }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------ softmax + output (warps 2..9)
-    const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
-    const uint32_t half = (uint32_t)(warp - 2) >> 2;   // which 64 of the 128 columns: warps w, w+4 pair up
-    const uint32_t row = quarter * 32 + lane;       // query row within the tile
-    const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    const uint32_t to = lane_addr + 2 * kTile + half * 64;      // this thread's part of O
-    const float c = P.scale_log2;
-    // the whole warp takes the same decision, since what follows a wait is warp-collective
-    auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-      return __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag,
-                                                            kAttnWaitLimit)) != 0;
-    };
-    // the two threads of a row swap a value (64-thread named barrier of their two warps)
-    auto swap_with_partner = [&](float v) -> float {
-      bars->exchange[half][row] = v;
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      const float o = bars->exchange[half ^ 1][row];
-      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-      return o;
-    };
-    // After a wait has given up this warp is "dead": it does no more work, but it still walks
-    // every item and tile and meets its partner at every named barrier, so that no warp is
-    // left waiting at one (a named barrier cannot time out).  The abort flag makes every other
-    // wait in the CTA give up at once, so the walk is short.
-    uint32_t g = 0;
-    bool dead = false;
-    for (uint32_t item = blockIdx.x; item < P.num_items; item += gridDim.x) {
-      uint32_t qt, b, h;
-      decode_item(P, item, qt, b, h);
-      const uint32_t n = qt + 1;
-      float m = -1e30f, l = 0.f;   // m: shared by the row's two threads; l: this thread's columns only
-      for (uint32_t j = 0; j < n; ++j) {
-        const uint32_t t = g + j;
-        if (!dead && !warp_wait(&bars->s_full[t & 1], (t >> 1) & 1)) dead = true;
-        uint32_t r[2][32];
-        float own_max = -INFINITY;
-        if (!dead) {
-          ptx::tc_fence_after_sync();
-          const uint32_t ts = lane_addr + (t & 1) * kTile + half * 64;
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch) ptx::tmem_ld_32x32(ts + ch * 32, r[ch]);
-          ptx::tmem_ld_wait();
-          if (j == qt) {   // diagonal tile: keys after the query do not exist
-#pragma unroll
-            for (int ch = 0; ch < 2; ++ch)
-#pragma unroll
-              for (int i = 0; i < 32; ++i)
-                if (half * 64 + (uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
-          }
-          float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-          for (int ch = 0; ch < 2; ++ch)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) mx[i & 3] = fmaxf(mx[i & 3], __uint_as_float(r[ch][i]));
-          own_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        }
-        const float tile_max = fmaxf(own_max, swap_with_partner(own_max));
-        if (dead) continue;
-        if (j == 0) {
-          m = tile_max;   // O is still empty: nothing to rescale
-        } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
-          // Raise the offset: O and l of this row shrink by alpha (both warps of a pair see the
-          // same maxima and take this branch together).  P V of the previous key tile must have
-          // finished accumulating; the next one starts after our p_full arrival.
-          if (!warp_wait(&bars->pv_done[(t - 1) & 1], ((t - 1) >> 1) & 1)) { dead = true; continue; }
-          ptx::tc_fence_after_sync();
-          const float m_new = fmaxf(m, tile_max);
-          const float alpha = ex2f((m - m_new) * c);
-          l *= alpha;
-          m = m_new;
-#pragma unroll 1
-          for (int ch = 0; ch < 2; ++ch) {
-            uint32_t o[32];
-            ptx::tmem_ld_32x32(to + ch * 32, o);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            ptx::tmem_st_32x32(to + ch * 32, o);
-          }
-          ptx::tmem_st_wait();
-        }
-        // the P buffer of this tile was last read by the P V MMA two tiles ago
-        if (!warp_wait(&bars->pv_done[t & 1], ((t >> 1) & 1) ^ 1)) { dead = true; continue; }
-        // P = exp2(S c - m c) as fp16 into this thread's 64-key block of the swizzled operand tile
-        const float mc = m * c;
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-        uint8_t* prow = gen_p + (t & 1) * kTileBytes + half * kBlockBytes + row * 128;
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2f(fmaf(__uint_as_float(r[ch][i]), c, -mc));
-            const float p1 = ex2f(fmaf(__uint_as_float(r[ch][i + 1]), c, -mc));
-            sum[(i >> 1) & 3] += p0 + p1;
-            const __half2 hp = __floats2half2_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
-          }
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const uint32_t chunk = (uint32_t)(ch * 4 + v) ^ (row & 7);
-            *reinterpret_cast<uint4*>(prow + chunk * 16) =
-                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-          }
-        }
-        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-        ptx::fence_proxy_async_smem();
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[t & 1]));
-      }
-      // all key tiles accumulated: normalise and store this thread's stick of the packed output
-      const uint32_t tl = g + n - 1;
-      if (!dead && !warp_wait(&bars->pv_done[tl & 1], (tl >> 1) & 1)) dead = true;
-      const float inv = 1.f / (l + swap_with_partner(l));
-      g += n;
-      if (dead) continue;
-      ptx::tc_fence_after_sync();
-      const bool row_ok = qt * kTile + row < P.seq;   // the last tile may run past the sequence
-      const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
-      __half* dst = P.out + (int64_t)(2 * h + half) * P.stick_stride + grow * kStickHalfs;
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t o[32];
-        ptx::tmem_ld_32x32(to + ch * 32, o);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          Vec8h ov;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = v * 8 + 2 * e;
-            ov.h2[e] = __floats2half2_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-          }
-          if (row_ok) st_global_v4(dst + ch * 32 + v * 8, ov.u);
-        }
-      }
-      ptx::tc_fence_before_sync();
-    }
-  }
-
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
-    ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, kAttnTmemCols);
-  }
-  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
 }
 
 // ---- two query tiles per CTA -----------------------------------------------------------
@@ -398,7 +71,7 @@ attention_causal_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 // of one (batch, head) together: they share every K / V tile, and each has its own group of
 // four softmax warps (one thread per query row), its own score buffer, output accumulator
 // and P tile.  While one group is in its exponentials the other one's waits and the MMAs of
-// both run underneath, which is what the one-tile kernel above cannot do.
+// both run underneath.
 //   tensor memory: S_A | S_B | O_A | O_B (4 x 128 columns)
 //   shared memory: Q_A Q_B | K (2 buffers) | V (1 buffer) | P_A P_B
 // Each group has its own MMA-issuing thread (warps 1 and 10), so that neither waits on the
@@ -431,49 +104,56 @@ static_assert(sizeof(PairAttnBars) <= 256, "barrier block outgrew its shared-mem
 // When the slices left over after the last full round are no more than the SMs left over
 // after heads_per_round * pairs, those spare CTAs take one left-over slice each, all its pairs,
 // instead of a short last round that would land on CTAs already carrying a full share.
-__device__ __forceinline__ void pair_layout(const AttnParams& P, uint32_t& main_ctas, uint32_t& main_rounds,
-                                            bool& spares_take_rest) {
-  const uint32_t pairs = P.q_tiles / 2, bh_count = P.batch * P.heads;
-  main_ctas = P.heads_per_round * pairs;
+__device__ __forceinline__ void unit_layout(const AttnParams& P, uint32_t units, uint32_t& main_ctas,
+                                            uint32_t& main_rounds, bool& spares_take_rest) {
+  const uint32_t bh_count = P.batch * P.heads;
+  main_ctas = P.heads_per_round * units;
   const uint32_t full = bh_count / P.heads_per_round, rest = bh_count % P.heads_per_round;
   spares_take_rest = rest != 0 && rest <= gridDim.x - main_ctas;
   main_rounds = full + ((rest != 0 && !spares_take_rest) ? 1 : 0);
 }
-__device__ __forceinline__ uint32_t pair_item_count(const AttnParams& P) {
-  const uint32_t pairs = P.q_tiles / 2, bh_count = P.batch * P.heads;
-  if (P.heads_per_round == 0) return pairs * bh_count;
+// `units` = work items per (batch, head) slice: tile pairs for the two-tile kernels, tiles for the
+// one-tile kernel.
+__device__ __forceinline__ uint32_t unit_item_count(const AttnParams& P, uint32_t units) {
+  const uint32_t bh_count = P.batch * P.heads;
+  if (P.heads_per_round == 0) return units * bh_count;
   uint32_t main_ctas, main_rounds;
   bool spares;
-  pair_layout(P, main_ctas, main_rounds, spares);
-  return (main_rounds > pairs ? main_rounds : pairs) * gridDim.x;
+  unit_layout(P, units, main_ctas, main_rounds, spares);
+  return (main_rounds > units ? main_rounds : units) * gridDim.x;
 }
-__device__ __forceinline__ bool decode_pair_item(const AttnParams& P, uint32_t item, uint32_t& pr,
+__device__ __forceinline__ bool decode_unit_item(const AttnParams& P, uint32_t units, uint32_t item, uint32_t& pr,
                                                  uint32_t& b, uint32_t& h) {
-  const uint32_t pairs = P.q_tiles / 2, bh_count = P.batch * P.heads;
+  const uint32_t bh_count = P.batch * P.heads;
   uint32_t bh;
   if (P.heads_per_round == 0) {
-    pr = pairs - 1 - item / bh_count;
+    pr = units - 1 - item / bh_count;
     bh = item % bh_count;
   } else {
     uint32_t main_ctas, main_rounds;
     bool spares;
-    pair_layout(P, main_ctas, main_rounds, spares);
+    unit_layout(P, units, main_ctas, main_rounds, spares);
     const uint32_t r = item / gridDim.x, c = item - r * gridDim.x;
     if (c < main_ctas) {
       if (r >= main_rounds) return false;
-      bh = r * P.heads_per_round + c / pairs;
-      const uint32_t k = (c % pairs + r) % pairs;
-      pr = (k & 1) ? pairs - 1 - (k >> 1) : (k >> 1);   // 0, last, 1, last-1, ...: neighbours sum to a constant
+      bh = r * P.heads_per_round + c / units;
+      const uint32_t k = (c % units + r) % units;
+      pr = (k & 1) ? units - 1 - (k >> 1) : (k >> 1);   // 0, last, 1, last-1, ...: neighbours sum to a constant
     } else {
-      if (!spares || r >= pairs) return false;
+      if (!spares || r >= units) return false;
       bh = (bh_count / P.heads_per_round) * P.heads_per_round + (c - main_ctas);
-      pr = pairs - 1 - r;                                // a whole slice, heaviest pair first
+      pr = units - 1 - r;                                // a whole slice, heaviest unit first
     }
     if (bh >= bh_count) return false;
   }
   b = bh % P.batch;
   h = bh / P.batch;
   return true;
+}
+__device__ __forceinline__ uint32_t pair_item_count(const AttnParams& P) { return unit_item_count(P, P.q_tiles / 2); }
+__device__ __forceinline__ bool decode_pair_item(const AttnParams& P, uint32_t item, uint32_t& pr,
+                                                 uint32_t& b, uint32_t& h) {
+  return decode_unit_item(P, P.q_tiles / 2, item, pr, b, h);
 }
 
 #ifdef TSB_TUNING   // kept for experiments only: the variant with P in shared memory
@@ -1183,6 +863,419 @@ attention_causal_pair64_kernel(const __grid_constant__ CUtensorMap map_q, const 
   if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
 }
 
+// ---- one query tile per CTA, 128 keys at a time, probabilities in tensor memory -----------------
+// The two-tile kernel above is held back by its 64-key score MMAs (a 128x64x16 MMA occupies the
+// tensor pipe as long as a 128x128x16 one).  With one query tile per CTA the 512 columns hold three
+// full-width score buffers and the output:
+//   tensor memory: S0 S1 S2 O   (128 columns each)      shared memory: Q | K (3 tiles) | V (3 tiles)
+// so the scores run two key tiles ahead of the softmax threads: the buffer that S(j+2) goes into
+// was last read by P V(j-1), which finished a step ago, so the chain P(j) -> P V(j) -> "done" ->
+// next scores never delays the softmax (with two buffers it did: S(j+2) had to wait for P V(j)).
+// Every MMA is 128 wide.  One softmax thread per query row (four warps, the row's 128 scores in
+// registers); P goes back over the scores it was computed from and the P V product reads it from
+// there.  (Measured and dropped: two threads per row sharing its columns, and two sets of warps
+// taking alternate steps; both lose more to the 168-register limit of a 10-warp CTA and to the
+// hand-offs than the overlap gains.)  CTAs that run together share the K / V of a few
+// (batch, head) slices through the work order of decode_unit_item.
+constexpr int kT1Threads = 192;                  // producer warp, MMA warp, 4 softmax warps
+constexpr int kT1KStages = 3, kT1VStages = 3;
+constexpr int kT1SmemTiles = 1 + kT1KStages + kT1VStages;
+
+struct T1Bars {
+  uint64_t q_full, q_empty, k_full[kT1KStages], k_empty[kT1KStages], v_full[kT1VStages], v_empty[kT1VStages];
+  uint64_t s_full[3], p_full[3], pv_done[3];   // per score buffer
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(T1Bars) <= 512, "barrier block outgrew its shared-memory reservation");
+constexpr int kT1Smem = kT1SmemTiles * kTileBytes + 1024 /*align*/ + 512 /*barriers*/;
+
+__global__ void __launch_bounds__(kT1Threads, 1)
+attention_causal_tmem_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw);
+  const uint32_t sq = base, sk = sq + kTileBytes, sv = sk + kT1KStages * kTileBytes;
+  T1Bars* bars = reinterpret_cast<T1Bars*>(gen_base + kT1SmemTiles * kTileBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+  const uint32_t units = P.q_tiles;
+  const uint32_t num_items = unit_item_count(P, units);
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 1);
+    for (int i = 0; i < kT1KStages; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->k_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->k_empty[i]), 1);
+    }
+    for (int i = 0; i < kT1VStages; ++i) {
+      ptx::mbar_init(ptx::smem_u32(&bars->v_full[i]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->v_empty[i]), 1);
+    }
+    for (int b = 0; b < 3; ++b) {
+      ptx::mbar_init(ptx::smem_u32(&bars->s_full[b]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[b]), 4);   // one arrival per softmax warp
+      ptx::mbar_init(ptx::smem_u32(&bars->pv_done[b]), 1);
+    }
+    bars->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_q);
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kAttnTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producers: lane 0 Q and K, lane 1 V
+    if (lane == 0) {
+      uint32_t kt = 0, item_n = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        uint32_t qt, b, h;
+        if (!decode_unit_item(P, units, item, qt, b, h)) continue;
+        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_empty), (item_n & 1) ^ 1, abort_flag, kAttnWaitLimit)) break;
+        ++item_n;
+        const uint32_t qf = ptx::smem_u32(&bars->q_full);
+        ptx::mbar_arrive_expect_tx(qf, kTileBytes);
+        ptx::tma_load_5d(sq, &map_q, qf, 0, (int)(qt * kTile), (int)b, (int)(2 * h), 0);
+        ptx::tma_load_5d(sq + kBlockBytes, &map_q, qf, 0, (int)(qt * kTile), (int)b, (int)(2 * h + 1), 0);
+        for (uint32_t j = 0; j <= qt; ++j, ++kt) {
+          const uint32_t st = kt % kT1KStages, ph = (kt / kT1KStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_empty[st]), ph ^ 1, abort_flag, kAttnWaitLimit)) {
+            ok = false;
+            break;
+          }
+          const uint32_t kf = ptx::smem_u32(&bars->k_full[st]);
+          ptx::mbar_arrive_expect_tx(kf, kTileBytes);
+          ptx::tma_load_5d(sk + st * kTileBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sk + st * kTileBytes + kBlockBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
+        }
+      }
+      if (*abort_flag) {   // after an abort only: let copies in flight land before the CTA exits
+        for (uint32_t k = 0; k < (kt < (uint32_t)kT1KStages ? kt : (uint32_t)kT1KStages); ++k) {
+          const uint32_t t = kt - 1 - k;
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[t % kT1KStages]), (t / kT1KStages) & 1, kAttnDrainLimit);
+        }
+        if (item_n > 0) ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
+      }
+    } else if (lane == 1) {
+      uint32_t kt = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+        uint32_t qt, b, h;
+        if (!decode_unit_item(P, units, item, qt, b, h)) continue;
+        for (uint32_t j = 0; j <= qt; ++j, ++kt) {
+          const uint32_t st = kt % kT1VStages, ph = (kt / kT1VStages) & 1;
+          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_empty[st]), ph ^ 1, abort_flag, kAttnWaitLimit)) {
+            ok = false;
+            break;
+          }
+          const uint32_t vf = ptx::smem_u32(&bars->v_full[st]);
+          ptx::mbar_arrive_expect_tx(vf, kTileBytes);
+          ptx::tma_load_5d(sv + st * kTileBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
+          ptx::tma_load_5d(sv + st * kTileBytes + kBlockBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
+        }
+      }
+      if (*abort_flag)
+        for (uint32_t k = 0; k < (kt < (uint32_t)kT1VStages ? kt : (uint32_t)kT1VStages); ++k) {
+          const uint32_t t = kt - 1 - k;
+          ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full[t % kT1VStages]), (t / kT1VStages) & 1, kAttnDrainLimit);
+        }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // Two cursors walk the CTA's steps (key tiles of its items, in order): one issues scores, up to
+    // three steps ahead of the other, which issues P V products as the probabilities arrive.  The
+    // score cursor crosses item boundaries, so the first scores of the next query tile are ready
+    // when the softmax threads get there.
+    if (lane == 0) {
+      const uint32_t idesc_s = ptx::idesc_f16_f32(kTile, kTile, 0, 0);        // 128 queries x 128 keys
+      const uint32_t idesc_pv = ptx::idesc_f16_f32(kTile, kTile, 0, 1);       // 128 queries x 128 dims, V MN-major
+      const uint32_t tg = tmem_base, to = tmem_base + 384;
+      auto ready = [&](uint64_t* bar, uint32_t parity) { return ptx::mbar_test_wait(ptx::smem_u32(bar), parity); };
+      // first valid item at or after `item`: its step count, or 0 when there is none
+      auto seek = [&](uint32_t& item) -> uint32_t {
+        for (; item < num_items; item += gridDim.x) {
+          uint32_t qt, b, h;
+          if (decode_unit_item(P, units, item, qt, b, h)) return qt + 1;
+        }
+        return 0;
+      };
+      uint32_t item_s = blockIdx.x, item_p = blockIdx.x;
+      uint32_t n_s = seek(item_s), n_p = seek(item_p);
+      uint32_t s = 0, p = 0;       // step within the cursor's item
+      uint32_t gs = 0, gp = 0;     // steps issued so far by either cursor: ring slots and barrier phases
+      uint32_t q_items = 0;        // items whose scores have been started: phase of q_full
+      long long t_last = clock64();
+      while (n_p != 0) {
+        bool progress = false;
+        if (n_s != 0 && gs < gp + 3) {
+          const uint32_t ks = gs % kT1KStages, sb = gs % 3;
+          bool can = ready(&bars->k_full[ks], (gs / kT1KStages) & 1);
+          if (can && s == 0) can = ready(&bars->q_full, q_items & 1);
+          if (can && gs >= 3)   // the buffer's previous P has been consumed
+            can = ready(&bars->pv_done[sb], ((gs - 3) / 3) & 1);
+          if (can) {
+            ptx::tc_fence_after_sync();
+            const uint32_t kb = sk + ks * kTileBytes;
+#pragma unroll
+            for (int k16 = 0; k16 < kTile / 16; ++k16) {
+              const uint32_t off = (k16 >> 2) * kBlockBytes + (k16 & 3) * 32;
+              ptx::umma_f16(tg + sb * kTile, ptx::smem_desc_sw128(sq + off, 16, 1024),
+                            ptx::smem_desc_sw128(kb + off, 16, 1024), idesc_s, k16 != 0);
+            }
+            ptx::umma_commit(ptx::smem_u32(&bars->s_full[sb]));
+            ptx::umma_commit(ptx::smem_u32(&bars->k_empty[ks]));
+            ++gs;
+            if (++s == n_s) {   // Q is not read again: the producer may load the next item's
+              ptx::umma_commit(ptx::smem_u32(&bars->q_empty));
+              ++q_items;
+              s = 0;
+              item_s += gridDim.x;
+              n_s = seek(item_s);
+            }
+            progress = true;
+          }
+        }
+        if (gp < gs) {
+          const uint32_t vs = gp % kT1VStages, sb = gp % 3;
+          bool can = ready(&bars->v_full[vs], (gp / kT1VStages) & 1);
+#ifdef TSB_TUNING
+          if (P.tune_mode != 1)
+#endif
+          if (can) can = ready(&bars->p_full[sb], (gp / 3) & 1);
+          if (can) {
+            ptx::tc_fence_after_sync();
+            const uint32_t vb = sv + vs * kTileBytes;
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk) {
+              const uint64_t db = ptx::smem_desc_sw128(vb + kk * 2048, kBlockBytes, 1024);
+              ptx::umma_f16_ts(to, tg + sb * kTile + kk * 8, db, idesc_pv, (p ? 1u : 0u) | (uint32_t)kk);
+            }
+            ptx::umma_commit(ptx::smem_u32(&bars->pv_done[sb]));
+            ptx::umma_commit(ptx::smem_u32(&bars->v_empty[vs]));
+            ++gp;
+            if (++p == n_p) {
+              p = 0;
+              item_p += gridDim.x;
+              n_p = seek(item_p);
+            }
+            progress = true;
+          }
+        }
+        if (progress) {
+          t_last = clock64();
+        } else {
+          if (*abort_flag) break;
+          if (clock64() - t_last > kAttnWaitLimit) { *abort_flag = 1; break; }
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ softmax + output: one query row per thread
+    const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
+    const uint32_t row = quarter * 32 + lane;
+    const uint32_t tg = tmem_base + ((quarter * 32u) << 16), to = tg + 384;
+    const float c = P.scale_log2;
+    auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag,
+                                                            kAttnWaitLimit)) != 0;
+    };
+    uint32_t U = 0;   // steps processed in earlier items
+    bool ok = true;
+    // The finished item whose output is still in tensor memory.  It is written out after the
+    // probabilities of the next item's first step have been computed (the wait for the item's last
+    // P V product is hidden behind that arithmetic) and before they are announced: the next item's
+    // first P V product overwrites O.
+    bool pending = false;
+    uint32_t pend_last = 0;          // global index of the pending item's last step
+    float pend_inv = 0.f;
+    int64_t pend_grow = 0;
+    uint32_t pend_h = 0;
+    bool pend_row_ok = false;
+    auto write_output = [&]() -> bool {
+      // the last P V product (MMAs complete in order, so every earlier one has finished too)
+      if (!warp_wait(&bars->pv_done[pend_last % 3], (pend_last / 3) & 1)) return false;
+      ptx::tc_fence_after_sync();
+      uint32_t o[4][32];
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld_32x32(to + ch * 32, o[ch]);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        __half* dst = P.out + (int64_t)(2 * pend_h + (ch >> 1)) * P.stick_stride + pend_grow * kStickHalfs + (ch & 1) * 32;
+#pragma unroll
+        for (int v = 0; v < 4; v += 2) {
+          Vec8h ov[2];
+#pragma unroll
+          for (int w = 0; w < 2; ++w)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = (v + w) * 8 + 2 * e;
+              ov[w].h2[e] = __floats2half2_rn(__uint_as_float(o[ch][i]) * pend_inv, __uint_as_float(o[ch][i + 1]) * pend_inv);
+            }
+          if (pend_row_ok) ptx::st_global_v8(dst + v * 8, ov[0].u, ov[1].u);   // whole 32-byte sectors
+        }
+      }
+      ptx::tc_fence_before_sync();
+      pending = false;
+      return true;
+    };
+#ifdef TSB_TUNING
+    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long prof_start = clock64();
+    if (P.tune_mode == 1) ok = false;
+#endif
+    for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+      uint32_t qt, b, h;
+      if (!decode_unit_item(P, units, item, qt, b, h)) continue;
+      const uint32_t n = qt + 1;
+      float m = -1e30f, l = 0.f;
+      for (uint32_t u = 0; u < n; ++u) {
+        const uint32_t ug = U + u, buf = ug % 3, ts = tg + buf * kTile;
+        bool got_s;
+        ATTN_PROF(0, got_s = warp_wait(&bars->s_full[buf], (ug / 3) & 1));
+        if (!got_s) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        uint32_t r[4][32];
+#ifdef TSB_TUNING
+        const long long t_ld = clock64();
+#endif
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld_32x32(ts + ch * 32, r[ch]);
+        ptx::tmem_ld_wait();
+#ifdef TSB_TUNING
+        const long long t_max = clock64();
+        prof[1] += t_max - t_ld;
+#endif
+        if (u == qt) {   // diagonal tile: keys after the query do not exist
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if ((uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
+        }
+        float mx[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(r[ch][i]));
+        const float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
+                                     fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        if (u == 0) {
+          m = tile_max;   // key 0 exists for every query, so this is finite
+        } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
+          // raise the exponent offset (lazily): O and l shrink by alpha.  O must be at rest: the latest
+          // P V product is the one of the previous step.
+          if (!warp_wait(&bars->pv_done[(ug - 1) % 3], ((ug - 1) / 3) & 1)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const float m_new = fmaxf(m, tile_max);
+          const float alpha = ex2f((m - m_new) * c);
+          l *= alpha;
+          m = m_new;
+#pragma unroll 1
+          for (int ch = 0; ch < 4; ++ch) {
+            uint32_t o[32];
+            ptx::tmem_ld_32x32(to + ch * 32, o);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ptx::tmem_st_32x32(to + ch * 32, o);
+          }
+          ptx::tmem_st_wait();
+        }
+        const float mc = m * c;
+        float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#ifdef TSB_TUNING
+        const long long t_exp = clock64();
+        prof[2] += t_exp - t_max;
+#endif
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {   // 64 keys -> 32 packed columns at a time
+          uint32_t packed[32];
+#pragma unroll
+          for (int ch = 0; ch < 2; ++ch)
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+              const float p0 = ex2f(fmaf(__uint_as_float(r[hf * 2 + ch][i]), c, -mc));
+              const float p1 = ex2f(fmaf(__uint_as_float(r[hf * 2 + ch][i + 1]), c, -mc));
+              sum[(i >> 1) & 3] += p0 + p1;
+              const __half2 hp = __floats2half2_rn(p0, p1);
+              packed[ch * 16 + (i >> 1)] = *reinterpret_cast<const uint32_t*>(&hp);
+            }
+          ptx::tmem_st_32x32(ts + hf * 32, packed);   // P over the scores just read: keys 2c, 2c+1 in column c
+        }
+        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+#ifdef TSB_TUNING
+        const long long t_st = clock64();
+        prof[3] += t_st - t_exp;
+#endif
+        ptx::tmem_st_wait();
+        if (u == 0 && pending) {
+#ifdef TSB_TUNING
+          const long long t_fin = clock64();
+#endif
+          if (!write_output()) { ok = false; break; }
+#ifdef TSB_TUNING
+          prof[5] += clock64() - t_fin;
+#endif
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[buf]));
+#ifdef TSB_TUNING
+        prof[4] += clock64() - t_st;
+#endif
+      }
+      if (!ok) break;
+      U += n;
+      pending = true;
+      pend_last = U - 1;
+      pend_inv = 1.f / l;
+      pend_row_ok = qt * kTile + row < P.seq;
+      pend_grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
+      pend_h = h;
+    }
+    if (ok && pending) {
+#ifdef TSB_TUNING
+      const long long t_fin = clock64();
+#endif
+      write_output();
+#ifdef TSB_TUNING
+      prof[5] += clock64() - t_fin;
+#endif
+    }
+#ifdef TSB_TUNING
+    if (warp == 2 && lane == 0) {
+      for (int i = 0; i < 6; ++i) atomicAdd(&g_attn_prof[i], (unsigned long long)prof[i]);
+      atomicAdd(&g_attn_prof[7], (unsigned long long)(clock64() - prof_start));
+    }
+#endif
+  }
+
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kAttnTmemCols);
+  }
+  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
+}
+
 int g_attn_sm_count = 0;
 
 }  // namespace
@@ -1224,6 +1317,22 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
 #ifdef TSB_TUNING
   P.tune_mode = getenv("TS_ATTN_MODE") ? atoi(getenv("TS_ATTN_MODE")) : 0;
 #endif
+  int which_kernel = 0;   // 0: by shape
+#ifdef TSB_TUNING
+  if (getenv("TS_ATTN_KERNEL")) which_kernel = atoi(getenv("TS_ATTN_KERNEL"));
+#endif
+  if (q_tiles % 2 != 0 || which_kernel == 3) {
+    // one query tile per CTA
+    const int64_t sms = g_attn_sm_count > 0 ? g_attn_sm_count : 148;
+    P.heads_per_round = (uint32_t)std::min<int64_t>(sms / q_tiles, batch * heads);
+    const uint32_t grid1 = (uint32_t)std::min<int64_t>(items, sms);
+    const cudaError_t e3 = cudaFuncSetAttribute(attention_causal_tmem_kernel,
+                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kT1Smem);
+    if (e3 != cudaSuccess) { note_cuda_error(e3); return TS_ERR_CUDA; }
+    attention_causal_tmem_kernel<<<grid1, kT1Threads, kT1Smem, (cudaStream_t)stream>>>(mq, mk, mv, P);
+    TSB_CHECK_LAUNCH();
+    return TS_OK;
+  }
   if (q_tiles % 2 == 0) {
     // two query tiles per CTA
     const int64_t pair_items = items / 2, pairs = q_tiles / 2;
@@ -1232,7 +1341,7 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
     // every SM gets a CTA: those beyond heads_per_round * pairs are the spares of pair_layout()
     const uint32_t grid2 = (uint32_t)std::min<int64_t>(pair_items, sms);
 #ifdef TSB_TUNING
-    if (getenv("TS_ATTN_KERNEL") && atoi(getenv("TS_ATTN_KERNEL")) == 1) {   // experiment: P through shared memory
+    if (which_kernel == 1) {   // experiment: P through shared memory
       const cudaError_t e1 = cudaFuncSetAttribute(attention_causal_pair_kernel,
                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, kPairAttnSmem);
       if (e1 != cudaSuccess) { note_cuda_error(e1); return TS_ERR_CUDA; }
@@ -1248,13 +1357,7 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
     TSB_CHECK_LAUNCH();
     return TS_OK;
   }
-  const cudaError_t e = cudaFuncSetAttribute(attention_causal_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
-  if (e != cudaSuccess) { note_cuda_error(e); return TS_ERR_CUDA; }
-  const uint32_t grid = (uint32_t)std::min<int64_t>(items, g_attn_sm_count > 0 ? g_attn_sm_count : 148);
-  attention_causal_kernel<<<grid, kAttnThreads, kAttnSmem, (cudaStream_t)stream>>>(mq, mk, mv, P);
-  TSB_CHECK_LAUNCH();
-  return TS_OK;
+  return TS_ERR_UNSUPPORTED;   // not reached: every tile count is served above
 }
 
 // Synchronises the device and reports (and clears) the sticky error word the attention kernel

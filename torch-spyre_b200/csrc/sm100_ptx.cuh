@@ -297,6 +297,13 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
                : "memory");
 }
 
+// 32-byte global store (one whole sector): sm_100 has 256-bit vector stores.  `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* p, uint4 lo, uint4 hi) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+               "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w)
+               : "memory");
+}
+
 // ---- descriptors ----------------------------------------------------------------
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
 // Addresses and offsets are given in bytes.
