@@ -89,6 +89,25 @@ def layer_forward_fp32(x: torch.Tensor, w: dict, cfg: LayerConfig) -> torch.Tens
     return layer_forward(x.float(), {k: v.float() for k, v in w.items()}, cfg)
 
 
+def make_model_weights(cfg: LayerConfig, vocab: int, n_layers: int, seed: int = 0) -> dict:
+    """Seeded weights of a small model: embedding, `n_layers` layers, final norm, output projection."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    return {"embed": (torch.randn(vocab, cfg.d_model, generator=g)).half(),
+            "layers": [make_weights(cfg, seed=seed + 1 + i) for i in range(n_layers)],
+            "final_norm": (torch.randn(cfg.d_model, generator=g) * 0.02 + 1.0).half(),
+            "lm_head": (torch.randn(vocab, cfg.d_model, generator=g) * 0.02).half()}
+
+
+def model_forward(ids: torch.Tensor, mw: dict, cfg: LayerConfig, dtype=torch.float16) -> torch.Tensor:
+    """Token ids [batch, seq] -> logits [batch, seq, vocab]; every op in `dtype`, rounding after each."""
+    conv = (lambda t: t.to(dtype))
+    x = F.embedding(ids, conv(mw["embed"]))
+    for w in mw["layers"]:
+        x = layer_forward(x, {k: conv(v) for k, v in w.items()}, cfg)
+    x = rms_norm(x, conv(mw["final_norm"]), cfg.eps)
+    return F.linear(x, conv(mw["lm_head"]))
+
+
 def attention_forward(q, k, v, heads: int, scale: float):
     """Causal attention on packed [batch, seq, heads*head_dim] tensors, every op in q.dtype."""
     b, s, width = q.shape
