@@ -1046,7 +1046,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="all",
                     help="all (headline + every other configuration), or one of: fused " +
-                         " ".join(OTHER_CONFIGS + EXTRA_WORKLOADS))
+                         " ".join(OTHER_CONFIGS + EXTRA_WORKLOADS) + "; tp_llama_layer under torchrun")
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -1076,6 +1076,21 @@ def main():
         dist.init_process_group("nccl")     # no device_id: with spyre registered it is the process's accelerator type, not cuda
 
     run = Runner(args, rank, world, local, dev, dist)
+    if args.workload == "tp_llama_layer":      # the tensor-parallel layer alone (needs more than one rank)
+        if world < 2 or 32 % world:
+            raise SystemExit("tp_llama_layer runs under torchrun on 2, 4 or 8 ranks")
+        r = measure_tp(run)
+        if run.sampler:
+            run.sampler.stop()
+        if rank == 0:
+            line = {"metric": metric_name(r["unit"]), "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                    "higher_is_better": True, "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                    "config": {"workload": r["workload"], "sharding": r["sharding"],
+                               "l2": "activations and weights far larger than L2", "launch": "one host launch per step"}}
+            line.update({k: v for k, v in r.items() if k not in ("workload", "sharding")})
+            print(json.dumps(line))
+        dist.destroy_process_group()
+        return
     head_name = HEADLINE if args.workload == "all" else args.workload
     head = run.measure(head_name, cpu_budget=None if args.no_cpu_baseline else 12.0, e2e=not args.no_e2e)
     wl = head.pop("_wl")

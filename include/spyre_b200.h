@@ -384,6 +384,24 @@ int ts_gemm_error_state(void);
 int ts_gemm_f16_scatter_add(const void* a, const void* b, void* const* c_owner, int owners, int64_t M,
                             int64_t N, int64_t K, int b_kmajor, void* stream);
 
+/* The same reduce-scatter with plain peer stores instead of reductions: every tile of this rank's
+ * partial product is STORED into c_owner[r], which the caller points at this rank's own slot inside
+ * owner r's memory (owner r holds one [M / owners, N] image per writing rank).  Stores cross NVLink
+ * as whole 128-byte sticks at link rate where fp16 reductions do not; after a barrier each owner
+ * sums its slots locally with ts_sum_slots_f16, in fp32 with one rounding, so the result no longer
+ * depends on arrival order.  Same argument rules as ts_gemm_f16_scatter_add.
+ * Reference: none (single device, torch_spyre/__init__.py:87-89); the layer ladder of
+ * tests/test_modules.py:133-211 is the goal it serves. */
+int ts_gemm_f16_scatter_store(const void* a, const void* b, void* const* c_owner, int owners, int64_t M,
+                              int64_t N, int64_t K, int b_kmajor, void* stream);
+
+/* out = residual + sum of `n_slots` fp16 stick images (`slot_stride` elements apart, `n` elements
+ * each, n % 8 == 0), summed in fp32 and rounded to fp16 once; `residual` may be NULL.  The local
+ * half of the reduce-scatter above, and of the residual add that follows a row-parallel linear
+ * (x + linear(...), tests/test_modules.py:133-211). */
+int ts_sum_slots_f16(const void* slots, int n_slots, int64_t slot_stride, const void* residual, void* out,
+                     int64_t n, void* stream);
+
 /* The all-gather half of the same layer: a 2-D device-to-device copy on `stream` whose destination
  * (or source) may be a peer GPU's memory.  A rank's block of rows of a stick image is one
  * contiguous piece of `width` bytes per stick column, `height` of them, `spitch` / `dpitch` bytes

@@ -81,6 +81,7 @@ struct GemmParams {
   // buffers (this GPU's and its peers'), and a tile is added into its owner's buffer with
   // fp16x2 reductions instead of being stored.  owners == 0: plain stores into c.
   uint32_t owners, rows_per_owner;
+  uint32_t owner_store;   // 1: plain stores into the owners' buffers (each rank writes a slot of its own) instead of reductions
   __half* c_owner[8];
 };
 
@@ -167,7 +168,7 @@ __device__ __forceinline__ void store_stick(const GemmParams& P, const uint32_t 
 #ifdef TSB_TUNING
       if (P.tune_epi == 3) { if (v.u.x == 0x7fff7fffu) st_global_v4(dst, v.u); continue; }
 #endif
-      if (P.owners) red_add_v4(dst + (int64_t)rr * kStickHalfs, v.u);
+      if (P.owners && !P.owner_store) red_add_v4(dst + (int64_t)rr * kStickHalfs, v.u);
       else st_global_v4(dst + (int64_t)rr * kStickHalfs, v.u);
     }
   }
@@ -750,7 +751,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
                        const void* bias, const void* residual, void* c, int64_t c_stick_stride,
                        int64_t c_head_stride, int64_t heads, int64_t batch, int64_t M,
                        int64_t N, int64_t K, int b_kmajor, int b_batched, void* stream,
-                       int swiglu = 0, void* const* c_owner = nullptr, int owners = 0) {
+                       int swiglu = 0, void* const* c_owner = nullptr, int owners = 0, int owner_store = 0) {
   if ((uintptr_t)residual % 16) return TS_ERR_ALIGNMENT;
   if (owners) {
     if (owners < 1 || owners > 8 || !c_owner || residual || bias || swiglu || batch != 1 || heads != 1)
@@ -787,6 +788,7 @@ static int gemm_launch(const void* a, int64_t a_stick_stride, int64_t a_head_str
   P.c_stick_stride = c_stick_stride;
   P.c_head_stride = c_head_stride;
   P.owners = (uint32_t)owners;
+  P.owner_store = (uint32_t)owner_store;
   if (owners) {
     P.rows_per_owner = (uint32_t)(M / owners);
     P.c_stick_stride = (int64_t)P.rows_per_owner * kStickHalfs;   // every owner's buffer is the image of [M / owners, N]
@@ -945,6 +947,12 @@ extern "C" int ts_gemm_f16_scatter_add(const void* a, const void* b, void* const
                                        int64_t M, int64_t N, int64_t K, int b_kmajor, void* stream) {
   return gemm_launch(a, 0, 0, b, 0, 0, nullptr, nullptr, nullptr, 0, 0, 1, 1, M, N, K, b_kmajor, 0, stream, 0,
                      c_owner, owners);
+}
+
+extern "C" int ts_gemm_f16_scatter_store(const void* a, const void* b, void* const* c_owner, int owners,
+                                         int64_t M, int64_t N, int64_t K, int b_kmajor, void* stream) {
+  return gemm_launch(a, 0, 0, b, 0, 0, nullptr, nullptr, nullptr, 0, 0, 1, 1, M, N, K, b_kmajor, 0, stream, 0,
+                     c_owner, owners, 1);
 }
 
 extern "C" int ts_gemm_f16_swiglu(const void* a, const void* w_gate_up, void* c, int64_t batch,

@@ -47,3 +47,63 @@ extern "C" int ts_peer_copy_2d(void* dst, int64_t dpitch, const void* src, int64
   }
   return TS_OK;
 }
+
+namespace tsb {
+namespace {
+// out = residual + sum over slots of slot[s], eight fp16 at a time, summed in fp32 and rounded once.
+// Grid-stride over 16-byte vectors; the slots are equally spaced images of the same shape.
+__global__ void __launch_bounds__(256) sum_slots_kernel(const uint4* __restrict__ slots, int n_slots,
+                                                        int64_t slot_vecs, const uint4* __restrict__ residual,
+                                                        uint4* __restrict__ out, int64_t n_vecs) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vecs; i += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8];
+    Vec8h v;
+    if (residual) {
+      v.u = ld_stream_v4(residual + i);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(v.h2[e]);
+        acc[2 * e] = f.x;
+        acc[2 * e + 1] = f.y;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    }
+    for (int s = 0; s < n_slots; ++s) {
+      v.u = ld_stream_v4(slots + (int64_t)s * slot_vecs + i);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(v.h2[e]);
+        acc[2 * e] += f.x;
+        acc[2 * e + 1] += f.y;
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) v.h2[e] = __floats2half2_rn(acc[2 * e], acc[2 * e + 1]);
+    st_stream_v4(out + i, v.u);
+  }
+}
+}  // namespace
+}  // namespace tsb
+
+// The local half of a reduce-scatter done with plain peer stores (ts_gemm_f16_scatter_store):
+// `n_slots` fp16 stick images of one shape, `slot_stride` elements apart (one per rank that wrote
+// a partial product into this GPU's memory), are summed in fp32, the optional `residual` image
+// added, and the result rounded to fp16 once.  `n` elements per image, a multiple of 8 (whole
+// sticks always are); every pointer 16-byte aligned.
+extern "C" int ts_sum_slots_f16(const void* slots, int n_slots, int64_t slot_stride, const void* residual,
+                                void* out, int64_t n, void* stream) {
+  if (n < 0 || n_slots < 1 || n_slots > 64 || slot_stride < n) return TS_ERR_INVALID;
+  if (n == 0) return TS_OK;
+  if (!slots || !out) return TS_ERR_INVALID;
+  if (n % 8 || slot_stride % 8) return TS_ERR_UNSUPPORTED;
+  if (((uintptr_t)slots | (uintptr_t)out | (uintptr_t)residual) % 16) return TS_ERR_ALIGNMENT;
+  const int64_t vecs = n / 8;
+  const int64_t blocks = (vecs + 255) / 256;
+  const int grid = (int)(blocks < 148 * 8 ? blocks : 148 * 8);
+  tsb::sum_slots_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const uint4*)slots, n_slots, slot_stride / 8,
+                                                              (const uint4*)residual, (uint4*)out, vecs);
+  TSB_CHECK_LAUNCH();
+  return TS_OK;
+}

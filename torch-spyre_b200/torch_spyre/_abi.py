@@ -94,6 +94,9 @@ SIGNATURES = {
     "ts_peer_copy_2d": (ctypes.c_int, [vp, ctypes.c_int64, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp]),
     "ts_gemm_f16_scatter_add": (ctypes.c_int, [vp, vp, ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int, vp]),
+    "ts_gemm_f16_scatter_store": (ctypes.c_int, [vp, vp, ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int64,
+                                                 ctypes.c_int64, ctypes.c_int64, ctypes.c_int, vp]),
+    "ts_sum_slots_f16": (ctypes.c_int, [vp, ctypes.c_int, ctypes.c_int64, vp, vp, ctypes.c_int64, vp]),
     "ts_gemm_f16_swiglu": (ctypes.c_int, [vp, vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                           ctypes.c_int64, vp]),
     "ts_gemm_f16_residual": (ctypes.c_int, [vp, vp, vp, vp, vp, ctypes.c_int64, ctypes.c_int64,

@@ -420,6 +420,32 @@ def matmul_scatter_add(a: StickTensor, b: StickTensor, owner_ptrs: Sequence[int]
     _abi.check(rc, "ts_gemm_f16_scatter_add")
 
 
+def matmul_scatter_store(a: StickTensor, b: StickTensor, slot_ptrs: Sequence[int], b_kmajor: bool = True) -> None:
+    """Partial product a[M, K_local] @ b stored, block of rows by block of rows, at `slot_ptrs`: the
+    address, inside each owner's memory, of the [M / len(slot_ptrs), N] image reserved for this rank.
+    See ts_gemm_f16_scatter_store for what the caller has to order."""
+    M, K = a.shape[-2], a.shape[-1]
+    N = b.shape[-2] if b_kmajor else b.shape[-1]
+    rc = _abi.lib().ts_gemm_f16_scatter_store(a.ptr(), b.ptr(), _abi.ptrs(list(slot_ptrs)), len(slot_ptrs), M, N, K,
+                                              int(b_kmajor), _stream())
+    _abi.check(rc, "ts_gemm_f16_scatter_store")
+
+
+def sum_slots(slots: torch.Tensor, n_slots: int, shape: Sequence[int], residual: Optional[StickTensor] = None,
+              out: Optional[StickTensor] = None) -> StickTensor:
+    """Sum of `n_slots` stick images of `shape` lying back to back in `slots` (a flat fp16 CUDA tensor),
+    plus `residual`, in fp32 with one rounding."""
+    if out is None:
+        out = empty(tuple(shape), torch.float16, slots.device)
+    n = out.image.numel()
+    if slots.numel() < n_slots * n:
+        raise _abi.SpyreKernelError("sum_slots: the slot buffer is smaller than n_slots images")
+    rc = _abi.lib().ts_sum_slots_f16(slots.data_ptr(), n_slots, n, residual.ptr() if residual is not None else None,
+                                     out.ptr(), n, _stream())
+    _abi.check(rc, "ts_sum_slots_f16")
+    return out
+
+
 def swiglu_matmul(a: StickTensor, w_gate_up: StickTensor, out: Optional[StickTensor] = None) -> StickTensor:
     """silu(a @ Wg^T) * (a @ Wu^T) in one GEMM.  a: [..., M, K]; w_gate_up: [2*N, K], rows alternating
     between Wg and Wu in blocks of 64 (see ``interleave_gate_up``)."""

@@ -12,10 +12,13 @@ can be split over the GPUs of one box the Megatron way, with the activations sha
     -> RMSNorm -> all-gather -> column-parallel SwiGLU gate/up [M, f/R]
         -> row-parallel down_proj, reduce-scatter in the GEMM epilogue, + residual -> [M/R, d]
 
-The two reduce-scatters are not separate collectives: ``ts_gemm_f16_scatter_add`` adds every tile
-of the rank's partial product into the owning rank's result buffer over NVLink (plain vector
-reductions into peer memory) while the rest of the GEMM is still running, so per layer
-2 x [M, d] fp16 cross NVLink under the matmuls.  The all-gathers are peer copies of each rank's
+The two reduce-scatters are not separate collectives: ``ts_gemm_f16_scatter_store`` stores every
+tile of the rank's partial product into the rank's own slot in the owning rank's memory over NVLink
+(plain 16-byte stores covering whole sticks) while the rest of the GEMM is still running, so per
+layer 2 x [M, d] fp16 cross NVLink under the matmuls; the owner then sums its slots locally in
+fp32 (``ts_sum_slots_f16``, which also adds the residual).  (``ts_gemm_f16_scatter_add``, fp16
+reductions straight into one buffer per owner, is the same idea without the slots; reductions cross
+NVLink far below link rate, which made the layer slower on 8 GPUs than on 4.)  The all-gathers are peer copies of each rank's
 row block into every rank's full image (the copy engines, one 2-D copy per peer).  Buffers that
 peers write live in symmetric memory (``torch.distributed._symmetric_memory``); ordering between
 ranks is its device-side barrier on the current stream.  No TMA copy ever names a peer's memory.
@@ -120,15 +123,19 @@ class TPGroup:
 
 # ---- the sharded ops ------------------------------------------------------------------------------
 
-def all_gather_rows(tp: TPGroup, shard: StickTensor, full: PeerBuffer, rows_total: int) -> StickTensor:
+def all_gather_rows(tp: TPGroup, shard: StickTensor, full: PeerBuffer, rows_total: int,
+                    entry_barrier: bool = True) -> StickTensor:
     """Every rank's [rows, cols] block copied into every rank's image of [rows_total, cols].  In the
-    stick image a row block is one contiguous piece per stick column: a 2-D copy per peer."""
+    stick image a row block is one contiguous piece per stick column: a 2-D copy per peer.
+    `entry_barrier=False` when the caller knows that every rank has passed a barrier since it last
+    read `full` (its old contents are then dead everywhere)."""
     rows, cols = shard.rows, shard.cols
     sticks = -(-cols // STICK)
     width, spitch, dpitch = rows * 128, rows * 128, rows_total * 128
     off = tp.rank * rows * 128
     stream = torch.cuda.current_stream().cuda_stream
-    tp.barrier()          # every rank is done reading the previous contents of `full`
+    if entry_barrier:
+        tp.barrier()      # every rank is done reading the previous contents of `full`
     for peer in range(tp.world):
         rc = K._abi.lib().ts_peer_copy_2d(full.ptrs[peer] + off, dpitch, shard.ptr(), spitch, width, sticks, stream)
         K._abi.check(rc, f"ts_peer_copy_2d to rank {peer}")
@@ -136,22 +143,24 @@ def all_gather_rows(tp: TPGroup, shard: StickTensor, full: PeerBuffer, rows_tota
     return StickTensor(full.local[: sticks * rows_total * STICK], (rows_total, cols))
 
 
-def row_parallel_linear(tp: TPGroup, a: StickTensor, w_local: StickTensor, out: PeerBuffer,
-                        residual_shard: Optional[StickTensor]) -> StickTensor:
+def row_parallel_linear(tp: TPGroup, a: StickTensor, w_local: StickTensor, slots: PeerBuffer,
+                        residual_shard: Optional[StickTensor], entry_barrier: bool = True) -> StickTensor:
     """a: [M, K/R] (this rank's slice of the reduction dim), w_local: [N, K/R].  Returns this rank's
-    [M/R, N] block of a @ w^T summed over the ranks (+ residual_shard), which is `out.local`."""
+    [M/R, N] block of a @ w^T summed over the ranks (+ residual_shard).  `slots` holds, on every rank,
+    one [M/R, N] image per writing rank: the GEMM stores each block of rows of its partial product
+    into its own slot on the owning rank (whole sticks over NVLink, under the rest of the GEMM), and
+    after the barrier the owner adds its slots up locally in fp32."""
     M, N = a.rows, w_local.shape[0]
     rows = M // tp.world
-    n = (-(-N // STICK)) * rows * STICK
-    mine = out.local[:n]
-    if residual_shard is not None:
-        mine.copy_(residual_shard.image[:n])
-    else:
-        mine.zero_()
-    tp.barrier()          # every owner's buffer holds its starting value before anybody adds to it
-    K.matmul_scatter_add(a, w_local, out.ptrs, b_kmajor=True)
-    tp.barrier()          # every rank's additions have landed
-    return StickTensor(mine, (rows, N))
+    n = (-(-N // STICK)) * rows * STICK                 # elements of one slot
+    if slots.local.numel() < tp.world * n:
+        raise ValueError("slot buffer too small for one image per rank")
+    if entry_barrier:     # (not needed when every rank has passed a barrier since it last summed `slots`)
+        tp.barrier()      # every owner has finished adding up the slots of the previous call
+    mine = [slots.ptrs[owner] + tp.rank * n * 2 for owner in range(tp.world)]
+    K.matmul_scatter_store(a, w_local, mine, b_kmajor=True)
+    tp.barrier()          # every rank's stores have landed
+    return K.sum_slots(slots.local, tp.world, (rows, N), residual_shard)
 
 
 class TPDecoderLayer:
@@ -174,14 +183,19 @@ class TPDecoderLayer:
             raise ValueError("rows per rank must be a multiple of 32")
         self.rows = self.M // tp.world
         self.full = tp.buffer(self.M * self.d)                     # gathered activations [M, d]
-        self.out_a, self.out_b = tp.buffer(self.rows * self.d), tp.buffer(self.rows * self.d)
+        # one [rows, d] image per writing rank, for each of the two row-parallel linears
+        self.out_a, self.out_b = tp.buffer(tp.world * self.rows * self.d), tp.buffer(tp.world * self.rows * self.d)
         self.nvlink_bytes_per_call = 0
 
     def __call__(self, x_shard: StickTensor) -> StickTensor:
         tp, w = self.tp, self.w
         R = tp.world
+        # Four barriers per layer: one after each gather and one after each scatter.  The entry
+        # barriers of the helpers are not needed here: between a rank's last read of `full` (or its
+        # sum over a slot buffer) and the next write into it by any peer lies at least one of those
+        # four, and a barrier completes only when every rank's earlier work on its stream has.
         h = K.rmsnorm_rows(x_shard, w["norm1"], self.eps)
-        hf = all_gather_rows(tp, h, self.full, self.M)
+        hf = all_gather_rows(tp, h, self.full, self.M, entry_barrier=False)
         q = K.matmul(hf, w["q"], b_kmajor=True)
         k = K.matmul(hf, w["k"], b_kmajor=True)
         v = K.matmul(hf, w["v"], b_kmajor=True)
@@ -191,11 +205,12 @@ class TPDecoderLayer:
         k = K.rotary(StickTensor(k.image, shape3), self.cos, self.sin, self.batch, self.seq, self.heads_local)
         attn = K.causal_attention(q, k, StickTensor(v.image, shape3), self.batch, self.seq, self.heads_local,
                                   128 ** -0.5)
-        x2 = row_parallel_linear(tp, StickTensor(attn.image, (self.M, width)), w["o"], self.out_a, x_shard)
+        x2 = row_parallel_linear(tp, StickTensor(attn.image, (self.M, width)), w["o"], self.out_a, x_shard,
+                                 entry_barrier=False)
         h2 = K.rmsnorm_rows(x2, w["norm2"], self.eps)
-        hf2 = all_gather_rows(tp, h2, self.full, self.M)
+        hf2 = all_gather_rows(tp, h2, self.full, self.M, entry_barrier=False)
         act = K.swiglu_matmul(hf2, w["gate_up"])
-        y = row_parallel_linear(tp, act, w["down"], self.out_b, x2)
-        # bytes this rank sent to peers: two gathers of its block and two scatter-adds of its partial product
+        y = row_parallel_linear(tp, act, w["down"], self.out_b, x2, entry_barrier=False)
+        # bytes this rank sent to peers: two gathers of its block and two scatters of its partial product
         self.nvlink_bytes_per_call = 2 * (R - 1) * self.rows * self.d * 2 + 2 * (R - 1) * self.rows * self.d * 2
         return y
