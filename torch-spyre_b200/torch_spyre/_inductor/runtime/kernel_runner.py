@@ -48,7 +48,7 @@ class SpyreFusedKernelRunner:
         if given and len(given) != n_results:
             raise RuntimeError(f"{self.name}: expected {n_in} inputs and {n_results} outputs, got {len(tensors)} tensors")
         shapes = info.get("input_shapes") or [None] * n_in
-        with torch.cuda.device(like.device.index or 0):
+        with ops._with_device(like):
             # an operand is the buffer viewed with the shape its index expression walks
             sticks = [ops._st(t if s is None or tuple(t.shape) == tuple(s) else t.reshape(tuple(s)))
                       for t, s in zip(inputs, shapes)]

@@ -15,6 +15,8 @@ from __future__ import annotations
 
 from typing import List, Optional, Sequence, Tuple
 
+import contextlib
+
 import torch
 
 from . import _C, stick_ops as K
@@ -62,6 +64,22 @@ def _st(t: torch.Tensor) -> StickTensor:
     return st
 
 
+def _broadcast_shapes(*shapes) -> tuple:
+    """torch.broadcast_shapes for plain integer shapes (the torch function goes through symbolic-shape
+    guards and costs tens of microseconds per eager op)."""
+    rank = max((len(s) for s in shapes), default=0)
+    out = [1] * rank
+    for s in shapes:
+        off = rank - len(s)
+        for i, d in enumerate(s):
+            d = int(d)
+            if d != 1:
+                if out[off + i] not in (1, d):
+                    raise RuntimeError(f"shapes {[tuple(x) for x in shapes]} cannot be broadcast together")
+                out[off + i] = d
+    return tuple(out)
+
+
 def _new(shape: Sequence[int], like: torch.Tensor) -> torch.Tensor:
     return torch.empty(tuple(shape), dtype=like.dtype, device=like.device)
 
@@ -75,8 +93,15 @@ def _number(x) -> float:
     return float(x.item()) if isinstance(x, torch.Tensor) else float(x)
 
 
+_NO_SWITCH = contextlib.nullcontext()
+
+
 def _with_device(t: torch.Tensor):
-    return torch.cuda.device(t.device.index if t.device.index is not None else 0)
+    """Context in which the tensor's CUDA device is current (nothing to do when it already is)."""
+    index = t.device.index if t.device.index is not None else 0
+    if torch._C._cuda_getDevice() == index:
+        return _NO_SWITCH
+    return torch.cuda.device(index)
 
 
 # ---- pointwise -------------------------------------------------------------------------
@@ -121,7 +146,7 @@ def _binary(op: str, a, b, rop: Optional[str] = None, alpha=1) -> torch.Tensor:
         a, b, op = b, a, rop
     _check_fp16(a)
     shape_b = () if _is_number(b) else tuple(b.shape)
-    shape = torch.broadcast_shapes(tuple(a.shape), shape_b)
+    shape = _broadcast_shapes(tuple(a.shape), shape_b)
     out = _new(shape, a)
     if out.numel() == 0:
         return out
@@ -211,7 +236,7 @@ _impl("rsub.Scalar")(lambda a, b, alpha=1: _binary("SUB", _number(b), a, "RSUB",
 def _where(cond, a, b):
     _check_fp16(cond)
     like = cond
-    shape = torch.broadcast_shapes(tuple(cond.shape), () if _is_number(a) else tuple(a.shape),
+    shape = _broadcast_shapes(tuple(cond.shape), () if _is_number(a) else tuple(a.shape),
                                    () if _is_number(b) else tuple(b.shape))
     out = _new(shape, like)
     with _with_device(like):
