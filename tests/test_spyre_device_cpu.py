@@ -61,3 +61,17 @@ def test_eager_ops_are_registered():
     for must in ("add.Tensor", "mul.Tensor", "exp", "_softmax", "native_layer_norm", "mm", "bmm",
                  "addmm", "sum.dim_IntList", "mean.dim", "fill_.Scalar", "clone", "where.self"):
         assert must in names, must
+
+
+def test_plain_shape_broadcast_matches_torch():
+    """The eager ops broadcast operand shapes without torch's symbolic-shape machinery."""
+    import pytest
+
+    from torch_spyre.ops import _broadcast_shapes
+
+    cases = [((3, 1), (1, 4)), ((5,), (2, 1, 5)), ((), (3,)), ((0, 3), (1, 3)), ((2, 3), (2, 3)), ((7, 1, 1), (1, 6, 5)),
+             ((), ())]
+    for shapes in cases:
+        assert _broadcast_shapes(*shapes) == tuple(torch.broadcast_shapes(*shapes)), shapes
+    with pytest.raises(RuntimeError):
+        _broadcast_shapes((2, 3), (4, 3))
