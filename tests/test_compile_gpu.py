@@ -119,3 +119,36 @@ def test_routes_and_fallback():
     rec = compiler.last_compiled[-1]
     assert rec.route == "inductor" and len(rec.kernel_specs) == 1
     assert abs(rec.kernel_specs[0].op_info["reduce_scale"] - 1 / 256) < 1e-9
+
+
+# ---- the cases the reference lists but skips or comments out, and its transposes ----------------
+# (tests/_inductor/test_inductor_ops.py:104,117,183 "3d input causes eager timeout"; :189-197
+#  "skipping these - not working yet"; :198-218 transposes; :219-238 where)
+
+@pytest.mark.parametrize("op", ["abs", "exp", "relu", "tanh"])
+def test_unary_3d(op):
+    check(getattr(torch, op), rnd(67, 71, 256))
+
+
+@pytest.mark.parametrize("op", [torch.add, torch.mul, torch.sub, torch.div])
+def test_binary_3d(op):
+    check(op, rnd(67, 71, 256, positive=True), rnd(67, 71, 256, seed=1, positive=True))
+
+
+@pytest.mark.parametrize("dim", [0, 1, 2])
+def test_reduce_3d(dim):
+    check(lambda x: torch.sum(x, dim), rnd(67, 71, 256), atol=3e-2)     # sums of 67..256 terms of N(0,1) in fp16
+    check(lambda x: torch.amax(x, dim), rnd(67, 71, 256))
+
+
+def test_transposes_compiled():
+    check(lambda x: x.t().contiguous() + 1.0, rnd(1088, 320))
+    check(lambda x: x.transpose(0, 2).contiguous(), rnd(512, 256, 128, positive=True))
+    check(lambda x: x.transpose(1, 2).contiguous() * 2.0, rnd(512, 256, 128, positive=True))
+
+
+@pytest.mark.parametrize("cond", [lambda x, y: x == y, lambda x, y: x >= y])
+def test_where_1d(cond):
+    x, y = rnd(256), rnd(256, seed=1)
+    y[::3] = x[::3]           # some equal elements
+    check(lambda x, y: torch.where(cond(x, y), x, y * 2.0), x, y)
