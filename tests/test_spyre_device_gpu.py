@@ -432,3 +432,38 @@ def test_reference_custom_ops_on_the_device():
     scaled = torch.ops.spyre.layernormscale(stats, 1e-5)
     got = torch.ops.spyre.layernormnorm(xs, stats, scaled, ws, bs)
     assert_close(got.cpu(), ref, atol=1e-2)
+
+
+def test_cases_the_reference_skips():
+    """tests/test_ops.py of the reference, the cases it carries under @unittest.skip ("Swapping
+    stick dimension is unsupported", "matmuls have some issues with shapes", "mean will fail"),
+    with its own inputs: transposes and permutes of small tensors, adds of transposed operands, mm /
+    bmm / matmul in every operand order of a 3 x 5 x 7 problem, mean over either dim."""
+    h = torch.float16
+    x = torch.tensor([[1, -2, 3], [4, 5, 6]], dtype=h)
+    assert torch.equal(x.to(DEV).t().cpu(), x.t())                                   # test_t_2d
+    assert torch.equal(x.to(DEV).transpose(0, 1).cpu(), x.transpose(0, 1))           # test_transpose_2d
+    assert torch.equal(x.to(DEV).permute(1, 0).cpu(), x.permute(1, 0))               # test_permute_2d
+    x3 = torch.tensor([[[1, -2, 3], [4, 5, 6]], [[7, 8, 9], [10, 11, 12]]], dtype=h)
+    assert torch.equal(x3.to(DEV).transpose(0, 1).cpu(), x3.transpose(0, 1))         # test_transpose_3d
+    a, b = torch.tensor([1, 2, 3], dtype=h), torch.tensor([4, 5, 6], dtype=h)
+    assert torch.equal(torch.add(a.to(DEV), b.to(DEV)).cpu(), a + b)                 # test_add_Tensor
+    p, q = torch.arange(8, dtype=h).view(2, 4), torch.arange(8, dtype=h).view(4, 2) * 10
+    ps, qs = p.to(DEV), q.to(DEV)                                                    # test_add_Tensor_transpose
+    assert torch.equal(torch.add(ps, qs.t().contiguous()).cpu(), p + q.t())
+    assert torch.equal(torch.add(ps.t().contiguous(), qs).cpu(), p.t() + q)
+    A, B, C = 3, 5, 7
+    for (m, k, n) in ((A, B, C), (A, C, B), (B, A, C), (B, C, A), (C, A, B), (C, B, A)):   # test_mm_*
+        u = torch.arange(m * k, dtype=h).view(m, k)
+        v = torch.arange(k * n, dtype=h).view(k, n)
+        assert_close(torch.mm(u.to(DEV), v.to(DEV)).cpu(), torch.mm(u, v), rtol=1e-3, atol=1e-3)
+    for (m, k, n) in ((A, B, C), (C, B, A)):                                         # test_bmm_*, test_matmul_*
+        u = torch.arange(m * k, dtype=h).view(1, m, k)
+        v = torch.arange(k * n, dtype=h).view(1, k, n)
+        assert_close(torch.bmm(u.to(DEV), v.to(DEV)).cpu(), torch.bmm(u, v), rtol=1e-3, atol=1e-3)
+        assert_close(torch.matmul(u.to(DEV), v[0].to(DEV)).cpu(), torch.matmul(u, v[0]), rtol=1e-3, atol=1e-3)
+    y = torch.tensor([[[1, 2, 3], [4, 5, 6]]], dtype=h)                              # test_mean
+    ys = y.to(DEV)
+    assert_close(torch.mean(ys, dim=[0]).cpu(), torch.mean(y, dim=[0]))
+    assert_close(torch.mean(ys, dim=[1]).cpu(), torch.mean(y, dim=[1]))
+    assert_close(torch.mean(ys, dim=[0], keepdim=True).cpu(), torch.mean(y, dim=[0], keepdim=True))
