@@ -1,0 +1,68 @@
+"""Module tests of the reference that it carries as skipped (tests/test_modules.py:43-131), moved
+to the spyre device eagerly, unmodified: nn.Linear, transformers' RobertaSelfAttention and
+RobertaLayer with the reference's sizes (hidden 144, 12 heads of 12: nothing is a multiple of a
+stick).  Oracle: the same module on CPU; the layer, a dozen fp16 ops deep, against an fp32
+evaluation as well (the device may be at most 1.5 times as far from it as CPU fp16 eager is)."""
+import copy
+
+import pytest
+import torch
+import torch.nn as nn
+
+import torch_spyre  # noqa: F401
+from oracle import math_ref
+from oracle.math_ref import assert_close
+
+transformers = pytest.importorskip("transformers")
+pytestmark = pytest.mark.gpu
+DEV = "spyre"
+H = torch.float16
+
+
+@pytest.fixture(autouse=True)
+def _need_gpu(cuda):
+    yield
+
+
+def test_linear_module():
+    torch.manual_seed(0)
+    m = nn.Linear(3, 5, dtype=H)
+    ms = copy.deepcopy(m).to(DEV)
+    x = torch.arange(6, dtype=H).view(2, 3)
+    with torch.no_grad():
+        assert_close(ms(x.to(DEV)).cpu(), m(x))
+
+
+def _first(y):
+    return y[0] if isinstance(y, (tuple, list)) else y
+
+
+def _roberta(cls, shape):
+    from transformers import RobertaConfig
+
+    torch.manual_seed(0)
+    cfg = RobertaConfig()
+    cfg.hidden_size = 144
+    m = cls(cfg).eval().to(H)
+    ms = copy.deepcopy(m).to(DEV)
+    x = torch.rand(*shape, cfg.hidden_size, dtype=H)
+    with torch.no_grad():
+        cpu16 = _first(m(x))
+        got = _first(ms(x.to(DEV))).cpu()
+        truth = _first(copy.deepcopy(m).float()(x.float()))
+    return got, cpu16, truth
+
+
+def test_roberta_self_attention():
+    from transformers.models.roberta.modeling_roberta import RobertaSelfAttention
+
+    got, cpu16, _ = _roberta(RobertaSelfAttention, (2, 10))
+    assert_close(got, cpu16)
+
+
+def test_roberta_layer():
+    from transformers.models.roberta.modeling_roberta import RobertaLayer
+
+    got, cpu16, truth = _roberta(RobertaLayer, (2, 10))
+    assert got.shape == cpu16.shape
+    math_ref.assert_no_worse_than_cpu_fp16(got, cpu16, truth, what="RobertaLayer")
