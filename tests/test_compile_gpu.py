@@ -152,3 +152,50 @@ def test_where_1d(cond):
     x, y = rnd(256), rnd(256, seed=1)
     y[::3] = x[::3]           # some equal elements
     check(lambda x, y: torch.where(cond(x, y), x, y * 2.0), x, y)
+
+
+# ---- the reference's building blocks with its own sizes (tests/_inductor/test_building_blocks.py) --
+
+def test_reference_softplus_form():
+    """:38-66: softplus written with full-shape parameter tensors."""
+    def softplus(x, beta, threshold, one, minus):
+        bx = beta * x
+        return torch.where(bx >= threshold, x, torch.log(one + torch.exp(minus * abs(bx))) + F.relu(bx))
+
+    d, t = 64, 128
+    full = lambda v: torch.full([d, t], v, dtype=torch.float16)     # noqa: E731
+    check(softplus, rnd(d, t), full(1.0), full(20.0), full(1.0), full(-1.0))
+
+
+def test_reference_simple_attention():
+    """:68-89: 4 heads x 64 queries against 256 keys of width 128, the scale as a vector."""
+    q, k, v = rnd(4 * 64, 128), rnd(256, 128, seed=1), rnd(256, 128, seed=2)
+    scale = torch.tensor(1 / (128 ** 0.5), dtype=torch.float16).repeat(256)
+
+    def attn(q, k, v, sm_scale):
+        qk = q @ k.transpose(-1, -2).contiguous()
+        qk = qk * sm_scale
+        return qk.softmax(dim=-1) @ v
+
+    check(attn, q, k, v, scale)
+
+
+def test_reference_mlp():
+    """:91-118 (skipped there: "result divergent from CPU"): SwiGLU MLP, 256 x 1024 -> 4096 -> 1024
+    with Kaiming-uniform weights.  Three matmuls deep, so the device and CPU fp16 eager are both
+    measured against an fp32 evaluation."""
+    torch.manual_seed(SEED)
+    seq, emb = 256, 1024
+    x = torch.randn(seq, emb)
+    gate, up, down = torch.empty(emb, 4 * emb), torch.empty(emb, 4 * emb), torch.empty(4 * emb, emb)
+    for w in (gate, up, down):
+        torch.nn.init.kaiming_uniform_(w)
+
+    def mlp(x, gate, up, down):
+        return ((x @ up) * F.silu(x @ gate)) @ down
+
+    args16 = [t.half() for t in (x, gate, up, down)]
+    truth = mlp(*[t.float() for t in args16])
+    cpu16 = mlp(*args16)
+    got = torch.compile(mlp)(*[t.to(DEV) for t in args16]).cpu()
+    math_ref.assert_no_worse_than_cpu_fp16(got, cpu16, truth, what="mlp")
