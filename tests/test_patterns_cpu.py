@@ -154,3 +154,31 @@ def test_device_only_custom_ops_refuse_host_tensors():
         with pytest.raises(NotImplementedError):
             call()
     assert torch.equal(torch.ops.spyre.compact(x.reshape(-1, 1)), x)       # compact has no device restriction
+
+
+def test_fp32_softmax_idiom_becomes_the_fp16_softmax():
+    """softmax(x, dim, dtype=float32).to(float16) on an fp16 tensor (how attention code keeps the
+    reduction in fp32) is one fp16 softmax for the device, whose kernel computes in fp32 and rounds
+    once; an fp32 softmax with any other user is left alone."""
+    from torch.fx.experimental.proxy_tensor import make_fx
+
+    from torch_spyre._inductor import patterns
+
+    def wanted(x):
+        return torch.softmax(x, -1, dtype=torch.float32).to(torch.float16) * 2
+
+    gm = make_fx(wanted)(torch.randn(4, 8).half())
+    assert patterns.rewrite_aten_graph(gm) == 1
+    targets = [n.target for n in gm.graph.nodes if n.op == "call_function"]
+    assert torch.ops.aten._to_copy.default not in targets
+    sm = [n for n in gm.graph.nodes if n.op == "call_function" and n.target is torch.ops.aten._softmax.default]
+    assert len(sm) == 1 and sm[0].meta["val"].dtype == torch.float16
+    x = torch.randn(64, 200).half()
+    torch.testing.assert_close(gm(x), wanted(x), rtol=1e-3, atol=1e-5)
+
+    def shared(x):
+        s = torch.softmax(x, -1, dtype=torch.float32)
+        return s.to(torch.float16), s.sum()
+
+    gm2 = make_fx(shared)(torch.randn(4, 8).half())
+    assert patterns.rewrite_aten_graph(gm2) == 0

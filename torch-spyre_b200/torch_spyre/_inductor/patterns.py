@@ -257,11 +257,51 @@ def _match_swiglu(mul: Node):
     return None
 
 
+def _match_fp32_softmax(back: Node):
+    """softmax(x, dim, dtype=float32).to(float16) on an fp16 x, as model code writes it to keep the
+    reduction in fp32: _to_copy(fp16 -> fp32) -> _softmax -> _to_copy(-> fp16).  The device's fp16
+    softmax already computes in fp32 and rounds once at the end, which is exactly this."""
+    if not _is(back, aten._to_copy.default) or _dtype(back) != torch.float16 or not back.args:
+        return None
+    sm = back.args[0]
+    if not _is(sm, aten._softmax.default) or _dtype(sm) != torch.float32 or not _only_users(sm, back):
+        return None
+    if len(sm.args) < 3 or sm.args[2]:
+        return None
+    up = sm.args[0]
+    if not _is(up, aten._to_copy.default) or _dtype(up) != torch.float32 or not _only_users(up, sm):
+        return None
+    x = up.args[0]
+    if not isinstance(x, Node) or _dtype(x) != torch.float16:
+        return None
+    # only a dtype change on either side: no move to another device, no other layout, no copy semantics
+    here = x.meta["val"].device if isinstance(x.meta.get("val"), torch.Tensor) else None
+    for conv in (up, back):
+        for key, value in conv.kwargs.items():
+            if key == "dtype" or value is None or (key == "layout" and value == torch.strided) or \
+                    (key == "device" and here is not None and torch.device(value) == here) or \
+                    (key in ("non_blocking", "pin_memory") and not value):
+                continue
+            return None
+    return x, sm.args[1], [back, sm, up]
+
+
 def rewrite_aten_graph(gm: GraphModule) -> int:
     g = gm.graph
     count = 0
     for n in list(g.nodes):
         if n.op != "call_function" or not n.users and n.op != "output":
+            continue
+        hit = _match_fp32_softmax(n)
+        if hit is not None:
+            x, dim, dead = hit
+            with g.inserting_before(n):
+                new = g.call_function(aten._softmax.default, (x, dim, False))
+            new.meta = dict(n.meta)
+            n.replace_all_uses_with(new)
+            for d in dead:
+                g.erase_node(d)
+            count += 1
             continue
         hit = _match_swiglu(n)
         if hit is not None:
