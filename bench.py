@@ -44,6 +44,8 @@ MIN_TIMED_S = 0.050
 HEADLINE = "fused"
 OTHER_CONFIGS = ("softmax", "softmax_scaled", "relayout", "relayout_permuted", "bmm", "llama_layer",
                  "hf_llama_layer")
+SEQ_OVERRIDE = None      # --seq: sequence length of the attention workload (profiling aid: an odd number of
+                         # 128-row tiles runs the one-tile kernel)
 EXTRA_WORKLOADS = ("pointwise", "attention", "restickify")      # not part of the default line
 
 
@@ -228,7 +230,7 @@ def cpu_side(name: str, rank: int = 0, world: int = 1, rows=None, strong: bool =
                     sharding="the batch of 8 split over the ranks, weights replicated, no collective")
     if name == "attention":
         from oracle import llama_ref as LR
-        batch, seq, heads, hd = rows or shard(8, rank, world), 2048, 32, 128
+        batch, seq, heads, hd = rows or shard(8, rank, world), SEQ_OVERRIDE or 2048, 32, 128
         g = torch.Generator().manual_seed(rank)
         q, k, v = (torch.randn(batch, seq, heads * hd, generator=g).half() for _ in range(3))
         scale = 1.0 / math.sqrt(hd)
@@ -1055,8 +1057,12 @@ def main():
                     help="seconds of CPU work per secondary configuration's baseline")
     ap.add_argument("--rows", type=int, default=None,
                     help="profiling aid: leading extent of the workload (rows / outer / batch)")
+    ap.add_argument("--seq", type=int, default=None,
+                    help="profiling aid: sequence length of the attention workload (default 2048)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    global SEQ_OVERRIDE
+    SEQ_OVERRIDE = args.seq
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -109,7 +109,9 @@ __device__ __forceinline__ void unit_layout(const AttnParams& P, uint32_t units,
   const uint32_t bh_count = P.batch * P.heads;
   main_ctas = P.heads_per_round * units;
   const uint32_t full = bh_count / P.heads_per_round, rest = bh_count % P.heads_per_round;
-  spares_take_rest = rest != 0 && rest <= gridDim.x - main_ctas;
+  // (a spare CTA then does a whole slice, `units` items, while the others do `full` items each: only
+  // worth it when that is no more than their share)
+  spares_take_rest = rest != 0 && rest <= gridDim.x - main_ctas && units <= full;
   main_rounds = full + ((rest != 0 && !spares_take_rest) ? 1 : 0);
 }
 // `units` = work items per (batch, head) slice: tile pairs for the two-tile kernels, tiles for the
