@@ -1107,7 +1107,7 @@ def main():
             "config": config_block(wl, wl, args), "timed": head["timed"],
             "roofline": head["roofline"], "gpu_launches": head["gpu_launches"],
             "clocks": head.get("clocks"), "parity": head["parity"]}
-    for key in ("e2e", "cpu_baseline", "parity_detail"):
+    for key in ("e2e", "cpu_baseline", "parity_detail", "library_gemm"):
         if key in head:
             line[key] = head[key]
     del wl, head

@@ -291,6 +291,30 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, 
 }
 // Arrives (once the pair's MMAs issued so far have finished) on a barrier given by its
 // cluster address.
+// The same MMA keeping its A operand in the tensor core's collector buffer (`keep`: the next MMA
+// reads the same A) or taking it from there for the last time (`reuse`).
+__device__ __forceinline__ void umma_f16_pair_a_fill(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                     uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16.collector::a::fill [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair_a_lastuse(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16.collector::a::lastuse [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                    cluster_bar)
