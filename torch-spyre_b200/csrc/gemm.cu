@@ -42,7 +42,7 @@ constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;   // epilogue: 32 rows 
 constexpr int kSmemBytes = kStages * kStageBytes + kStagingBytes + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimit = 4000000000ll;  // ~2 s of SM clocks
-constexpr double kWideCost = 0.93;              // time of a 256 x 512 pair tile relative to two 256 x 256 ones
+constexpr double kWideCost = 0.80;              // time of a 256 x 512 pair tile relative to two 256 x 256 ones (measured 0.73-0.83)
 constexpr long long kDrainLimit = 200000ll;     // ~0.1 ms: far longer than a TMA copy is in flight
 
 __device__ int g_gemm_error;  // sticky: set when a bounded wait gave up
