@@ -242,3 +242,47 @@ def test_rms_norm(shape, cuda):
     assert_close(down(y), want_module)
     y = K.rmsnorm_rows(up(x, cuda), up(w, cuda), eps, False)
     assert_close(down(y), F.rms_norm(x, (shape[-1],), w, eps))
+
+
+def test_back_to_back_launches_keep_stream_order(cuda):
+    """The streaming kernels are launched so that a kernel may be placed on the SMs while the one
+    before it on the stream is still finishing; it must nevertheless see everything that one
+    wrote.  A ping-pong of dependent launches (pointwise -> pointwise -> row sum -> softmax of the
+    pointwise result), each reading what the previous one wrote into reused buffers, is enqueued
+    without any synchronisation and compared bit for bit with the same sequence run with a
+    device synchronisation after every launch."""
+    rows, cols = 4096, 4096
+    x = randn(rows, cols)
+    b = randn(cols, seed=SEED + 1)
+
+    def sequence(sync):
+        bufs = [K.empty((rows, cols), device=cuda), K.empty((rows, cols), device=cuda)]
+        cur = up(x, cuda)
+        sb = up(b, cuda)
+        sums = []
+        for i in range(6):
+            c = Chain()
+            c.emit("LOAD", c.tensor(cur)).emit("MUL", c.imm(0.5)).emit("ADD", c.tensor(sb)).store(0)
+            (cur,), _ = K.run_chain(c, (rows, cols), outputs=[bufs[i & 1]])
+            if sync:
+                torch.cuda.synchronize()
+            c2 = Chain()
+            c2.emit("LOAD", c2.tensor(cur)).emit("ABS")
+            _, r = K.run_chain(c2, (rows, cols), n_outputs=0, reduce="sum", reduce_scale=1.0 / cols)
+            if sync:
+                torch.cuda.synchronize()
+            sums.append(r)
+        y = K.softmax(cur, -1)
+        torch.cuda.synchronize()
+        return [down(s) for s in sums] + [down(y), down(cur)]
+
+    want = sequence(True)
+    for _ in range(5):
+        got = sequence(False)
+        for g, w in zip(got, want):
+            assert torch.equal(g.view(torch.int16), w.view(torch.int16))
+    # and the arithmetic itself, once
+    ref = x
+    for _ in range(6):
+        ref = ref * 0.5 + b
+    assert_close(want[-1], ref)

@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/spyre_b200.h"
 
@@ -38,6 +39,43 @@ struct FastDiv {
 };
 
 __host__ __device__ __forceinline__ int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// ---- programmatic dependent launch ---------------------------------------------------
+// A kernel launched with launch_after_tail() may be scheduled onto the SMs while the grid
+// before it on the stream is still finishing, so the launch latency and the placement of the
+// first CTAs overlap that grid's tail.  Such a kernel calls grid_dependency_wait() before it
+// touches global memory: the call returns once the earlier grid has completed and its writes
+// are visible, which keeps stream order exactly as without the attribute.  Both calls do
+// nothing in a kernel launched the ordinary way, and the launch falls back to ordinary
+// stream order after anything that is not a kernel or that never releases its dependents early.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_release_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+#ifdef TSB_TUNING
+inline bool tune_pdl_on() {
+  const char* e = getenv("TS_PDL");
+  return !e || e[0] != '0';
+}
+#endif
+
+template <class P, class A>
+inline cudaError_t launch_after_tail(void (*kernel)(P), uint32_t grid, uint32_t block, size_t smem,
+                                     cudaStream_t st, const A& arg) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(block, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+#ifdef TSB_TUNING
+  if (!tune_pdl_on()) cfg.numAttrs = 0;
+#endif
+  return cudaLaunchKernelEx(&cfg, kernel, arg);
+}
 
 inline int launch_status(cudaError_t e) { return e == cudaSuccess ? TS_OK : TS_ERR_CUDA; }
 

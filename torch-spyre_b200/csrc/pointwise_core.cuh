@@ -506,6 +506,8 @@ __device__ __forceinline__ void split_row(const Params& P, Item& it) {
 // ---- no reduction: items are the 16-byte vectors of the output image ----------
 template <class Prog, int U>
 __global__ void __launch_bounds__(kThreads) flat_kernel(const __grid_constant__ Params P) {
+  grid_dependency_wait();
+  grid_release_dependents();
   ItemCtx<U> ctx(P);
 #pragma unroll
   for (int u = 0; u < U; ++u) {
@@ -658,6 +660,8 @@ __host__ __device__ constexpr int prefetch_operand() {
 template <class Prog, int RED, int U, bool FULL, int RG, uint32_t CLS, int PF = -1>
 __global__ void __launch_bounds__(kThreads, (CLS == kClsAllGeneric ? 1 : 4)) rowred_kernel(const __grid_constant__ Params P) {
   __shared__ float part[8][4];
+  grid_dependency_wait();
+  grid_release_dependents();
   constexpr int kLastOp = code_op(Prog::template at<Prog::n - 1>());
   constexpr bool kFuseTail = is_unary_f32(kLastOp);
   constexpr int kPerGroup = U / RG;
@@ -982,7 +986,7 @@ void launch_stream(const Params& P, uint32_t blocks, cudaStream_t st) {
 template <class Prog, int RED, int U, uint32_t CLS = kClsAllGeneric>
 void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
   if constexpr (RED == TS_RED_NONE) {
-    flat_kernel<Prog, U><<<blocks, kThreads, 0, st>>>(P);
+    launch_after_tail(flat_kernel<Prog, U>, blocks, kThreads, 0, st, P);
   } else if constexpr (!Prog::kStatic) {
     rowred_dyn_kernel<RED, U><<<blocks, kThreads, 0, st>>>(P);
   } else {
@@ -1002,14 +1006,14 @@ void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
         // the streamed operand is loaded one step ahead: half the items per step, so that the
         // extra buffer still fits 64 registers (4 CTAs per SM); measured 8 % faster than the
         // wider step without the look-ahead on [8192, 8192]
-        rowred_kernel<Prog, RED, U, true, 2, CLS, kPF><<<grid, kThreads, 0, st>>>(P);
+        launch_after_tail(rowred_kernel<Prog, RED, U, true, 2, CLS, kPF>, grid, kThreads, 0, st, P);
       } else {
-        rowred_kernel<Prog, RED, 2 * U, true, 2, CLS><<<grid, kThreads, 0, st>>>(P);
+        launch_after_tail(rowred_kernel<Prog, RED, 2 * U, true, 2, CLS>, grid, kThreads, 0, st, P);
       }
     } else if (full) {
-      rowred_kernel<Prog, RED, U, true, 1, CLS><<<blocks, kThreads, 0, st>>>(P);
+      launch_after_tail(rowred_kernel<Prog, RED, U, true, 1, CLS>, blocks, kThreads, 0, st, P);
     } else {
-      rowred_kernel<Prog, RED, U, false, 1, CLS><<<blocks, kThreads, 0, st>>>(P);
+      launch_after_tail(rowred_kernel<Prog, RED, U, false, 1, CLS>, blocks, kThreads, 0, st, P);
     }
   }
 }

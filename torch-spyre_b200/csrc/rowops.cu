@@ -74,6 +74,8 @@ __device__ __forceinline__ float ex2_f(float x) {
 template <int K, int OP, bool FULL>
 __global__ void __launch_bounds__(kThreads) row_kernel(const __grid_constant__ RowParams P) {
   __shared__ float part[kWarps][4];
+  grid_dependency_wait();
+  grid_release_dependents();
   constexpr bool kSoft = OP == kSoftmax || OP == kLogSoftmax || OP == kCausalSoftmax;
   constexpr bool kCausal = OP == kCausalSoftmax;
   constexpr float kLog2e = 1.4426950408889634f;
@@ -250,8 +252,8 @@ int launch_rows(const RowParams& P0, cudaStream_t st) {
   const bool full = P.cols % 64 == 0 && P.nsticks % (1u << ws_log) == 0 &&
                     P.rows % (4 * (kWarps >> ws_log)) == 0;
 #define TSB_ROW_CASE(KK)                                                        \
-  if (full && per_thread == KK) row_kernel<KK, OP, true><<<blocks, kThreads, 0, st>>>(P); \
-  else row_kernel<KK, OP, false><<<blocks, kThreads, 0, st>>>(P)
+  if (full && per_thread == KK) launch_after_tail(row_kernel<KK, OP, true>, blocks, kThreads, 0, st, P); \
+  else launch_after_tail(row_kernel<KK, OP, false>, blocks, kThreads, 0, st, P)
   if (per_thread <= 1) { TSB_ROW_CASE(1); }
   else if (per_thread <= 2) { TSB_ROW_CASE(2); }
   else if (per_thread <= 4) { TSB_ROW_CASE(4); }
