@@ -304,7 +304,9 @@ def gpu_side(name: str, dev, cpu: dict):
         compiled = torch.compile(lambda t, u, v: torch.exp(t * u + v).sum(-1))
 
         def step_e2e():
-            return compiled(xp.to(spyre_dev), ap.to(spyre_dev), bp.to(spyre_dev)).cpu()
+            # pinned host tensors, so the copies may be queued without waiting for each one
+            return compiled(xp.to(spyre_dev, non_blocking=True), ap.to(spyre_dev, non_blocking=True),
+                            bp.to(spyre_dev, non_blocking=True)).cpu()
 
         wl.update(step_dev=step_dev, step_e2e=step_e2e, launches=1,
                   h2d=rows * cols * 2 + 2 * cols * 2, d2h=rows * 2, graph_period=ring,
@@ -380,7 +382,7 @@ def gpu_side(name: str, dev, cpu: dict):
 
         def step_e2e():
             # the calls a user makes: pinned host tensor -> spyre -> eager softmax -> pinned host tensor
-            return y_host.copy_(torch.softmax(xp.to(spyre_dev), -1))
+            return y_host.copy_(torch.softmax(xp.to(spyre_dev, non_blocking=True), -1))
 
         wl.update(step_dev=step_dev, step_e2e=step_e2e, launches=1, h2d=rows * cols * 2,
                   d2h=rows * cols * 2, graph_period=ring if rows == 256 else 0,

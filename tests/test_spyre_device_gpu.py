@@ -467,3 +467,22 @@ def test_cases_the_reference_skips():
     assert_close(torch.mean(ys, dim=[0]).cpu(), torch.mean(y, dim=[0]))
     assert_close(torch.mean(ys, dim=[1]).cpu(), torch.mean(y, dim=[1]))
     assert_close(torch.mean(ys, dim=[0], keepdim=True).cpu(), torch.mean(y, dim=[0], keepdim=True))
+
+
+def test_non_blocking_copy_from_pinned_memory():
+    """`.to("spyre", non_blocking=True)` from pinned memory queues the copy and returns, as torch's
+    CUDA copies do; work queued after it sees the data, and a pageable source still blocks."""
+    g = torch.Generator().manual_seed(7)
+    for shape in ((3,), (300, 200), (4096, 4096), (6, 1024, 1024)):
+        x = torch.randn(*shape, generator=g).half()
+        xp = x.pin_memory()
+        outs = []
+        for _ in range(3):   # back to back: the staging block and the copy stream are reused at once
+            d = xp.to(DEV, non_blocking=True)
+            outs.append(d + 1.0)
+        for o in outs:
+            assert torch.equal(o.cpu(), x + 1.0)
+        assert torch.equal(x.to(DEV, non_blocking=True).cpu(), x)     # pageable: an ordinary copy
+        d = torch.empty(shape, dtype=torch.float16, device=DEV)
+        d.copy_(xp, non_blocking=True)
+        assert torch.equal(d.cpu(), x)

@@ -187,7 +187,13 @@ at::Tensor view_in(const at::Tensor& raw, const at::Tensor& t) {
   return raw.view({-1}).as_strided(t.sizes(), t.strides(), t.storage_offset());
 }
 
-void host_to_device(const at::Tensor& src_cpu, const at::Tensor& dst) {
+// `non_blocking` is honoured for a pinned source, as torch's own CUDA copies do: the copies and
+// relayout kernels are queued on the current stream and the call returns; the caller keeps the
+// host buffer unchanged until the stream has passed that point.  (The staging block goes back to
+// the caching allocator at once: it is bound to the current stream, and every copy into it is
+// followed on that stream by the relayout kernel that consumes it, so later work on the stream
+// cannot see it early.)
+void host_to_device(const at::Tensor& src_cpu, const at::Tensor& dst, bool non_blocking) {
   StorageCtx* ctx = storage_ctx(dst);
   const c10::cuda::CUDAGuard guard(ctx->device);
   at::Tensor src = src_cpu.dim() == 0 && dst.dim() == 1 ? src_cpu.reshape({1}) : src_cpu;
@@ -217,8 +223,8 @@ void host_to_device(const at::Tensor& src_cpu, const at::Tensor& dst) {
                                   strides.data(), (int)shape.size(), lay.dsize, lay.dstride, lay.dmap,
                                   lay.ndev, st);
     }
-    // the host buffer and the staging block must outlive the copy
-    C10_CUDA_CHECK(cudaStreamSynchronize(st));
+    // the host buffer must outlive the copy: wait for it unless the caller took that on
+    if (!(non_blocking && rc == TS_OK && src_cpu.is_pinned())) C10_CUDA_CHECK(cudaStreamSynchronize(st));
     c10::cuda::CUDACachingAllocator::raw_delete(staging);
     check_status(rc, "copy host to device");
     return;
@@ -354,7 +360,7 @@ at::Tensor spyre_copy_from(const at::Tensor& self, const at::Tensor& dst, bool n
   TORCH_CHECK(self.scalar_type() == dst.scalar_type(),
               "Spyre backend does not support type conversion yet during copy.");
   if (self.is_cpu() && dst.is_privateuseone()) {
-    host_to_device(self, dst);
+    host_to_device(self, dst, non_blocking);
   } else if (self.is_privateuseone() && dst.is_cpu()) {
     device_to_host(self, dst);
   } else if (self.is_privateuseone() && dst.is_privateuseone()) {

@@ -645,7 +645,7 @@ def _to_copy(x, *, dtype=None, layout=None, device=None, pin_memory=None, non_bl
         converted = _convert_on_device(x, dtype)
         return converted if device == x.device else converted.to(device)
     out = torch.empty(x.shape, dtype=dtype, device=device)
-    out.copy_(x)
+    out.copy_(x, non_blocking=non_blocking)
     return out
 
 
