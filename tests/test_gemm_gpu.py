@@ -184,20 +184,21 @@ def test_scatter_add_epilogue_on_one_gpu(owners, m, k, n, cuda):
     assert lib.ts_gemm_f16_scatter_add(p, p, _abi.ptrs([0]), 1, 64, 64, 64, 1, None) == _abi.TS_ERR_ALIGNMENT
 
 
-@pytest.mark.parametrize("owners,m,k,n", [(2, 512, 256, 320), (4, 1024, 512, 256), (8, 2048, 384, 1024), (1, 256, 128, 128)])
-def test_scatter_store_epilogue_and_slot_sum_on_one_gpu(owners, m, k, n, cuda):
-    """The reduce-scatter with plain stores, every owner's slots on this GPU: two "ranks", each
-    holding half of K, store their partial products into their own slot of each owner's buffer; the
-    owners then add their two slots and the residual in fp32.  One rounding after the sum: the
+@pytest.mark.parametrize("owners,m,k,n,ranks", [(2, 512, 256, 320, 2), (4, 1024, 512, 256, 2), (8, 2048, 384, 1024, 2),
+                                                  (1, 256, 128, 128, 2), (8, 2048, 128, 512, 8), (4, 512, 64, 192, 4)])
+def test_scatter_store_epilogue_and_slot_sum_on_one_gpu(owners, m, k, n, ranks, cuda):
+    """The reduce-scatter with plain stores, every owner's slots on this GPU: `ranks` "ranks", each
+    holding a slice of K, store their partial products into their own slot of each owner's buffer;
+    the owners then add their slots and the residual in fp32.  One rounding after the sum: the
     result meets the default tolerance where the reduction form needs a looser one."""
     g = torch.Generator().manual_seed(32)
-    a = torch.randn(m, 2 * k, generator=g).half()
-    w = (torch.randn(n, 2 * k, generator=g) * 0.05).half()
+    a = torch.randn(m, ranks * k, generator=g).half()
+    w = (torch.randn(n, ranks * k, generator=g) * 0.05).half()
     res = torch.randn(m, n, generator=g).half()
-    rows, ranks = m // owners, 2
+    rows = m // owners
     slot = -(-n // 64) * rows * 64                       # elements of one [rows, n] image
     bufs = [torch.full((ranks * slot,), float("nan"), dtype=torch.float16, device=cuda) for _ in range(owners)]
-    for rank in range(ranks):     # the two ranks' launches, one after the other on this stream
+    for rank in range(ranks):     # the ranks' launches, one after the other on this stream
         sa = up(a[:, rank * k:(rank + 1) * k].contiguous(), cuda)
         sw = up(w[:, rank * k:(rank + 1) * k].contiguous(), cuda)
         K.matmul_scatter_store(sa, sw, [b.data_ptr() + rank * slot * 2 for b in bufs], b_kmajor=True)
@@ -207,11 +208,12 @@ def test_scatter_store_epilogue_and_slot_sum_on_one_gpu(owners, m, k, n, cuda):
     no_kernel_timeout()
     got = torch.cat([down(o) for o in outs], 0)
     partial = [(a[:, r * k:(r + 1) * k].float() @ w[:, r * k:(r + 1) * k].float().t()).half().float() for r in range(ranks)]
-    want = (res.float() + partial[0] + partial[1]).half()
+    total = sum(partial)
+    want = (res.float() + total).half()
     assert_close(got, want)
     # without a residual
     plain = K.sum_slots(bufs[0], ranks, (rows, n))
-    assert_close(down(plain), (partial[0] + partial[1])[:rows].half())
+    assert_close(down(plain), total[:rows].half())
     lib = _abi.lib()
     p = bufs[0].data_ptr()
     assert lib.ts_sum_slots_f16(p, 0, slot, None, p, slot, None) == _abi.TS_ERR_INVALID
