@@ -265,10 +265,6 @@ int ts_pointwise_chain(const ts_pw_insn* insns, int n_insns,
  * chain whose opcodes and operand selectors match one of them runs on it; any
  * other chain runs on the interpreter kernel).  No counterpart in the reference. */
 int ts_pointwise_static_count(void);
-/* Synchronises the device; returns 1 (and clears it) if a streamed pointwise or
- * reduction kernel gave up on a bounded wait for one of its bulk copies since the
- * last call, else 0.  No counterpart in the reference. */
-int ts_stream_error_state(void);
 
 /* ---- row-wise normalisations along the stick dim ---------------------------
  *

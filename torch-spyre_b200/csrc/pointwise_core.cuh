@@ -757,204 +757,6 @@ __global__ void __launch_bounds__(kThreads, (CLS == kClsAllGeneric ? 1 : 4)) row
   }
 }
 
-// ---- the same reduction with its full-shape inputs streamed by bulk async copies ----
-// Each warp owns a ring of kStages shared-memory stages.  One stage holds, for every
-// streamed tensor, kChunk chunks of 512 bytes: the warp's 4 rows x 128 bytes of one
-// stick column.  Lane 0 issues the copies (cp.async.bulk completing on an mbarrier),
-// so the number of bytes in flight does not depend on how the compiler schedules the
-// arithmetic, and a 512-byte request costs one instruction instead of 32.  Inputs
-// that are broadcast along rows (vectors) still come through ordinary cached loads.
-constexpr int kChunk = 4;          // stick columns per stage (= items per step)
-constexpr int kChunkBytes = 512;   // 4 rows x one stick
-constexpr int kMaxStreams = 2;
-// Measured slower than the register path on B200 for the benchmark shapes (more
-// instructions per byte); kept selectable for shapes where occupancy is the limit.
-constexpr bool kUseStreamKernels = false;
-
-static __device__ int g_stream_error;  // sticky: a bounded wait gave up (one copy per source file)
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                              uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-__device__ __forceinline__ void mbar_init1(uint32_t bar) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar));
-}
-__device__ __forceinline__ void mbar_expect(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-template <int NSTREAM>
-struct StreamCtx {
-  static constexpr int kPrefetch = -1;
-  const Params& P;
-  const __half* base[TS_PW_MAX_INPUTS];   // non-streamed tensors: as in RowCtx
-  int64_t sstride[TS_PW_MAX_INPUTS];
-  __half2 bval[TS_PW_MAX_INPUTS];
-  int slot[TS_PW_MAX_INPUTS];             // >= 0: index of the tensor's stream
-  int64_t out_base, out_stride;
-  uint32_t lv, lane, s[kChunk];
-  const uint8_t* stage;                   // current stage of this warp's ring
-
-  __device__ __forceinline__ StreamCtx(const Params& p, uint32_t row, uint32_t lane_id)
-      : P(p), lv(lane_id & 7), lane(lane_id), stage(nullptr) {
-    uint32_t i0 = 0, i1 = 0, i2 = 0;
-    if (p.need_index) {
-      uint32_t q;
-      p.div_d2.divmod(row, q, i2);
-      p.div_d1.divmod(q, i0, i1);
-    }
-    out_base = (int64_t)row * kStickHalfs + lv * 8;
-    out_stride = (int64_t)p.rows * kStickHalfs;
-    int next = 0;
-#pragma unroll
-    for (int t = 0; t < TS_PW_MAX_INPUTS; ++t) {
-      base[t] = nullptr;
-      sstride[t] = 0;
-      slot[t] = -1;
-      bval[t] = __float2half2_rn(0.f);
-      if (t < p.n_in) {
-        const TensorDesc& d = p.in[t];
-        if (d.flat) {
-          slot[t] = next++;
-        } else {
-          const uint32_t trow = i0 * (uint32_t)d.m0 + i1 * (uint32_t)d.m1 + i2 * (uint32_t)d.m2;
-          base[t] = d.ptr + (int64_t)trow * kStickHalfs + (d.col_bcast ? 0 : lv * 8);
-          sstride[t] = d.col_bcast ? 0 : d.stick_stride;
-          if (d.col_bcast) bval[t] = __half2half2(__ldg(base[t]));
-        }
-      }
-    }
-  }
-  __device__ __forceinline__ void tensor(int t, int u, V& v) const {
-    Vec8h x;
-    if (slot[t] >= 0) {
-      x.u = *reinterpret_cast<const uint4*>(stage + (slot[t] * kChunk + u) * kChunkBytes + lane * 16);
-    } else if (P.in[t].col_bcast) {
-      set_all(v, bval[t]);
-      return;
-    } else {
-      x.u = ld_global_v4(base[t] + (int64_t)s[u] * sstride[t]);
-    }
-#pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = x.h2[j];
-  }
-  __device__ __forceinline__ void store(int o, int u, const V& v) const {
-    Vec8h t;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) t.h2[j] = v[j];
-    st_global_v4(P.out[o] + out_base + (int64_t)s[u] * out_stride, t.u);
-  }
-};
-
-template <class Prog, int RED, int NSTREAM>
-__global__ void __launch_bounds__(kThreads) rowred_stream_kernel(const __grid_constant__ Params P) {
-  constexpr int kStages = 4 / NSTREAM;
-  constexpr int kStageBytes = NSTREAM * kChunk * kChunkBytes;
-  extern __shared__ __align__(128) uint8_t ring[];  // [8 warps][kStages][kStageBytes]
-  __shared__ uint64_t full[8][kStages];
-  __shared__ float part[8][4];
-  constexpr int kLastOp = code_op(Prog::template at<Prog::n - 1>());
-  constexpr bool kFuseTail = is_unary_f32(kLastOp);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int ws = 1 << P.ws_log;
-  const int ws_idx = warp & (ws - 1);
-  const uint32_t group = blockIdx.x * (8 >> P.ws_log) + (warp >> P.ws_log);
-  const uint32_t row0 = group * 4, row = row0 + (lane >> 3);
-  StreamCtx<NSTREAM> ctx(P, row, lane);
-  uint8_t* my_ring = ring + warp * (kStages * kStageBytes);
-  const uint32_t nsteps = P.nsticks / (ws * kChunk);   // stages this warp consumes in total
-
-  // streamed tensors' global bases for this warp's row group (lane 0 only needs them)
-  const __half* gsrc[NSTREAM];
-#pragma unroll
-  for (int k = 0; k < NSTREAM; ++k) gsrc[k] = nullptr;
-#pragma unroll
-  for (int t = 0; t < TS_PW_MAX_INPUTS; ++t)
-    if (t < P.n_in && ctx.slot[t] >= 0 && ctx.slot[t] < NSTREAM)
-      gsrc[ctx.slot[t]] = P.in[t].ptr + (int64_t)row0 * kStickHalfs;
-  const int64_t gstride = (int64_t)P.rows * kStickHalfs;
-
-  auto issue = [&](uint32_t step) {   // lane 0: fill stage (step % kStages) with step's chunks
-    const uint32_t st = step % kStages;
-    const uint32_t bar = smem_addr(&full[warp][st]);
-    mbar_expect(bar, kStageBytes);
-#pragma unroll
-    for (int k = 0; k < NSTREAM; ++k)
-#pragma unroll
-      for (int c = 0; c < kChunk; ++c) {
-        const uint32_t s = ws_idx + (step * kChunk + c) * ws;
-        bulk_copy_g2s(smem_addr(my_ring + st * kStageBytes + (k * kChunk + c) * kChunkBytes),
-                      gsrc[k] + (int64_t)s * gstride, kChunkBytes, bar);
-      }
-  };
-  if (lane == 0) {
-    for (int st = 0; st < kStages; ++st) mbar_init1(smem_addr(&full[warp][st]));
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    for (uint32_t step = 0; step < (uint32_t)kStages && step < nsteps; ++step) issue(step);
-  }
-  __syncwarp();
-
-  float partial = red_identity<RED>();
-  Regs<kChunk> R;
-  bool ok = true;
-  for (uint32_t step = 0; step < nsteps && ok; ++step) {
-    const uint32_t st = step % kStages, parity = (step / kStages) & 1;
-    const uint32_t bar = smem_addr(&full[warp][st]);
-    if (!mbar_test(bar, parity)) {
-      const long long t0 = clock64();
-      while (!mbar_test(bar, parity)) {
-        if (clock64() - t0 > 4000000000ll) { ok = false; break; }
-      }
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) break;
-    ctx.stage = my_ring + st * kStageBytes;
-#pragma unroll
-    for (int u = 0; u < kChunk; ++u) ctx.s[u] = ws_idx + (step * kChunk + u) * ws;
-    run_program<Prog, kChunk, (kFuseTail ? Prog::n - 1 : Prog::n)>(P, R, ctx);
-    // the stage has been read into registers: refill it with the step kStages ahead
-    __syncwarp();
-    if (lane == 0 && step + kStages < nsteps) {
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      issue(step + kStages);
-    }
-#pragma unroll
-    for (int u = 0; u < kChunk; ++u) {
-      float t = red_identity<RED>();
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float2 x = __half22float2(R.acc[u][j]);
-        if (kFuseTail) {
-          x.x = unary_f32(kLastOp, x.x);
-          x.y = unary_f32(kLastOp, x.y);
-        }
-        t = red_combine<RED>(t, red_combine<RED>(x.x, x.y));
-      }
-      partial = red_combine<RED>(partial, t);
-    }
-  }
-  if (!ok && lane == 0) atomicExch(&g_stream_error, 1);
-  finish_row<RED>(P, partial, row, true, lane, warp, ws, ws_idx, part);
-}
-
 // ---- registry of pre-instantiated programs ----------------------------------------
 using LaunchFn = void (*)(const Params&, uint32_t blocks, cudaStream_t);
 
@@ -974,15 +776,6 @@ inline bool rows_full(const Params& P, int U) {
   return P.cols % 64 == 0 && P.nsticks % (ws * U) == 0 && P.rows % (4 * (8 >> P.ws_log)) == 0;
 }
 
-template <class Prog, int RED, int NSTREAM>
-void launch_stream(const Params& P, uint32_t blocks, cudaStream_t st) {
-  constexpr int kBytes = 8 * 4 * kChunk * kChunkBytes;  // 8 warps x (stages x streams = 4) x 2 KiB
-  // per device and idempotent; cheap enough to repeat on every launch
-  cudaFuncSetAttribute(rowred_stream_kernel<Prog, RED, NSTREAM>,
-                       cudaFuncAttributeMaxDynamicSharedMemorySize, kBytes);
-  rowred_stream_kernel<Prog, RED, NSTREAM><<<blocks, kThreads, kBytes, st>>>(P);
-}
-
 template <class Prog, int RED, int U, uint32_t CLS = kClsAllGeneric>
 void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
   if constexpr (RED == TS_RED_NONE) {
@@ -990,15 +783,9 @@ void launch_instance(const Params& P, uint32_t blocks, cudaStream_t st) {
   } else if constexpr (!Prog::kStatic) {
     rowred_dyn_kernel<RED, U><<<blocks, kThreads, 0, st>>>(P);
   } else {
-    int nflat = 0;
-    for (int t = 0; t < P.n_in; ++t) nflat += P.in[t].flat ? 1 : 0;
     const bool full = rows_full(P, U);
     const uint32_t groups_per_block = 8u >> P.ws_log;
-    if (kUseStreamKernels && full && U == kChunk && nflat == 1) {
-      launch_stream<Prog, RED, 1>(P, blocks, st);
-    } else if (kUseStreamKernels && full && U == kChunk && nflat == 2) {
-      launch_stream<Prog, RED, 2>(P, blocks, st);
-    } else if (full && P.rows % (8 * groups_per_block) == 0) {
+    if (full && P.rows % (8 * groups_per_block) == 0) {
       // two row groups per warp step: operands broadcast along rows are fetched once for both
       constexpr int kPF = prefetch_operand<Prog, CLS>();
       const uint32_t grid = P.rows / (8 * groups_per_block);

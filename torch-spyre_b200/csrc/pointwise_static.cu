@@ -68,14 +68,3 @@ PW_REG(TS_RED_SUM, UR, LD0, enc(TS_PW_SUB, T, 1), enc(TS_PW_EXP))
 }  // namespace pw
 }  // namespace tsb
 
-// Synchronises the device and reports (and clears) the sticky word the streamed
-// kernels of this file set when a bounded wait on a bulk copy gave up.
-extern "C" int ts_stream_error_state(void) {
-  int v = 0;
-  if (cudaMemcpyFromSymbol(&v, tsb::pw::g_stream_error, sizeof(int)) != cudaSuccess) return TS_ERR_CUDA;
-  if (v) {
-    const int zero = 0;
-    cudaMemcpyToSymbol(tsb::pw::g_stream_error, &zero, sizeof(int));
-  }
-  return v;
-}

@@ -73,7 +73,6 @@ SIGNATURES = {
                                           ctypes.POINTER(vp), ctypes.c_int, c_i64p, ctypes.c_int,
                                           ctypes.c_float, vp, ctypes.c_int, ctypes.c_int64, vp]),
     "ts_pointwise_static_count": (ctypes.c_int, []),
-    "ts_stream_error_state": (ctypes.c_int, []),
     "ts_softmax_rows": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int, vp]),
     "ts_softmax_rows_causal": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                               ctypes.c_float, vp]),
