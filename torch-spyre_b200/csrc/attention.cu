@@ -69,31 +69,13 @@ __device__ __forceinline__ float ex2f(float x) {
 // ---- two query tiles per CTA -----------------------------------------------------------
 // For sequences of an even number of tiles.  A CTA takes the query tiles 2p ("A") and 2p+1 ("B")
 // of one (batch, head) together: they share every K / V tile, and each has its own group of
-// four softmax warps (one thread per query row), its own score buffer, output accumulator
-// and P tile.  While one group is in its exponentials the other one's waits and the MMAs of
-// both run underneath.
-//   tensor memory: S_A | S_B | O_A | O_B (4 x 128 columns)
-//   shared memory: Q_A Q_B | K (2 buffers) | V (1 buffer) | P_A P_B
-// Each group has its own MMA-issuing thread (warps 1 and 10), so that neither waits on the
-// other's softmax: S_x(t+1) is issued as soon as group x has taken S_x(t) into registers, and
-// P_x(t) V(t) as soon as P_x(t) has arrived.  K / V / Q buffers are released by both threads.
-// K tiles alternate between two buffers and V tiles use one, and the two streams are loaded by two
-// different threads of the TMA warp, each waiting only for its own buffers: a K buffer is
-// released as soon as both score products of its key tile have run (early in the step before the
-// one that needs the next tile in it), so K loads run two steps ahead; the V buffer is released
-// when both P V products of a step are done and its reload has the next step's softmax to hide
-// behind.  (One thread loading K and V in turn would hold every K load back behind the V buffer.)
+// four softmax warps (one thread per query row), its own score buffers and output accumulator.
+// While one group is in its exponentials the other one's waits and the MMAs of both run
+// underneath.  Each group has its own MMA-issuing thread (warps 1 and 10), so that neither waits
+// on the other's softmax; K and V are loaded by two different threads of the TMA warp, each
+// waiting only for its own buffers (one thread loading K and V in turn would hold every K load
+// back behind the V buffer).
 constexpr int kPairAttnThreads = 352;   // TMA warp, MMA warp A, 8 softmax warps, MMA warp B
-constexpr int kPairSmemTiles = 7;       // Q_A Q_B K0 K1 V P_A P_B
-[[maybe_unused]] constexpr int kPairAttnSmem = kPairSmemTiles * kTileBytes + 1024 /*align*/ + 256 /*barriers*/;
-
-struct PairAttnBars {
-  uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full, v_empty, s_full[2], s_empty[2], p_full[2],
-      pv_done[2];
-  uint32_t tmem_base;
-  int abort_flag;
-};
-static_assert(sizeof(PairAttnBars) <= 256, "barrier block outgrew its shared-memory reservation");
 
 // Work order of the two-tile kernel.  The grid is heads_per_round x (pairs per head) CTAs; in
 // round r CTA c works on (batch, head) slice r * heads_per_round + c / pairs and on tile pair
@@ -158,375 +140,11 @@ __device__ __forceinline__ bool decode_pair_item(const AttnParams& P, uint32_t i
   return decode_unit_item(P, P.q_tiles / 2, item, pr, b, h);
 }
 
-#ifdef TSB_TUNING   // kept for experiments only: the variant with P in shared memory
-__global__ void __launch_bounds__(kPairAttnThreads, 1)
-attention_causal_pair_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                             const __grid_constant__ CUtensorMap map_v, const __grid_constant__ AttnParams P) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t raw = ptx::smem_u32(smem_raw);
-  const uint32_t base = (raw + 1023u) & ~1023u;
-  uint8_t* gen_base = smem_raw + (base - raw);
-  const uint32_t sq = base, sk = sq + 2 * kTileBytes, sv = sk + 2 * kTileBytes, sp = sv + kTileBytes;
-  uint8_t* gen_p = gen_base + (sp - base);
-  PairAttnBars* bars = reinterpret_cast<PairAttnBars*>(gen_base + kPairSmemTiles * kTileBytes);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  volatile int* abort_flag = &bars->abort_flag;
-  const uint32_t num_items = pair_item_count(P);
-
-  if (threadIdx.x == 0) {
-    ptx::mbar_init(ptx::smem_u32(&bars->q_full), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 2);        // released by both MMA threads
-    ptx::mbar_init(ptx::smem_u32(&bars->v_full), 1);
-    ptx::mbar_init(ptx::smem_u32(&bars->v_empty), 2);          // released by both MMA threads
-    for (int i = 0; i < 2; ++i) {
-      ptx::mbar_init(ptx::smem_u32(&bars->k_full[i]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->k_empty[i]), 2);
-      ptx::mbar_init(ptx::smem_u32(&bars->s_full[i]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->s_empty[i]), 4);   // one arrival per softmax warp of the group
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[i]), 4);
-      ptx::mbar_init(ptx::smem_u32(&bars->pv_done[i]), 1);
-    }
-    bars->abort_flag = 0;
-    ptx::fence_barrier_init();
-    ptx::prefetch_tensormap(&map_q);
-    ptx::prefetch_tensormap(&map_k);
-    ptx::prefetch_tensormap(&map_v);
-  }
-  if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), kAttnTmemCols);
-    ptx::tmem_relinquish();
-  }
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  ptx::tc_fence_after_sync();
-  const uint32_t tmem_base = bars->tmem_base;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      // lane 0: the query tiles and the K stream
-      uint32_t kt = 0, item_n = 0;   // kt: key tiles loaded so far (K buffer and phase)
-      bool ok = true;
-      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
-        uint32_t pr, b, h;
-        if (!decode_pair_item(P, item, pr, b, h)) continue;
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_empty), (item_n & 1) ^ 1, abort_flag,
-                                    kAttnWaitLimit)) break;
-        const uint32_t qf = ptx::smem_u32(&bars->q_full);
-        ptx::mbar_arrive_expect_tx(qf, 2 * kTileBytes);
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {   // query tiles 2p (A) and 2p+1 (B)
-          const int qrow = (int)((2 * pr + x) * kTile);
-          ptx::tma_load_5d(sq + x * kTileBytes, &map_q, qf, 0, qrow, (int)b, (int)(2 * h), 0);
-          ptx::tma_load_5d(sq + x * kTileBytes + kBlockBytes, &map_q, qf, 0, qrow, (int)b, (int)(2 * h + 1), 0);
-        }
-        const uint32_t n = 2 * pr + 2;
-        for (uint32_t j = 0; j < n; ++j, ++kt) {
-          const uint32_t st = kt & 1, ph = (kt >> 1) & 1;
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->k_empty[st]), ph ^ 1, abort_flag,
-                                      kAttnWaitLimit)) { ok = false; break; }
-          const uint32_t kf = ptx::smem_u32(&bars->k_full[st]);
-          ptx::mbar_arrive_expect_tx(kf, kTileBytes);
-          ptx::tma_load_5d(sk + st * kTileBytes, &map_k, kf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
-          ptx::tma_load_5d(sk + st * kTileBytes + kBlockBytes, &map_k, kf, 0, (int)(j * kTile), (int)b,
-                           (int)(2 * h + 1), 0);
-        }
-      }
-      if (*abort_flag) {   // after an abort only: let copies in flight land before the CTA exits
-        for (uint32_t k = 0; k < (kt < 2u ? kt : 2u); ++k) {
-          const uint32_t t = kt - 1 - k;
-          ptx::mbar_wait_drain(ptx::smem_u32(&bars->k_full[t & 1]), (t >> 1) & 1, kAttnDrainLimit);
-        }
-        if (item_n > 0)
-          ptx::mbar_wait_drain(ptx::smem_u32(&bars->q_full), (item_n - 1) & 1, kAttnDrainLimit);
-      }
-    } else if (lane == 1) {
-      // lane 1: the V stream
-      uint32_t kt = 0;
-      bool ok = true;
-      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-        uint32_t pr, b, h;
-        if (!decode_pair_item(P, item, pr, b, h)) continue;
-        const uint32_t n = 2 * pr + 2;
-        for (uint32_t j = 0; j < n; ++j, ++kt) {
-          if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->v_empty), (kt & 1) ^ 1, abort_flag,
-                                      kAttnWaitLimit)) { ok = false; break; }
-          const uint32_t vf = ptx::smem_u32(&bars->v_full);
-          ptx::mbar_arrive_expect_tx(vf, kTileBytes);
-          ptx::tma_load_5d(sv, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h), 0);
-          ptx::tma_load_5d(sv + kBlockBytes, &map_v, vf, 0, (int)(j * kTile), (int)b, (int)(2 * h + 1), 0);
-        }
-      }
-      if (*abort_flag && kt > 0)
-        ptx::mbar_wait_drain(ptx::smem_u32(&bars->v_full), (kt - 1) & 1, kAttnDrainLimit);
-    }
-    __syncwarp();
-  } else if (warp == 1 || warp == 10) {
-    // ------------------------------------------------------------ MMA issuers: warp 1 for group A, warp 10 for B
-    if (lane == 0) {
-      const int x = warp == 1 ? 0 : 1;
-      const uint32_t idesc_s = ptx::idesc_f16_f32(kTile, kTile, 0, 0);
-      const uint32_t idesc_pv = ptx::idesc_f16_f32(kTile, kTile, 0, 1);
-      const uint32_t qb = sq + x * kTileBytes, pb = sp + x * kTileBytes;
-      uint32_t kt = 0, item_n = 0;   // key tiles of finished items; items done
-      uint32_t gs = 0, gp = 0;       // this group's score tiles / P V products issued so far
-#ifdef TSB_TUNING
-      long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      const long long prof_start = clock64();
-#endif
-      auto ready = [&](uint64_t* bar, uint32_t parity) { return ptx::mbar_test_wait(ptx::smem_u32(bar), parity); };
-      // S_x = Q_x K_t^T for global key tile t (the group uses it: has_work), then the K buffer is
-      // released on this thread's behalf.  Only called once the operands are there.
-      auto issue_scores = [&](uint32_t t, bool has_work) {
-        const uint32_t ks = t & 1;
-        if (has_work) {
-          ptx::tc_fence_after_sync();
-          const uint32_t kb = sk + ks * kTileBytes;
-#pragma unroll
-          for (int k16 = 0; k16 < kTile / 16; ++k16) {
-            const uint32_t off = (k16 >> 2) * kBlockBytes + (k16 & 3) * 32;
-            ptx::umma_f16(tmem_base + x * kTile, ptx::smem_desc_sw128(qb + off, 16, 1024),
-                          ptx::smem_desc_sw128(kb + off, 16, 1024), idesc_s, k16 != 0);
-          }
-          ptx::umma_commit(ptx::smem_u32(&bars->s_full[x]));
-          ++gs;
-        }
-        ptx::umma_commit(ptx::smem_u32(&bars->k_empty[ks]));
-      };
-      auto scores_ready = [&](uint32_t t, bool has_work) {
-#ifdef TSB_TUNING
-        if (P.tune_mode == 1) return ready(&bars->k_full[t & 1], (t >> 1) & 1);
-#endif
-        return ready(&bars->k_full[t & 1], (t >> 1) & 1) && (!has_work || ready(&bars->s_empty[x], (gs & 1) ^ 1));
-      };
-      bool ok = true;
-      for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x, ++item_n) {
-        uint32_t pr, b, h;
-        if (!decode_pair_item(P, item, pr, b, h)) continue;
-        const uint32_t n = 2 * pr + 2;          // key tiles loaded for the item
-        const uint32_t nx = n - 1 + x;          // key tiles this group uses (A stops one short)
-        if (!ptx::mbar_wait_bounded(ptx::smem_u32(&bars->q_full), item_n & 1, abort_flag, kAttnWaitLimit)) break;
-        // Per key tile j two things are issued: the scores of tile j + 1 and the P V product of tile
-        // j, whichever has its operands first (a tile this group does not use is still waited for
-        // and released).  The first tile's scores go before the loop.
-        uint32_t next_s = 0;   // next key tile of the item whose scores are to be issued
-        const long long t_item = clock64();
-#ifdef TSB_TUNING
-        prof[7] = t_item;
-#endif
-        for (uint32_t j = 0; ok && j < n;) {
-          bool progress = false;
-          if (next_s < n && next_s <= j + 1 && scores_ready(kt + next_s, next_s < nx)) {
-            issue_scores(kt + next_s, next_s < nx);
-            ++next_s;
-            if (next_s == nx) ptx::umma_commit(ptx::smem_u32(&bars->q_empty));   // Q_x is not read again
-            progress = true;
-          }
-          bool p_ready = j >= nx || ready(&bars->p_full[x], gp & 1);
-#ifdef TSB_TUNING
-          if (P.tune_mode == 1) p_ready = true;
-#endif
-          if (next_s > j && ready(&bars->v_full, (kt + j) & 1) && p_ready) {
-            if (j < nx) {
-              ptx::tc_fence_after_sync();
-#pragma unroll
-              for (int k16 = 0; k16 < kTile / 16; ++k16) {
-                const uint64_t da = ptx::smem_desc_sw128(pb + (k16 >> 2) * kBlockBytes + (k16 & 3) * 32, 16, 1024);
-                const uint64_t db = ptx::smem_desc_sw128(sv + k16 * 2048, kBlockBytes, 1024);
-                ptx::umma_f16(tmem_base + (2 + x) * kTile, da, db, idesc_pv, (j ? 1u : 0u) | (uint32_t)k16);
-              }
-              ptx::umma_commit(ptx::smem_u32(&bars->pv_done[x]));
-              ++gp;
-            }
-            ptx::umma_commit(ptx::smem_u32(&bars->v_empty));
-            ++j;
-            progress = true;
-          }
-          if (!progress) {
-            if (*abort_flag) { ok = false; break; }
-            if (clock64() - t_item > kAttnWaitLimit) { *abort_flag = 1; ok = false; break; }
-          }
-#ifdef TSB_TUNING
-          {   // attribute the time of a round without progress to the first thing that was missing
-            const long long now = clock64();
-            if (!progress) {
-              int why;
-              if (next_s > j) why = !ready(&bars->v_full, (kt + j) & 1) ? 2 : 3;
-              else why = !ready(&bars->k_full[(kt + next_s) & 1], ((kt + next_s) >> 1) & 1) ? 0 : 1;
-              prof[why] += now - prof[7];
-            }
-            prof[7] = now;
-          }
-#endif
-        }
-        kt += n;
-      }
-#ifdef TSB_TUNING
-      if (x == 0) {
-        for (int i = 0; i < 4; ++i) atomicAdd(&g_attn_prof[i], (unsigned long long)prof[i]);
-        atomicAdd(&g_attn_prof[4], (unsigned long long)(clock64() - prof_start));
-      }
-#endif
-    }
-    __syncwarp();
-  } else {
-    // ------------------------------------------------------------ softmax + output: group A = warps 2-5, B = 6-9
-    const uint32_t x = (uint32_t)(warp - 2) >> 2;   // group (warps 2-5: A, 6-9: B)
-    const uint32_t quarter = warp & 3;              // TMEM lane quarter this warp may read
-    const uint32_t row = quarter * 32 + lane;
-    const uint32_t lane_addr = tmem_base + ((quarter * 32u) << 16);
-    const uint32_t ts = lane_addr + x * kTile, to = lane_addr + (2 + x) * kTile;
-    const float c = P.scale_log2;
-    uint8_t* prow = gen_p + x * kTileBytes + row * 128;
-    auto warp_wait = [&](uint64_t* bar, uint32_t parity) -> bool {
-      return __all_sync(0xffffffffu, ptx::mbar_wait_bounded(ptx::smem_u32(bar), parity, abort_flag,
-                                                            kAttnWaitLimit)) != 0;
-    };
-    uint32_t g = 0;   // key tiles this group has processed (phases of s_full / p_full / pv_done)
-    bool ok = true;
-#ifdef TSB_TUNING
-    long long prof[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long prof_start = clock64();
-    if (P.tune_mode == 1) ok = false;
-#endif
-    for (uint32_t item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-      uint32_t pr, b, h;
-      if (!decode_pair_item(P, item, pr, b, h)) continue;
-      const uint32_t qt = 2 * pr + x, n = qt + 1;
-      float m = -1e30f, l = 0.f;
-      for (uint32_t j = 0; j < n; ++j, ++g) {
-        bool w_ok;
-        ATTN_PROF(5, w_ok = warp_wait(&bars->s_full[x], g & 1))
-        if (!w_ok) { ok = false; break; }
-        ptx::tc_fence_after_sync();
-        uint32_t r[4][32];
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) ptx::tmem_ld_32x32(ts + ch * 32, r[ch]);
-        ptx::tmem_ld_wait();
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->s_empty[x]));   // S_x may be overwritten
-        if (j == qt) {   // diagonal tile: keys after the query do not exist
-#pragma unroll
-          for (int ch = 0; ch < 4; ++ch)
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if ((uint32_t)(ch * 32 + i) > row) r[ch][i] = 0xff800000u;   // -inf
-        }
-        float mx[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) mx[i] = -INFINITY;
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) mx[i & 7] = fmaxf(mx[i & 7], __uint_as_float(r[ch][i]));
-        const float tile_max = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])),
-                                     fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
-        // The previous P V of this group has read the P tile about to be overwritten and is the
-        // last writer of O, which a rescale touches; it was issued a whole tile ago.
-        if (j > 0) {
-          bool w_ok2;
-          ATTN_PROF(6, w_ok2 = warp_wait(&bars->pv_done[x], (g - 1) & 1))
-          if (!w_ok2) { ok = false; break; }
-        }
-        if (j == 0) {
-          m = tile_max;
-        } else if (__any_sync(0xffffffffu, (tile_max - m) * c > kRescaleThreshold)) {
-          // raise the exponent offset (lazily, see the one-tile kernel): O and l shrink by alpha
-          ptx::tc_fence_after_sync();
-          const float m_new = fmaxf(m, tile_max);
-          const float alpha = ex2f((m - m_new) * c);
-          l *= alpha;
-          m = m_new;
-#pragma unroll 1
-          for (int ch = 0; ch < 4; ++ch) {
-            uint32_t o[32];
-            ptx::tmem_ld_32x32(to + ch * 32, o);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            ptx::tmem_st_32x32(to + ch * 32, o);
-          }
-          ptx::tmem_st_wait();
-        }
-        const float mc = m * c;
-        float sum[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t packed[16];
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2f(fmaf(__uint_as_float(r[ch][i]), c, -mc));
-            const float p1 = ex2f(fmaf(__uint_as_float(r[ch][i + 1]), c, -mc));
-            sum[(i >> 1) & 3] += p0 + p1;
-            const __half2 hp = __floats2half2_rn(p0, p1);
-            packed[i >> 1] = *reinterpret_cast<const uint32_t*>(&hp);
-          }
-          uint8_t* blk = prow + (ch >> 1) * kBlockBytes;
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            const uint32_t chunk = (uint32_t)((ch & 1) * 4 + v) ^ (row & 7);
-            *reinterpret_cast<uint4*>(blk + chunk * 16) =
-                make_uint4(packed[4 * v], packed[4 * v + 1], packed[4 * v + 2], packed[4 * v + 3]);
-          }
-        }
-        l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-        ptx::fence_proxy_async_smem();
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[x]));
-      }
-      if (!ok) break;
-      if (!warp_wait(&bars->pv_done[x], (g - 1) & 1)) break;
-      ptx::tc_fence_after_sync();
-      const float inv = 1.f / l;
-      const bool row_ok = qt * kTile + row < P.seq;
-      const int64_t grow = (int64_t)b * P.seq + (int64_t)qt * kTile + row;
-#pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
-        uint32_t o[32];
-        ptx::tmem_ld_32x32(to + ch * 32, o);
-        ptx::tmem_ld_wait();
-        __half* dst = P.out + (int64_t)(2 * h + (ch >> 1)) * P.stick_stride + grow * kStickHalfs +
-                      (ch & 1) * 32;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          Vec8h ov;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int i = v * 8 + 2 * e;
-            ov.h2[e] = __floats2half2_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
-          }
-          if (row_ok) st_global_v4(dst + v * 8, ov.u);
-        }
-      }
-      ptx::tc_fence_before_sync();
-    }
-#ifdef TSB_TUNING
-    if (warp == 2 && lane == 0) {
-      atomicAdd(&g_attn_prof[5], (unsigned long long)prof[5]);
-      atomicAdd(&g_attn_prof[6], (unsigned long long)prof[6]);
-      atomicAdd(&g_attn_prof[7], (unsigned long long)(clock64() - prof_start));
-    }
-#endif
-  }
-
-  ptx::tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 1) {
-    ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, kAttnTmemCols);
-  }
-  if (threadIdx.x == 0 && bars->abort_flag) atomicExch(&g_attn_error, 1);
-}
-
-#endif  // TSB_TUNING
-
 // ---- two query tiles per CTA, 64 keys at a time, probabilities in tensor memory ----------------
-// The kernel above keeps P in shared memory, which makes shared-memory bandwidth its limit: per
-// 128-key step the tensor cores read 256 KiB of operands, the softmax threads store 64 KiB of P and
-// TMA fills 64 KiB, 3000 cycles' worth at 128 B per clock for 2048 cycles of MMAs.  Here P never
-// touches shared memory: the softmax threads write it (fp16, two per 32-bit column) over the
+// Keeping P in shared memory makes shared-memory bandwidth the limit (per 128-key step the tensor
+// cores read 256 KiB of operands, the softmax threads store 64 KiB of P and TMA fills 64 KiB: 3000
+// cycles' worth at 128 B per clock for 2048 cycles of MMAs; that form measured 0.41 ms at the
+// benchmark shape and is no longer in the tree).  Here P never touches shared memory: the softmax threads write it (fp16, two per 32-bit column) over the
 // scores they have just read, and the P V product takes its A operand from tensor memory.  So that
 // scores can still be computed ahead of the softmax, a step is 64 keys: per group two 64-column
 // score buffers (S(u+1) is computed while the softmax works on S(u)) plus the 128-column output,
@@ -1342,16 +960,6 @@ extern "C" int ts_attention_causal_f16(const void* q, const void* k, const void*
     P.heads_per_round = (uint32_t)std::min<int64_t>(sms / pairs, batch * heads);
     // every SM gets a CTA: those beyond heads_per_round * pairs are the spares of pair_layout()
     const uint32_t grid2 = (uint32_t)std::min<int64_t>(pair_items, sms);
-#ifdef TSB_TUNING
-    if (which_kernel == 1) {   // experiment: P through shared memory
-      const cudaError_t e1 = cudaFuncSetAttribute(attention_causal_pair_kernel,
-                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, kPairAttnSmem);
-      if (e1 != cudaSuccess) { note_cuda_error(e1); return TS_ERR_CUDA; }
-      attention_causal_pair_kernel<<<grid2, kPairAttnThreads, kPairAttnSmem, (cudaStream_t)stream>>>(mq, mk, mv, P);
-      TSB_CHECK_LAUNCH();
-      return TS_OK;
-    }
-#endif
     const cudaError_t e2 = cudaFuncSetAttribute(attention_causal_pair64_kernel,
                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kP64Smem);
     if (e2 != cudaSuccess) { note_cuda_error(e2); return TS_ERR_CUDA; }
