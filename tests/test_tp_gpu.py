@@ -35,3 +35,12 @@ def test_sharded_layer_full_width_two_ranks(cuda):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     _run(2, 4096, 32, 11008, 1, 256, port=29617)
+
+
+def test_sharded_model_two_ranks(cuda):
+    """Token ids -> embedding -> three sharded decoder layers sharing their peer buffers -> final
+    norm -> logits (tensor_parallel.TPLlamaModel) on two ranks, against the unsharded CPU oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    out = _run(2, 512, 4, 1024, 2, 256, 1000, 3, port=29619)
+    assert "model layers=3" in out

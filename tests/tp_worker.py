@@ -21,6 +21,8 @@ def main():
 
     d_model, heads, ffn, batch, seq = (int(v) for v in sys.argv[1:6])
     cfg = L.LayerConfig(d_model=d_model, heads=heads, ffn=ffn)
+    if len(sys.argv) > 6:      # a whole model: vocabulary size and number of layers follow
+        return model_case(rank, world, cfg, batch, seq, int(sys.argv[6]), int(sys.argv[7]))
     w = L.make_weights(cfg)
     x = torch.randn(batch, seq, d_model, generator=torch.Generator().manual_seed(0)).half()
     cos, sin = L.rope_tables(seq, cfg.head_dim)
@@ -44,6 +46,36 @@ def main():
     if rank == 0:
         print(f"TP_OK world={world} nvlink_bytes_per_rank={layer.nvlink_bytes_per_call} "
               f"gpu_max={e['gpu_max']:.3e} cpu_max={e['cpu_max']:.3e} within_tol={e['frac_within_tol']:.4f}")
+    dist.destroy_process_group()
+
+
+def model_case(rank, world, cfg, batch, seq, vocab, n_layers):
+    """Token ids -> logits through TPLlamaModel against the unsharded CPU oracle, on this rank's rows."""
+    from oracle import llama_ref as L, math_ref
+    from torch_spyre import _abi, stick_ops as K, tensor_parallel as TP
+
+    mw = L.make_model_weights(cfg, vocab, n_layers)
+    ids = torch.randint(0, vocab, (batch, seq), generator=torch.Generator().manual_seed(3))
+    cos, sin = L.rope_tables(seq, cfg.head_dim)
+    tp = TP.TPGroup()
+    model = TP.TPLlamaModel(tp, mw, cfg.heads, cfg.eps, cos, sin, batch, seq)
+    rows = batch * seq // world
+    mine = ids.reshape(-1)[rank * rows:(rank + 1) * rows].contiguous().cuda()
+    for _ in range(2):          # twice: the layers share one set of peer buffers, reused from call to call
+        logits = model(mine)
+    got = K.from_sticks(logits).cpu()
+    torch.cuda.synchronize()
+    lib = _abi.lib()
+    assert lib.ts_gemm_error_state() == 0 and lib.ts_attention_error_state() == 0 and lib.ts_gather_error_state() == 0
+    assert got.shape == (rows, vocab)
+    cpu16 = L.model_forward(ids, mw, cfg).reshape(batch * seq, vocab)[rank * rows:(rank + 1) * rows]
+    truth = L.model_forward(ids, mw, cfg, dtype=torch.float32).reshape(batch * seq, vocab)[rank * rows:(rank + 1) * rows]
+    e = math_ref.assert_no_worse_than_cpu_fp16(got, cpu16, truth, factor=2.0, what=f"TP model rank {rank}")
+    ok = torch.tensor([1], device="cuda")
+    dist.all_reduce(ok)
+    if rank == 0:
+        print(f"TP_OK world={world} model layers={n_layers} gpu_max={e['gpu_max']:.3e} cpu_max={e['cpu_max']:.3e} "
+              f"within_tol={e['frac_within_tol']:.4f}")
     dist.destroy_process_group()
 
 

@@ -465,6 +465,24 @@ def swiglu_matmul(a: StickTensor, w_gate_up: StickTensor, out: Optional[StickTen
     return out
 
 
+# ---- row gather -----------------------------------------------------------------------
+
+def embedding_rows(table: StickTensor, ids: torch.Tensor) -> StickTensor:
+    """out[i, :] = table[ids[i], :] for the flattened `ids` (int32 or int64, contiguous, on the
+    table's GPU).  An index outside the table gives a row of zeros and raises the flag that
+    `ts_gather_error_state` reports."""
+    if len(table.shape) != 2:
+        raise _abi.SpyreKernelError("embedding_rows: the table must be 2-D")
+    if ids.dtype not in (torch.int32, torch.int64) or ids.device != table.image.device or not ids.is_contiguous():
+        raise _abi.SpyreKernelError("embedding_rows: ids must be contiguous int32 / int64 on the table's GPU")
+    vocab, dim = table.shape
+    out = empty((ids.numel(), dim), torch.float16, table.image.device)
+    rc = _abi.lib().ts_embedding_rows(table.ptr(), ids.data_ptr(), ids.element_size(), 0, 1, ids.numel(),
+                                      out.ptr(), vocab, dim, _stream())
+    _abi.check(rc, "ts_embedding_rows")
+    return out
+
+
 # ---- attention pieces -------------------------------------------------------------
 
 def rotary(x: StickTensor, cos: StickTensor, sin: StickTensor, batch: int, seq: int, heads: int,

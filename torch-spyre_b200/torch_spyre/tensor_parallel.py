@@ -168,7 +168,11 @@ class TPDecoderLayer:
     returns this rank's block of rows of the [batch * seq, d_model] activations."""
 
     def __init__(self, tp: TPGroup, weights: Dict[str, torch.Tensor], heads: int, eps: float,
-                 cos: torch.Tensor, sin: torch.Tensor, batch: int, seq: int):
+                 cos: torch.Tensor, sin: torch.Tensor, batch: int, seq: int, buffers=None):
+        """`buffers`: the (gathered activations, o-projection slots, down-projection slots) peer
+        buffers of another layer of the same shape, to share them.  That is safe for layers run
+        one after the other: a layer's first write into a peer's buffer comes after its first
+        barrier, which completes only when every rank has finished the layer before."""
         from ._inductor.customops import interleave_gate_up
 
         self.tp, self.eps, self.batch, self.seq = tp, eps, batch, seq
@@ -182,9 +186,13 @@ class TPDecoderLayer:
         if self.M % tp.world or (self.M // tp.world) % 32:
             raise ValueError("rows per rank must be a multiple of 32")
         self.rows = self.M // tp.world
-        self.full = tp.buffer(self.M * self.d)                     # gathered activations [M, d]
-        # one [rows, d] image per writing rank, for each of the two row-parallel linears
-        self.out_a, self.out_b = tp.buffer(tp.world * self.rows * self.d), tp.buffer(tp.world * self.rows * self.d)
+        if buffers is None:
+            # gathered activations [M, d]; one [rows, d] image per writing rank for each of the two
+            # row-parallel linears
+            buffers = (tp.buffer(self.M * self.d), tp.buffer(tp.world * self.rows * self.d),
+                       tp.buffer(tp.world * self.rows * self.d))
+        self.buffers = buffers
+        self.full, self.out_a, self.out_b = buffers
         self.nvlink_bytes_per_call = 0
 
     def __call__(self, x_shard: StickTensor) -> StickTensor:
@@ -214,3 +222,35 @@ class TPDecoderLayer:
         # bytes this rank sent to peers: two gathers of its block and two scatters of its partial product
         self.nvlink_bytes_per_call = 2 * (R - 1) * self.rows * self.d * 2 + 2 * (R - 1) * self.rows * self.d * 2
         return y
+
+
+class TPLlamaModel:
+    """Token ids to logits over the ranks of `tp`: the next rung above the sharded decoder layer
+    (the reference's module ladder, tests/test_modules.py:133-211, stops at one layer on one
+    device).  The activations stay sharded by rows from the embedding to the logits: every rank
+    looks up its own block of tokens (the table, the final norm and the output projection are
+    replicated), runs the stack of TPDecoderLayer, which share one set of peer buffers, and
+    returns the logits of its rows."""
+
+    def __init__(self, tp: TPGroup, weights: Dict, heads: int, eps: float, cos: torch.Tensor,
+                 sin: torch.Tensor, batch: int, seq: int):
+        self.tp, self.eps = tp, eps
+        self.embed = K.copy_host_to_sticks(weights["embed"].contiguous())
+        self.final_norm = K.copy_host_to_sticks(weights["final_norm"].contiguous())
+        self.lm_head = K.copy_host_to_sticks(weights["lm_head"].contiguous())
+        self.layers: List[TPDecoderLayer] = []
+        for w in weights["layers"]:
+            shared = self.layers[0].buffers if self.layers else None
+            self.layers.append(TPDecoderLayer(tp, w, heads, eps, cos, sin, batch, seq, buffers=shared))
+        self.rows = self.layers[0].rows if self.layers else batch * seq // tp.world
+
+    def __call__(self, ids_shard: torch.Tensor) -> StickTensor:
+        """`ids_shard`: this rank's block of the flattened [batch * seq] token ids (int32 or int64,
+        on this rank's GPU).  Returns the [rows, vocab] logits of those tokens."""
+        if ids_shard.numel() != self.rows:
+            raise ValueError(f"expected {self.rows} token ids, got {ids_shard.numel()}")
+        x = K.embedding_rows(self.embed, ids_shard)
+        for layer in self.layers:
+            x = layer(x)
+        x = K.rmsnorm_rows(x, self.final_norm, self.eps)
+        return K.matmul(x, self.lm_head, b_kmajor=True)
