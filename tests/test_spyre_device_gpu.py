@@ -486,3 +486,28 @@ def test_non_blocking_copy_from_pinned_memory():
         d = torch.empty(shape, dtype=torch.float16, device=DEV)
         d.copy_(xp, non_blocking=True)
         assert torch.equal(d.cpu(), x)
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (3, 2048, 4096), (5000, 3000), (17, 1000, 520), (2, 3, 1024, 1024)])
+def test_large_pageable_tensors_round_trip(shape):
+    """Pageable host tensors of more than a few MiB are staged through pinned blocks by helper
+    threads, chunk by chunk (torch's own tensors are pageable unless pinned): bit-exact both ways,
+    into a fresh `.cpu()` result and into an existing tensor, back to back so that the blocks and
+    the events are reused, and from a host tensor with gaps between its leading slices."""
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn(*shape, generator=g).half()
+    assert not x.is_pinned()
+    d1, d2 = x.to(DEV), (x + 1).to(DEV)
+    assert torch.equal(d1.cpu(), x)
+    assert torch.equal(d2.cpu(), x + 1)
+    out = torch.zeros_like(x)
+    out.copy_(d1)
+    assert torch.equal(out, x)
+    big = torch.randn(shape[0], 2, *shape[1:], generator=g).half()
+    gappy = big[:, 0]                       # leading slices one slice apart
+    assert not gappy.is_contiguous()
+    assert torch.equal(gappy.to(DEV).cpu(), gappy)
+    # a pinned copy in between takes the direct path and leaves the pageable one intact
+    xp = x.pin_memory()
+    assert torch.equal(xp.to(DEV, non_blocking=True).cpu(), x)
+    assert torch.equal(x.to(DEV).cpu(), x)

@@ -12,7 +12,11 @@
 //   * transpose_tiles  - the unit-stride dims differ (a permuted host tensor):
 //                        64x64 fp16 tiles are transposed through shared memory.
 #include <algorithm>
+#include <condition_variable>
+#include <cstring>
 #include <mutex>
+#include <thread>
+#include <vector>
 
 #include "common.cuh"
 
@@ -850,7 +854,133 @@ struct CopyPipe {
   bool ready = false, failed = false;
   cudaStream_t copy = nullptr;
   cudaEvent_t copied[2] = {nullptr, nullptr}, relaid[2] = {nullptr, nullptr};
+  // pinned bounce blocks for pageable host memory, one per staging half, grown on demand
+  void* pin[2] = {nullptr, nullptr};
+  int64_t pin_bytes = 0;
 };
+
+// ---- pageable host memory ---------------------------------------------------------------------
+// cudaMemcpyAsync on pageable memory is staged by the driver through one thread's memcpy, about
+// 10 GB/s here, and a freshly allocated destination (what `.cpu()` returns) adds its page faults to
+// that thread: 2 GB/s.  For chunked copies of pageable tensors the library stages the chunks
+// itself instead: a few threads copy between the tensor and a pinned block (the page faults of a
+// fresh destination spread over them) while the DMA engine moves the neighbouring chunk.
+constexpr int64_t kBounceMinBytes = 4ll << 20;   // smaller copies are not worth the threads
+constexpr int64_t kBounceMaxChunk = 32ll << 20;  // largest chunk a pinned block is grown to
+
+bool is_pageable(const void* p) {
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;   // unknown: leave it to the driver
+  }
+  return attr.type == cudaMemoryTypeUnregistered;
+}
+
+// Helper threads that live for one copy call (nothing outlives the call, so a later fork() of the
+// process finds no thread of the library missing).  copy() splits a span into page-aligned
+// slices, one per thread, and returns when all are done.
+class HostCopyTeam {
+ public:
+  explicit HostCopyTeam(int threads) {
+    for (int i = 1; i < threads; ++i) {
+      try {
+        helpers_.emplace_back([this, i] { worker(i); });
+      } catch (...) {
+        break;   // fewer helpers: the slices just get larger
+      }
+    }
+    n_ = (int)helpers_.size() + 1;
+  }
+  ~HostCopyTeam() {
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      stop_ = true;
+    }
+    cv_start_.notify_all();
+    for (auto& t : helpers_) t.join();
+  }
+  void copy(void* dst, const void* src, size_t bytes) {
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      dst_ = (char*)dst;
+      src_ = (const char*)src;
+      bytes_ = bytes;
+      slice_ = ((bytes / n_ + 4095) / 4096 + 1) * 4096;
+      pending_ = n_ - 1;
+      ++generation_;
+    }
+    cv_start_.notify_all();
+    copy_slice(0);
+    std::unique_lock<std::mutex> lock(mu_);
+    cv_done_.wait(lock, [this] { return pending_ == 0; });
+  }
+
+ private:
+  void copy_slice(int id) {
+    const size_t lo = std::min(bytes_, (size_t)id * slice_), hi = std::min(bytes_, lo + slice_);
+    if (hi > lo) std::memcpy(dst_ + lo, src_ + lo, hi - lo);
+  }
+  void worker(int id) {
+    uint64_t seen = 0;
+    std::unique_lock<std::mutex> lock(mu_);
+    for (;;) {
+      cv_start_.wait(lock, [&] { return stop_ || generation_ != seen; });
+      if (stop_) return;
+      seen = generation_;
+      lock.unlock();
+      copy_slice(id);
+      lock.lock();
+      if (--pending_ == 0) cv_done_.notify_one();
+    }
+  }
+  std::mutex mu_;
+  std::condition_variable cv_start_, cv_done_;
+  std::vector<std::thread> helpers_;
+  char* dst_ = nullptr;
+  const char* src_ = nullptr;
+  size_t bytes_ = 0, slice_ = 0;
+  uint64_t generation_ = 0;
+  int pending_ = 0, n_ = 1;
+  bool stop_ = false;
+};
+
+int bounce_threads() {
+  const unsigned hw = std::thread::hardware_concurrency();
+  return (int)std::min(8u, std::max(2u, hw / 4));
+}
+
+// Makes both pinned blocks at least `bytes` large.  Called with the pipe's mutex held and no DMA
+// of an earlier call still using the blocks (the callers wait for the `copied` events first).
+bool grow_bounce(CopyPipe* pipe, int64_t bytes) {
+  if (pipe->pin_bytes >= bytes) return true;
+  for (int i = 0; i < 2; ++i) {
+    if (pipe->pin[i]) cudaFreeHost(pipe->pin[i]);
+    pipe->pin[i] = nullptr;
+  }
+  pipe->pin_bytes = 0;
+  for (int i = 0; i < 2; ++i) {
+    if (cudaHostAlloc(&pipe->pin[i], (size_t)bytes, cudaHostAllocDefault) != cudaSuccess) {
+      cudaGetLastError();
+      for (int j = 0; j < 2; ++j) {
+        if (pipe->pin[j]) cudaFreeHost(pipe->pin[j]);
+        pipe->pin[j] = nullptr;
+      }
+      return false;
+    }
+  }
+  pipe->pin_bytes = bytes;
+  return true;
+}
+
+// Whether this chunked copy goes through the pinned blocks, which are then ready for it.
+bool use_bounce(CopyPipe* pipe, const void* host, int64_t bytes, int64_t chunk_span) {
+  if (bytes < kBounceMinBytes || chunk_span > kBounceMaxChunk || !is_pageable(host)) return false;
+  // the blocks may still be the source or target of an earlier call's last DMAs
+  if (cudaEventSynchronize(pipe->copied[0]) != cudaSuccess || cudaEventSynchronize(pipe->copied[1]) != cudaSuccess)
+    return false;
+  return grow_bounce(pipe, (chunk_span + 4095) & ~(int64_t)4095);
+}
 CopyPipe g_pipes[kMaxDevices];
 
 CopyPipe* pipe_for_current_device() {
@@ -939,14 +1069,25 @@ extern "C" int ts_copy_host_to_sticks_pipelined(const void* host, void* staging,
   // the copy stream may not touch the staging block before work already queued on `stream` is done with it
   if (cudaEventRecord(pipe->relaid[0], st) != cudaSuccess ||
       cudaStreamWaitEvent(pipe->copy, pipe->relaid[0], 0) != cudaSuccess) return TS_ERR_CUDA;
+  const int64_t chunk_span = (std::min(c.rows_per_chunk, host_size[0]) - 1) * c.row_bytes + c.rest_bytes;
+  const bool bounce = use_bounce(pipe, host, bytes, chunk_span);
+  HostCopyTeam team(bounce ? bounce_threads() : 1);
   int k = 0;
   for (int64_t r0 = 0; r0 < host_size[0]; r0 += c.rows_per_chunk, ++k) {
     const int slot = k & 1;
     const int64_t rows = std::min(c.rows_per_chunk, host_size[0] - r0);
     const int64_t span = (rows - 1) * c.row_bytes + c.rest_bytes;
     char* stage = (char*)staging + slot * half;
+    const char* from = (const char*)host + r0 * c.row_bytes;
+    if (bounce) {
+      // the DMA that last read this pinned block (chunk k - 2) must be done before it is refilled;
+      // the threads fill it while the DMA of chunk k - 1 runs
+      if (k >= 2 && cudaEventSynchronize(pipe->copied[slot]) != cudaSuccess) return TS_ERR_CUDA;
+      team.copy(pipe->pin[slot], from, (size_t)span);
+      from = (const char*)pipe->pin[slot];
+    }
     if (k >= 2 && cudaStreamWaitEvent(pipe->copy, pipe->relaid[slot], 0) != cudaSuccess) return TS_ERR_CUDA;
-    if (cudaMemcpyAsync(stage, (const char*)host + r0 * c.row_bytes, (size_t)span, cudaMemcpyHostToDevice,
+    if (cudaMemcpyAsync(stage, from, (size_t)span, cudaMemcpyHostToDevice,
                         pipe->copy) != cudaSuccess ||
         cudaEventRecord(pipe->copied[slot], pipe->copy) != cudaSuccess ||
         cudaStreamWaitEvent(st, pipe->copied[slot], 0) != cudaSuccess)
@@ -991,6 +1132,11 @@ extern "C" int ts_copy_sticks_to_host_pipelined(const void* sticks, void* stagin
   int64_t hs[kMaxDims], ds[kMaxDims];
   for (int i = 0; i < rank; ++i) hs[i] = host_size[i];
   for (int i = 0; i < ndev; ++i) ds[i] = device_size[i];
+  const int64_t chunk_span = (std::min(c.rows_per_chunk, host_size[0]) - 1) * c.row_bytes + c.rest_bytes;
+  const bool bounce = use_bounce(pipe, host, bytes, chunk_span);
+  HostCopyTeam team(bounce ? bounce_threads() : 1);
+  char* landed_to = nullptr;      // with the bounce: where the chunk before this one goes, and its size
+  int64_t landed_span = 0;
   int k = 0;
   for (int64_t r0 = 0; r0 < host_size[0]; r0 += c.rows_per_chunk, ++k) {
     const int slot = k & 1;
@@ -1005,12 +1151,28 @@ extern "C" int ts_copy_sticks_to_host_pipelined(const void* sticks, void* stagin
                                            elem_bytes, hs, host_strides, rank, ds, device_strides, dim_map, ndev,
                                            stream);
     if (rc != TS_OK) return rc;
+    char* to = (char*)host + r0 * c.row_bytes;
     if (cudaEventRecord(pipe->relaid[slot], st) != cudaSuccess ||
         cudaStreamWaitEvent(pipe->copy, pipe->relaid[slot], 0) != cudaSuccess ||
-        cudaMemcpyAsync((char*)host + r0 * c.row_bytes, stage, (size_t)span, cudaMemcpyDeviceToHost,
+        cudaMemcpyAsync(bounce ? (char*)pipe->pin[slot] : to, stage, (size_t)span, cudaMemcpyDeviceToHost,
                         pipe->copy) != cudaSuccess ||
         cudaEventRecord(pipe->copied[slot], pipe->copy) != cudaSuccess)
       return TS_ERR_CUDA;
+    if (bounce) {
+      // while this chunk's DMA runs, the threads move the one before it from its pinned block to
+      // the tensor (that block is not written again before the next iteration's DMA)
+      if (landed_to) {
+        if (cudaEventSynchronize(pipe->copied[slot ^ 1]) != cudaSuccess) return TS_ERR_CUDA;
+        team.copy(landed_to, pipe->pin[slot ^ 1], (size_t)landed_span);
+      }
+      landed_to = to;
+      landed_span = span;
+    }
+  }
+  if (bounce && landed_to) {
+    const int last = (k - 1) & 1;
+    if (cudaEventSynchronize(pipe->copied[last]) != cudaSuccess) return TS_ERR_CUDA;
+    team.copy(landed_to, pipe->pin[last], (size_t)landed_span);
   }
   // synchronising `stream` must cover the copies
   for (int slot = 0; slot < 2 && slot < k; ++slot)
