@@ -99,8 +99,14 @@ int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int el
  * needs staging_bytes >= ts_host_span_bytes(...) (TS_ERR_TOO_LARGE otherwise).
  * First use on a device creates that device's copy stream and four events
  * (no device memory); later calls on the device reuse them and are serialised
- * while they enqueue.  Same reference interfaces as above
- * (torch_spyre/csrc/spyre_mem.cpp:408-438).
+ * while they enqueue.  A pageable (neither pinned nor registered) host tensor
+ * of 4 MiB or more is staged by the library itself rather than by the driver:
+ * helper threads that live for the one call copy between it and two pinned
+ * blocks of one chunk each (allocated per device on first need, at most 32 MiB
+ * each) while the neighbouring chunk is on the bus; for such a tensor the
+ * device-to-host call has the data in `host` when it returns, and the
+ * host-to-device call no longer reads `host` after it returns.  Same reference
+ * interfaces as above (torch_spyre/csrc/spyre_mem.cpp:408-438).
  */
 int64_t ts_copy_staging_bytes(int elem_bytes, const int64_t* host_size, const int64_t* host_strides,
                               int rank);
