@@ -952,6 +952,33 @@ def host_overheads(dev):
     return out
 
 
+def host_copy_rates(dev):
+    """GB/s of the device's host copies for a [4096, 8192] fp16 tensor (64 MiB) through the public
+    API: pinned and pageable sources, an existing pageable destination and the fresh one `.cpu()`
+    returns.  Wall clock around blocking calls."""
+    import torch_spyre  # noqa: F401
+
+    sdev = torch.device("spyre", dev.index)
+    x = torch.randn(4096, 8192, generator=torch.Generator().manual_seed(6)).half()
+    xp, y = x.pin_memory(), torch.empty_like(x)
+    yp = torch.empty_like(x).pin_memory()
+    d = xp.to(sdev)
+    gb = x.numel() * 2 / 1e9
+
+    def rate(fn, n=3):
+        fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+        return gb * n / (time.perf_counter() - t0)
+
+    return {"pinned_to_device": rate(lambda: xp.to(sdev)), "pageable_to_device": rate(lambda: x.to(sdev)),
+            "device_to_pinned": rate(lambda: yp.copy_(d)), "device_to_pageable": rate(lambda: y.copy_(d)),
+            "device_to_fresh_cpu_tensor": rate(lambda: d.cpu()), "unit": "GB/s, [4096, 8192] fp16"}
+
+
 def measure_tp(run):
     """config 5's layer as ONE layer split over the ranks (tensor parallel, sequence-parallel
     activations): each rank holds 1/N of every weight and of the rows, the two reduce-scatters run in
@@ -1116,6 +1143,7 @@ def main():
     release()
     if world == 1 and not args.no_e2e:
         line["host_us_per_launch"] = host_overheads(dev)
+        line["host_copy_gbs"] = host_copy_rates(dev)
         release()
 
     if args.workload == "all":
