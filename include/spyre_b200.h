@@ -105,7 +105,9 @@ int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int el
  * blocks of one chunk each (allocated per device on first need, at most 32 MiB
  * each) while the neighbouring chunk is on the bus; for such a tensor the
  * device-to-host call has the data in `host` when it returns, and the
- * host-to-device call no longer reads `host` after it returns.  Same reference
+ * host-to-device call no longer reads `host` after it returns; the destination
+ * of such a device-to-host copy is marked for transparent huge pages
+ * (madvise), so that freshly allocated memory faults in 2 MiB at a time.  Same reference
  * interfaces as above (torch_spyre/csrc/spyre_mem.cpp:408-438).
  */
 int64_t ts_copy_staging_bytes(int elem_bytes, const int64_t* host_size, const int64_t* host_strides,

@@ -18,6 +18,8 @@
 #include <thread>
 #include <vector>
 
+#include <sys/mman.h>
+
 #include "common.cuh"
 
 namespace tsb {
@@ -945,6 +947,27 @@ class HostCopyTeam {
   bool stop_ = false;
 };
 
+// A destination that was only just allocated (the result of `.cpu()`) takes a page fault for
+// every 4 KiB the threads write.  Asking for transparent huge pages over its 2 MiB-aligned
+// interior turns those into one fault per 2 MiB where the system allows it ("madvise" or
+// "always" mode): 5.3 -> 9.8 GB/s for a fresh 128 MiB destination, no change for one that is
+// already backed by pages (measured in one process).  For memory that is not anonymous, or where
+// the system says "never", the call fails or does nothing.
+void advise_huge_pages(void* p, int64_t bytes) {
+#ifdef MADV_HUGEPAGE
+#ifdef TSB_TUNING
+  const char* knob = getenv("TS_COPY_HUGEPAGE");   // experiment: 0 = never
+  if (knob && knob[0] == '0') return;
+#endif
+  const uintptr_t two_mib = (uintptr_t)2 << 20;
+  const uintptr_t lo = ((uintptr_t)p + two_mib - 1) & ~(two_mib - 1), hi = ((uintptr_t)p + (uintptr_t)bytes) & ~(two_mib - 1);
+  if (hi > lo) (void)madvise((void*)lo, hi - lo, MADV_HUGEPAGE);
+#else
+  (void)p;
+  (void)bytes;
+#endif
+}
+
 int bounce_threads() {
   const unsigned hw = std::thread::hardware_concurrency();
   return (int)std::min(8u, std::max(2u, hw / 4));
@@ -1135,6 +1158,7 @@ extern "C" int ts_copy_sticks_to_host_pipelined(const void* sticks, void* stagin
   const int64_t chunk_span = (std::min(c.rows_per_chunk, host_size[0]) - 1) * c.row_bytes + c.rest_bytes;
   const bool bounce = use_bounce(pipe, host, bytes, chunk_span);
   HostCopyTeam team(bounce ? bounce_threads() : 1);
+  if (bounce) advise_huge_pages(host, bytes);
   char* landed_to = nullptr;      // with the bounce: where the chunk before this one goes, and its size
   int64_t landed_span = 0;
   int k = 0;
