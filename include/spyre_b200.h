@@ -112,6 +112,11 @@ int ts_copy_sticks_to_host(const void* sticks, void* staging, void* host, int el
  */
 int64_t ts_copy_staging_bytes(int elem_bytes, const int64_t* host_size, const int64_t* host_strides,
                               int rank);
+/* The helper-thread copy the pipelined calls use for pageable host memory, on its own: copies
+ * `bytes` bytes from `src` to `dst` (host pointers, not overlapping) with `threads` threads
+ * (1..64) that exist only for the call.  Needs no GPU; for tests of the host logic.  No
+ * counterpart in the reference. */
+int ts_host_copy_selftest(void* dst, const void* src, int64_t bytes, int threads);
 int ts_copy_host_to_sticks_pipelined(const void* host, void* staging, int64_t staging_bytes, void* sticks,
                                      int elem_bytes, const int64_t* host_size,
                                      const int64_t* host_strides, int rank, const int64_t* device_size,

@@ -126,3 +126,25 @@ def test_row_ops_validation_without_gpu():
     assert lib.ts_reduce_mid(16, 16, 4, 4, 63, 1, 1.0, None, None) == -1
     assert lib.ts_reduce_mid_scratch_bytes(1, 1 << 20, 64) > 0
     assert lib.ts_reduce_mid_scratch_bytes(4096, 16, 4096) == 0
+
+
+@pytest.mark.parametrize("threads", [1, 2, 5, 8])
+def test_helper_thread_copy_of_the_pageable_path(threads):
+    """The team of helper threads that stages pageable host tensors (csrc/relayout.cu): every byte
+    arrives, nothing beyond the span is written, for sizes around the slice and page boundaries
+    and for more threads than pages; bad arguments are refused."""
+    import numpy as np
+
+    lib = _abi.lib()
+    rng = np.random.default_rng(threads)
+    for n in (0, 1, 4095, 4096, 4097, 70_000, (8 << 20) + 13, 33 << 20):
+        src = rng.integers(0, 256, size=n + 64, dtype=np.uint8)
+        dst = np.full(n + 64, 0xEE, dtype=np.uint8)
+        rc = lib.ts_host_copy_selftest(dst.ctypes.data, src.ctypes.data, n, threads)
+        assert rc == _abi.TS_OK
+        assert np.array_equal(dst[:n], src[:n])
+        assert (dst[n:] == 0xEE).all()
+    buf = np.zeros(16, dtype=np.uint8)
+    assert lib.ts_host_copy_selftest(buf.ctypes.data, buf.ctypes.data, -1, 2) == _abi.TS_ERR_INVALID
+    assert lib.ts_host_copy_selftest(buf.ctypes.data, buf.ctypes.data, 8, 0) == _abi.TS_ERR_INVALID
+    assert lib.ts_host_copy_selftest(None, buf.ctypes.data, 8, 2) == _abi.TS_ERR_INVALID

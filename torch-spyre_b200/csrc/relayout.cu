@@ -1066,6 +1066,14 @@ extern "C" int64_t ts_copy_staging_bytes(int elem_bytes, const int64_t* host_siz
   return std::min<int64_t>((span + 255) & ~(int64_t)255, 2 * chunk);
 }
 
+extern "C" int ts_host_copy_selftest(void* dst, const void* src, int64_t bytes, int threads) {
+  if (bytes < 0 || threads < 1 || threads > 64 || (bytes > 0 && (!dst || !src))) return TS_ERR_INVALID;
+  tsb::HostCopyTeam team(threads);
+  for (int rep = 0; rep < 2; ++rep)   // twice: a team serves every chunk of a call
+    team.copy(dst, src, (size_t)bytes);
+  return TS_OK;
+}
+
 extern "C" int ts_copy_host_to_sticks_pipelined(const void* host, void* staging, int64_t staging_bytes,
                                                 void* sticks, int elem_bytes, const int64_t* host_size,
                                                 const int64_t* host_strides, int rank,

@@ -90,6 +90,7 @@ SIGNATURES = {
                                    ctypes.c_int64, ctypes.c_int, ctypes.c_int, vp]),
     "ts_gemm_error_state": (ctypes.c_int, []),
     "ts_gemm_wait_selftest": (ctypes.c_int, [ctypes.c_int64, vp]),
+    "ts_host_copy_selftest": (ctypes.c_int, [vp, vp, ctypes.c_int64, ctypes.c_int]),
     "ts_peer_copy_2d": (ctypes.c_int, [vp, ctypes.c_int64, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, vp]),
     "ts_gemm_f16_scatter_add": (ctypes.c_int, [vp, vp, ctypes.POINTER(vp), ctypes.c_int, ctypes.c_int64,
                                                ctypes.c_int64, ctypes.c_int64, ctypes.c_int, vp]),
