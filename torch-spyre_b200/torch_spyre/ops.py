@@ -16,10 +16,11 @@ from __future__ import annotations
 from typing import List, Optional, Sequence, Tuple
 
 import contextlib
+import threading
 
 import torch
 
-from . import _C, stick_ops as K
+from . import _C, _abi, stick_ops as K
 from .stick_ops import Chain, StickTensor
 
 _lib = torch.library.Library("aten", "IMPL")
@@ -106,12 +107,60 @@ def _with_device(t: torch.Tensor):
 
 # ---- pointwise -------------------------------------------------------------------------
 
+# One-output chains of the eager ops, marshalled once per (program, shapes) and thread: a call
+# patches the operand pointers (and the immediate) into the cached ctypes arrays and enqueues.
+# Building the instruction structs, the shape arrays and a CUDA view of every operand's storage
+# anew for each op was most of an eager op's host time.
+_tls = threading.local()
+_PLACEHOLDER = [object() for _ in range(4)]
+
+
+def _launch_cached(key, program, out_shape, in_shapes, in_tensors, out: torch.Tensor, imm=None) -> bool:
+    """False, having done nothing, if an operand is a view that is not its own stick image (the
+    caller then takes the general route, which copies such views first)."""
+    for t in in_tensors:
+        if not _C.is_canonical(t):
+            return False
+    plans = getattr(_tls, "plans", None)
+    if plans is None:
+        plans = _tls.plans = {}
+    plan = plans.get(key)
+    if plan is None:
+        if len(plans) >= 1024:
+            plans.clear()
+        chain = Chain()
+        program(chain, [chain.tensor(_PLACEHOLDER[i]) for i in range(len(in_shapes))])
+        shape = tuple(out_shape) if len(out_shape) else (1,)
+        flat: List[int] = []
+        for s_in in in_shapes:
+            flat += K.broadcast_shape4(shape, s_in)
+        shape4 = [1] * (4 - len(shape)) + list(shape) if len(shape) <= 4 else K.broadcast_shape4(shape, shape)
+        imm_at = next((i for i, ins in enumerate(chain.insns) if ins.a_kind == K.IMM), -1)   # emit() puts it in slot a
+        plan = plans[key] = ((_abi.PwInsn * len(chain.insns))(*chain.insns), len(chain.insns),
+                             _abi.ptrs([0] * len(in_shapes)), _abi.i64(flat), len(in_shapes), _abi.ptrs([0]),
+                             _abi.i64(shape4), imm_at, _abi.lib().ts_pointwise_chain)
+    insns, n, in_ptrs, shapes, n_in, out_ptrs, shape4, imm_at, fn = plan
+    for i, t in enumerate(in_tensors):
+        in_ptrs[i] = _C.storage_ptr(t)
+    out_ptrs[0] = _C.storage_ptr(out)
+    if imm_at >= 0:
+        insns[imm_at].a_imm = imm
+    rc = fn(insns, n, in_ptrs, shapes, n_in, out_ptrs, 1, shape4, 0, 1.0, None, 0, 1, K._stream())
+    if rc != 0:
+        _abi.check(rc, "ts_pointwise_chain")
+    return True
+
+
 def _unary(op: str, x: torch.Tensor) -> torch.Tensor:
     _check_fp16(x)
     out = _new(x.shape, x)
     if x.numel() == 0:
         return out
     with _with_device(x):
+        shape = tuple(x.shape)
+        if _launch_cached(("u", op, shape), lambda c, t: c.emit("LOAD", t[0]).emit(op).store(0), shape, (shape,),
+                          (x,), out):
+            return out
         c = Chain()
         c.emit("LOAD", c.tensor(_st(x))).emit(op).store(0)
         K.run_chain(c, x.shape, outputs=[_st(out)])
@@ -151,6 +200,16 @@ def _binary(op: str, a, b, rop: Optional[str] = None, alpha=1) -> torch.Tensor:
     if out.numel() == 0:
         return out
     with _with_device(a):
+        if alpha == 1 or _is_number(b):
+            sa = tuple(a.shape)
+            if _is_number(b):
+                if _launch_cached(("s", op, sa), lambda c, t: c.emit("LOAD", t[0]).emit(op, c.imm(0.0)).store(0),
+                                  shape, (sa,), (a,), out, imm=_number(b) * alpha):
+                    return out
+            elif b.device == a.device and b.dtype == torch.float16:
+                if _launch_cached(("b", op, sa, shape_b), lambda c, t: c.emit("LOAD", t[0]).emit(op, t[1]).store(0),
+                                  shape, (sa, shape_b), (a, b), out):
+                    return out
         c = Chain()
         if alpha != 1 and not _is_number(b):
             c.emit("LOAD", _operand(c, b, a)).emit("MUL", c.imm(alpha)).save(0)
